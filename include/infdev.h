@@ -1,0 +1,116 @@
+/* infdev: the thin C-ABI device layer under the MTLQwen Engine.
+ *
+ * It stands where the reference's Metal backend stands (backend/metal/device.hpp:17-140): buffers, a
+ * serial command stream with a blocking commit, the paged K/V pool, and one typed launch function per
+ * kernel of backend/metal/kernel/*.metal. The reference dispatches kernels by string name with
+ * positional tensors (device.hpp:122-139); here each kernel is a plain C function. All pointers named
+ * "device" are CUDA device addresses; no C++ or torch types cross this boundary.
+ *
+ * Return convention: 0 on success, a negative INFDEV_E_* code otherwise; the text of the last failure
+ * of a context is available from infdev_error(). Launches are asynchronous on the context's stream and
+ * execute in call order, like the reference's barrier-after-every-dispatch encoder (device.hpp:132).
+ */
+#ifndef INFDEV_H
+#define INFDEV_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct infdev_ctx infdev_ctx;
+
+enum {
+  INFDEV_OK = 0,
+  INFDEV_E_CUDA = -1,     /* a CUDA call failed */
+  INFDEV_E_ARGUMENT = -2, /* shape / alignment / type not supported */
+  INFDEV_E_TIMEOUT = -3,  /* commit deadline passed while the stream was still busy */
+  INFDEV_E_DEVICE = -4    /* a kernel gave up on a bounded wait and set the device status word */
+};
+
+/* ggml tensor type ids used by the GGUF files (forward.cpp:55 indexes kernels by `type - 11`). */
+enum { INFDEV_F32 = 0, INFDEV_F16 = 1, INFDEV_Q4_K = 12, INFDEV_Q6_K = 14 };
+
+/* Per-query ragged metadata, the CUDA form of GpuQuery (backend/metal/kernel/batch.hpp:11-16).
+ * previous/next are device addresses of the slot's state record (0 = fresh sequence); state is the first
+ * candidate-state row of a speculative query or 0xffffffff. `seed`/`stream` are additions: the Philox key
+ * of the slot and the absolute index of the first token this query samples. */
+typedef struct infdev_query {
+  uint64_t previous, next;
+  uint32_t start, count, position, slot, state, logit, samples;
+  float temperature, topP;
+  int32_t topK;
+  uint64_t seed;
+} infdev_query;
+
+/* Sizes of one per-slot state record (batch.hpp:3-8 with fp32 instead of fp16 conv taps and MTP seed). */
+enum {
+  INFDEV_CONV_STATE_BYTES = 8192 * 4 * 4,
+  INFDEV_RECURRENT_STATE_BYTES = 32 * 128 * 128 * 4,
+  INFDEV_GDN_LAYER_STATE_BYTES = INFDEV_CONV_STATE_BYTES + INFDEV_RECURRENT_STATE_BYTES
+};
+
+/* ---- context, memory, stream (Device::Device/empty/mapped/copy/command/commit, device.hpp:66-140) ---- */
+infdev_ctx* infdev_create(int device, char* error /* >= 1024 bytes, may be null */);
+void infdev_destroy(infdev_ctx* ctx);
+const char* infdev_error(infdev_ctx* ctx);
+int infdev_sm_count(infdev_ctx* ctx);
+/* hostVisible != 0: pinned host memory mapped into the device (Metal "shared" storage, device.cpp:82-85);
+ * the returned pointer is valid on both sides. Otherwise device memory, zero-filled. */
+void* infdev_alloc(infdev_ctx* ctx, size_t bytes, int hostVisible);
+void infdev_free(infdev_ctx* ctx, void* pointer);
+int infdev_upload(infdev_ctx* ctx, void* device, const void* host, size_t bytes);
+int infdev_download(infdev_ctx* ctx, void* host, const void* device, size_t bytes);
+int infdev_copy(infdev_ctx* ctx, void* destination, const void* source, size_t bytes);
+int infdev_fill(infdev_ctx* ctx, void* device, int byte, size_t bytes);
+/* Device::commit (device.cpp:138-145) with a deadline instead of an unbounded wait: blocks until the
+ * stream drains or timeoutMs passes (0 = no deadline), then reports the device status word. */
+int infdev_commit(infdev_ctx* ctx, uint32_t timeoutMs);
+/* Timing on the context's stream. */
+void* infdev_event_create(infdev_ctx* ctx);
+void infdev_event_destroy(infdev_ctx* ctx, void* event);
+int infdev_event_record(infdev_ctx* ctx, void* event);
+float infdev_event_elapsed_ms(infdev_ctx* ctx, void* start, void* stop);
+/* Overwrites `bytes` of scratch (>= L2 size) so the next launch starts with a cold L2. */
+int infdev_flush_l2(infdev_ctx* ctx);
+/* Activation split of the tensor-core GEMV: 2 = hi+lo fp16 (fp32-accurate, default), 1 = hi only. */
+int infdev_set_xsplit(infdev_ctx* ctx, int xsplit);
+/* CUDA-graph capture of a pass on the context's stream (no reference counterpart: Metal re-encodes every
+ * pass). begin/end bracket the launches; launch replays; the handle is freed with graph_destroy. */
+int infdev_graph_begin(infdev_ctx* ctx);
+void* infdev_graph_end(infdev_ctx* ctx);
+int infdev_graph_launch(infdev_ctx* ctx, void* graph);
+void infdev_graph_destroy(infdev_ctx* ctx, void* graph);
+
+/* ---- quantised linear algebra ---- */
+/* Block dequantisation to fp32, bit-exact with dequant_tile (quant_linear.metal:32-48 Q4_K, :69-85 Q6_K). */
+int infdev_dequant(infdev_ctx* ctx, int type, const void* blocks, int64_t count, float* out);
+/* y[m,n] = x[m,k] . W[n,k]^T (+ residual[m,n]); replaces Ops::linear (forward.cpp:51-70) over
+ * linear_decode_q4_k[_add] (quant_linear.metal:245-327), linear_decode_q6_k[_add] (:436-512) and, for
+ * m > 8, linear_prefill (:151-233). x, y, residual fp32 row-major; residual may alias y or be null. */
+int infdev_linear(infdev_ctx* ctx, int type, const void* w, int64_t n, int64_t k, const float* x, int64_t m, float* y, const float* residual);
+/* Up to four weight matrices sharing x in one launch (the q/k/v and qkv/z projections of Ops::decoder,
+ * forward.cpp:86-88, 98). */
+int infdev_linear_group(infdev_ctx* ctx, int type, int count, const void* const* w, const int64_t* n, int64_t k, const float* x, int64_t m,
+                        float* const* y);
+/* y[m,n] = silu(x.Wg^T) * (x.Wu^T): mlp_gate_up_q4_k_decode (fused_kernels.metal:11-78) and the post == 2
+ * epilogue of linear_prefill (quant_linear.metal:224-232). */
+int infdev_gate_up(infdev_ctx* ctx, int type, const void* wg, const void* wu, int64_t n, int64_t k, const float* x, int64_t m, float* y);
+
+/* ---- elementwise / normalisation ---- */
+/* Per-row token ids: embedding_q4_k's source selection (quant_linear.metal:581-584). mode 0 target pass
+ * (request ids, or draft proposals for speculative rows > 0), mode 2 previous MTP proposal. */
+int infdev_gather_tokens(infdev_ctx* ctx, const infdev_query* queries, int queryCount, const int32_t* requestData, uint32_t capacity,
+                         const int32_t* proposals, uint32_t mode, int32_t* rowTokens);
+/* out[row] = dequant(table[tokens[row]]): embedding_q4_k (quant_linear.metal:572-591), plus a Q6_K table. */
+int infdev_embedding(infdev_ctx* ctx, int type, const void* table, int64_t k, const int32_t* rowTokens, int64_t rows, float* out);
+/* rms_norm (native_ops.metal:6-34): y = x * rsqrt(mean(x^2) + 1e-6) * w over `dim` = 4096. */
+int infdev_rms_norm(infdev_ctx* ctx, const float* x, const float* w, int64_t rows, int64_t dim, float* y);
+/* rms_norm_gather (native_ops.metal:12-15): row i of y normalises the i-th sampled row of the pass. */
+int infdev_rms_norm_gather(infdev_ctx* ctx, const float* x, const float* w, const infdev_query* queries, int queryCount, int64_t count, float* y);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,361 @@
+// C-ABI device layer: context, memory, stream, and the typed kernel entry points declared in
+// include/infdev.h. This file holds no math; it validates arguments and launches.
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <unordered_map>
+#include "kernels.h"
+#include "ops.h"
+
+struct infdev_ctx {
+  int device = 0, sms = 0, xsplit = 2;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t done = nullptr;
+  int* status = nullptr;      // device status word written by kernels that abort a bounded wait
+  int* statusHost = nullptr;  // pinned mirror
+  void* flush = nullptr;
+  size_t flushBytes = 0;
+  std::mutex mutex;
+  std::unordered_map<void*, int> allocations;  // pointer -> hostVisible
+  std::string error;
+};
+
+namespace {
+
+int fail(infdev_ctx* ctx, int code, const std::string& text) {
+  if (ctx)
+    ctx->error = text;
+  return code;
+}
+
+int check(infdev_ctx* ctx, cudaError_t e, const char* what) {
+  if (e == cudaSuccess)
+    return INFDEV_OK;
+  return fail(ctx, INFDEV_E_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+struct Bind {  // makes the context's device current for the calling thread
+  explicit Bind(infdev_ctx* ctx) { cudaSetDevice(ctx->device); }
+};
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+extern "C" {
+
+infdev_ctx* infdev_create(int device, char* error) {
+  auto report = [&](const std::string& text) {
+    if (error) {
+      std::strncpy(error, text.c_str(), 1023);
+      error[1023] = 0;
+    }
+    return static_cast<infdev_ctx*>(nullptr);
+  };
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0)
+    return report(std::string("no CUDA device available: ") + cudaGetErrorString(e));
+  if (device < 0 || device >= count)
+    return report("device index out of range");
+  cudaDeviceProp prop;
+  if ((e = cudaSetDevice(device)) != cudaSuccess || (e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess)
+    return report(std::string("cudaSetDevice: ") + cudaGetErrorString(e));
+  if (prop.major != 10)
+    return report("this library contains sm_100a code only; device is sm_" + std::to_string(prop.major * 10 + prop.minor));
+  auto* ctx = new infdev_ctx;
+  ctx->device = device;
+  ctx->sms = prop.multiProcessorCount;
+  if (const char* env = std::getenv("INFENG_XSPLIT"))
+    ctx->xsplit = std::atoi(env) == 1 ? 1 : 2;
+  if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess ||
+      (e = cudaEventCreateWithFlags(&ctx->done, cudaEventDisableTiming)) != cudaSuccess ||
+      (e = cudaMalloc(reinterpret_cast<void**>(&ctx->status), sizeof(int))) != cudaSuccess ||
+      (e = cudaMemset(ctx->status, 0, sizeof(int))) != cudaSuccess ||
+      (e = cudaHostAlloc(reinterpret_cast<void**>(&ctx->statusHost), sizeof(int), cudaHostAllocDefault)) != cudaSuccess) {
+    std::string text = std::string("context setup: ") + cudaGetErrorString(e);
+    delete ctx;
+    return report(text);
+  }
+  *ctx->statusHost = 0;
+  return ctx;
+}
+
+void infdev_destroy(infdev_ctx* ctx) {
+  if (!ctx)
+    return;
+  Bind bind(ctx);
+  cudaStreamSynchronize(ctx->stream);
+  for (auto& entry : ctx->allocations)
+    entry.second ? cudaFreeHost(entry.first) : cudaFree(entry.first);
+  if (ctx->flush)
+    cudaFree(ctx->flush);
+  cudaFree(ctx->status);
+  cudaFreeHost(ctx->statusHost);
+  cudaEventDestroy(ctx->done);
+  cudaStreamDestroy(ctx->stream);
+  delete ctx;
+}
+
+const char* infdev_error(infdev_ctx* ctx) { return ctx ? ctx->error.c_str() : "null context"; }
+
+int infdev_sm_count(infdev_ctx* ctx) { return ctx->sms; }
+
+void* infdev_alloc(infdev_ctx* ctx, size_t bytes, int hostVisible) {
+  Bind bind(ctx);
+  void* pointer = nullptr;
+  if (bytes == 0)
+    bytes = 16;
+  cudaError_t e;
+  if (hostVisible) {
+    e = cudaHostAlloc(&pointer, bytes, cudaHostAllocMapped | cudaHostAllocPortable);
+    if (e == cudaSuccess)
+      std::memset(pointer, 0, bytes);
+  } else {
+    e = cudaMalloc(&pointer, bytes);
+    if (e == cudaSuccess)
+      e = cudaMemsetAsync(pointer, 0, bytes, ctx->stream);
+  }
+  if (check(ctx, e, "infdev_alloc") != INFDEV_OK)
+    return nullptr;
+  std::lock_guard<std::mutex> lock(ctx->mutex);
+  ctx->allocations[pointer] = hostVisible;
+  return pointer;
+}
+
+void infdev_free(infdev_ctx* ctx, void* pointer) {
+  if (!pointer)
+    return;
+  Bind bind(ctx);
+  int hostVisible;
+  {
+    std::lock_guard<std::mutex> lock(ctx->mutex);
+    auto found = ctx->allocations.find(pointer);
+    if (found == ctx->allocations.end())
+      return;
+    hostVisible = found->second;
+    ctx->allocations.erase(found);
+  }
+  // Work already queued on the stream may still use the buffer.
+  cudaStreamSynchronize(ctx->stream);
+  hostVisible ? cudaFreeHost(pointer) : cudaFree(pointer);
+}
+
+int infdev_upload(infdev_ctx* ctx, void* device, const void* host, size_t bytes) {
+  Bind bind(ctx);
+  return check(ctx, cudaMemcpyAsync(device, host, bytes, cudaMemcpyHostToDevice, ctx->stream), "infdev_upload");
+}
+
+int infdev_download(infdev_ctx* ctx, void* host, const void* device, size_t bytes) {
+  Bind bind(ctx);
+  int r = check(ctx, cudaMemcpyAsync(host, device, bytes, cudaMemcpyDeviceToHost, ctx->stream), "infdev_download");
+  return r ? r : check(ctx, cudaStreamSynchronize(ctx->stream), "infdev_download");
+}
+
+int infdev_copy(infdev_ctx* ctx, void* destination, const void* source, size_t bytes) {
+  Bind bind(ctx);
+  return check(ctx, cudaMemcpyAsync(destination, source, bytes, cudaMemcpyDefault, ctx->stream), "infdev_copy");
+}
+
+int infdev_fill(infdev_ctx* ctx, void* device, int byte, size_t bytes) {
+  Bind bind(ctx);
+  return check(ctx, cudaMemsetAsync(device, byte, bytes, ctx->stream), "infdev_fill");
+}
+
+int infdev_commit(infdev_ctx* ctx, uint32_t timeoutMs) {
+  Bind bind(ctx);
+  cudaError_t e = cudaMemcpyAsync(ctx->statusHost, ctx->status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream);
+  if (e == cudaSuccess)
+    e = cudaEventRecord(ctx->done, ctx->stream);
+  if (e != cudaSuccess)
+    return check(ctx, e, "infdev_commit");
+  if (timeoutMs == 0)
+    e = cudaEventSynchronize(ctx->done);
+  else {
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeoutMs);
+    while ((e = cudaEventQuery(ctx->done)) == cudaErrorNotReady) {
+      if (std::chrono::steady_clock::now() > deadline)
+        return fail(ctx, INFDEV_E_TIMEOUT, "commit deadline passed with work still queued on the stream");
+      std::this_thread::sleep_for(std::chrono::microseconds(20));
+    }
+  }
+  if (e != cudaSuccess)
+    return check(ctx, e, "infdev_commit");
+  if (*ctx->statusHost != 0) {
+    const int status = *ctx->statusHost;
+    *ctx->statusHost = 0;
+    cudaMemsetAsync(ctx->status, 0, sizeof(int), ctx->stream);
+    return fail(ctx, INFDEV_E_DEVICE, "a kernel abandoned a bounded wait (device status " + std::to_string(status) + ")");
+  }
+  return INFDEV_OK;
+}
+
+void* infdev_event_create(infdev_ctx* ctx) {
+  Bind bind(ctx);
+  cudaEvent_t event = nullptr;
+  return cudaEventCreate(&event) == cudaSuccess ? event : nullptr;
+}
+
+void infdev_event_destroy(infdev_ctx* ctx, void* event) {
+  Bind bind(ctx);
+  if (event)
+    cudaEventDestroy(static_cast<cudaEvent_t>(event));
+}
+
+int infdev_event_record(infdev_ctx* ctx, void* event) {
+  Bind bind(ctx);
+  return check(ctx, cudaEventRecord(static_cast<cudaEvent_t>(event), ctx->stream), "infdev_event_record");
+}
+
+float infdev_event_elapsed_ms(infdev_ctx* ctx, void* start, void* stop) {
+  Bind bind(ctx);
+  float ms = -1.f;
+  if (cudaEventSynchronize(static_cast<cudaEvent_t>(stop)) != cudaSuccess)
+    return -1.f;
+  cudaEventElapsedTime(&ms, static_cast<cudaEvent_t>(start), static_cast<cudaEvent_t>(stop));
+  return ms;
+}
+
+int infdev_flush_l2(infdev_ctx* ctx) {
+  Bind bind(ctx);
+  if (!ctx->flush) {
+    ctx->flushBytes = size_t(256) << 20;
+    if (int r = check(ctx, cudaMalloc(&ctx->flush, ctx->flushBytes), "infdev_flush_l2"))
+      return r;
+  }
+  return check(ctx, cudaMemsetAsync(ctx->flush, 1, ctx->flushBytes, ctx->stream), "infdev_flush_l2");
+}
+
+int infdev_set_xsplit(infdev_ctx* ctx, int xsplit) {
+  if (xsplit != 1 && xsplit != 2)
+    return fail(ctx, INFDEV_E_ARGUMENT, "xsplit must be 1 or 2");
+  ctx->xsplit = xsplit;
+  return INFDEV_OK;
+}
+
+int infdev_graph_begin(infdev_ctx* ctx) {
+  Bind bind(ctx);
+  return check(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal), "infdev_graph_begin");
+}
+
+void* infdev_graph_end(infdev_ctx* ctx) {
+  Bind bind(ctx);
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  if (check(ctx, cudaStreamEndCapture(ctx->stream, &graph), "infdev_graph_end") != INFDEV_OK)
+    return nullptr;
+  const int r = check(ctx, cudaGraphInstantiate(&exec, graph, 0), "cudaGraphInstantiate");
+  cudaGraphDestroy(graph);
+  return r == INFDEV_OK ? exec : nullptr;
+}
+
+int infdev_graph_launch(infdev_ctx* ctx, void* graph) {
+  Bind bind(ctx);
+  return check(ctx, cudaGraphLaunch(static_cast<cudaGraphExec_t>(graph), ctx->stream), "infdev_graph_launch");
+}
+
+void infdev_graph_destroy(infdev_ctx* ctx, void* graph) {
+  Bind bind(ctx);
+  if (graph)
+    cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(graph));
+}
+
+// ---- quantised linear algebra ----------------------------------------------------------------
+
+int infdev_dequant(infdev_ctx* ctx, int type, const void* blocks, int64_t count, float* out) {
+  Bind bind(ctx);
+  if (type != INFDEV_Q4_K && type != INFDEV_Q6_K)
+    return fail(ctx, INFDEV_E_ARGUMENT, "dequant: type must be Q4_K or Q6_K");
+  return check(ctx, infdev::dequant_launch(type, blocks, count, out, ctx->stream), "dequant");
+}
+
+static int linear_common(infdev_ctx* ctx, int type, bool pair, int count, const void* const* w, const void* const* w2, const int64_t* n, int64_t k,
+                         const float* x, int64_t m, float* const* y, const float* const* residual) {
+  Bind bind(ctx);
+  if (type != INFDEV_Q4_K && type != INFDEV_Q6_K)
+    return fail(ctx, INFDEV_E_ARGUMENT, "linear: weight type must be Q4_K or Q6_K");
+  if (pair && type != INFDEV_Q4_K)
+    return fail(ctx, INFDEV_E_ARGUMENT, "gate_up: only Q4_K pairs are supported");
+  if (count < 1 || count > 4 || m < 0 || k <= 0 || k % 256)
+    return fail(ctx, INFDEV_E_ARGUMENT, "linear: need 1..4 matrices and k a positive multiple of 256");
+  if (type == INFDEV_Q6_K && k % 2048)
+    return fail(ctx, INFDEV_E_ARGUMENT, "linear: Q6_K rows must be 16-byte aligned (k a multiple of 2048)");
+  if (pair && k > 4096)
+    return fail(ctx, INFDEV_E_ARGUMENT, "gate_up: k must not exceed 4096");
+  if (!aligned16(x) || (k % 4))
+    return fail(ctx, INFDEV_E_ARGUMENT, "linear: activations must be 16-byte aligned");
+  infdev::GemvParams p{};
+  p.nseg = count;
+  int tiles = 0;
+  for (int i = 0; i < count; ++i) {
+    if (n[i] <= 0 || n[i] % 16 || !aligned16(w[i]) || (pair && !aligned16(w2[i])))
+      return fail(ctx, INFDEV_E_ARGUMENT, "linear: n must be a positive multiple of 16 and weights 16-byte aligned");
+    p.seg[i] = {static_cast<const uint8_t*>(w[i]), pair ? static_cast<const uint8_t*>(w2[i]) : nullptr, y[i], residual ? residual[i] : nullptr,
+                int(n[i]), int(n[i]), tiles};
+    tiles += int(n[i] / 16);
+  }
+  p.tiles = tiles;
+  p.ldx = int(k);
+  p.k = int(k);
+  p.status = ctx->status;
+  // More than 8 activation rows: 8-row slices re-use the weights out of L2.
+  for (int64_t row = 0; row < m; row += 8) {
+    p.x = x + row * k;
+    p.m = int(m - row < 8 ? m - row : 8);
+    for (int i = 0; i < count; ++i) {
+      p.seg[i].y = y[i] + row * n[i];
+      p.seg[i].res = residual && residual[i] ? residual[i] + row * n[i] : nullptr;
+    }
+    if (int r = check(ctx, infdev::gemv_launch(type, pair, ctx->xsplit, p, ctx->sms, ctx->stream), "gemv launch"))
+      return r;
+  }
+  return INFDEV_OK;
+}
+
+int infdev_linear(infdev_ctx* ctx, int type, const void* w, int64_t n, int64_t k, const float* x, int64_t m, float* y, const float* residual) {
+  return linear_common(ctx, type, false, 1, &w, nullptr, &n, k, x, m, &y, &residual);
+}
+
+int infdev_linear_group(infdev_ctx* ctx, int type, int count, const void* const* w, const int64_t* n, int64_t k, const float* x, int64_t m,
+                        float* const* y) {
+  return linear_common(ctx, type, false, count, w, nullptr, n, k, x, m, y, nullptr);
+}
+
+int infdev_gate_up(infdev_ctx* ctx, int type, const void* wg, const void* wu, int64_t n, int64_t k, const float* x, int64_t m, float* y) {
+  return linear_common(ctx, type, true, 1, &wg, &wu, &n, k, x, m, &y, nullptr);
+}
+
+// ---- elementwise / normalisation ---------------------------------------------------------------
+
+int infdev_gather_tokens(infdev_ctx* ctx, const infdev_query* queries, int queryCount, const int32_t* requestData, uint32_t capacity,
+                         const int32_t* proposals, uint32_t mode, int32_t* rowTokens) {
+  Bind bind(ctx);
+  return check(ctx, infdev::gather_tokens_launch(queries, queryCount, requestData, capacity, proposals, mode, rowTokens, ctx->stream),
+               "gather_tokens");
+}
+
+int infdev_embedding(infdev_ctx* ctx, int type, const void* table, int64_t k, const int32_t* rowTokens, int64_t rows, float* out) {
+  Bind bind(ctx);
+  if ((type != INFDEV_Q4_K && type != INFDEV_Q6_K) || k % 256)
+    return fail(ctx, INFDEV_E_ARGUMENT, "embedding: table must be Q4_K or Q6_K with k a multiple of 256");
+  return check(ctx, infdev::embedding_launch(type, table, k, rowTokens, rows, out, ctx->stream), "embedding");
+}
+
+int infdev_rms_norm(infdev_ctx* ctx, const float* x, const float* w, int64_t rows, int64_t dim, float* y) {
+  Bind bind(ctx);
+  if (dim % 4 || !aligned16(x) || !aligned16(w) || !aligned16(y))
+    return fail(ctx, INFDEV_E_ARGUMENT, "rms_norm: dim must be a multiple of 4 and buffers 16-byte aligned");
+  return check(ctx, infdev::rms_norm_launch(x, w, nullptr, rows, dim, y, ctx->stream), "rms_norm");
+}
+
+int infdev_rms_norm_gather(infdev_ctx* ctx, const float* x, const float* w, const infdev_query* queries, int queryCount, int64_t count, float* y) {
+  Bind bind(ctx);
+  (void)queryCount;
+  return check(ctx, infdev::rms_norm_launch(x, w, queries, count, 4096, y, ctx->stream), "rms_norm_gather");
+}
+
+}  // extern "C"

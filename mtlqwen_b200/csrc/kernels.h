@@ -1,0 +1,27 @@
+// Internal launch interface between the C-ABI layer (infdev.cu) and the kernel files.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace infdev {
+
+// One weight matrix of a grouped GEMV: all segments of a launch share the activations.
+struct GemvSeg {
+  const uint8_t* w;   // [n][k/256] super-blocks
+  const uint8_t* w2;  // second matrix of a gate/up pair, else null
+  float* y;           // [m][ldy]
+  const float* res;   // residual added to the result (may alias y), else null
+  int n, ldy, tile0;  // tile0: index of this segment's first 16-row tile in the launch
+};
+
+struct GemvParams {
+  GemvSeg seg[4];
+  int nseg, tiles;
+  const float* x;  // [m][ldx] fp32, rows 16-byte aligned
+  int ldx, m, k;
+  int* status;
+};
+
+cudaError_t gemv_launch(int type, bool pair, int xsplit, const GemvParams& p, int sms, cudaStream_t stream);
+
+}  // namespace infdev

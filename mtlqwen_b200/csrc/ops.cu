@@ -1,0 +1,163 @@
+// Small memory-bound kernels of the forward step: block dequantisation, embedding gather, RMS norms and
+// the per-row token selection.
+#include "common.cuh"
+#include "ops.h"
+
+namespace infdev {
+namespace {
+
+// scale_min_k4, quant_linear.metal:12-20
+__device__ __forceinline__ void scale_min_k4(int j, const uint8_t* q, int& d, int& m) {
+  if (j < 4) {
+    d = q[j] & 63;
+    m = q[j + 4] & 63;
+  } else {
+    d = (q[j + 4] & 15) | ((q[j - 4] >> 6) << 4);
+    m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4);
+  }
+}
+
+// Element r of a Q4_K super-block, with the multiplication order of dequant_tile (quant_linear.metal:38-45)
+// and no fused multiply-add so the result is bit-identical to a plain fp32 evaluation.
+__device__ __forceinline__ float dequant_q4k_element(const uint8_t* b, int r) {
+  const float d = __half2float(*reinterpret_cast<const __half*>(b)), dm = __half2float(*reinterpret_cast<const __half*>(b + 2));
+  int sc, mn;
+  scale_min_k4(r >> 5, b + 4, sc, mn);
+  const uint8_t q = b[16 + (r >> 6) * 32 + (r & 31)];
+  const int v = (r & 32) ? (q >> 4) : (q & 15);
+  return __fsub_rn(__fmul_rn(__fmul_rn(d, float(sc)), float(v)), __fmul_rn(dm, float(mn)));
+}
+
+// Element r of a Q6_K super-block (quant_linear.metal:75-82).
+__device__ __forceinline__ float dequant_q6k_element(const uint8_t* b, int r) {
+  const float d = __half2float(*reinterpret_cast<const __half*>(b + 208));
+  const int h = r >> 7, rr = r & 127, l = r & 31, s = rr >> 5;
+  const uint8_t q = b[h * 64 + ((rr & 32) ? 32 : 0) + l];
+  const int lo = (rr & 64) ? (q >> 4) : (q & 15), hi = (b[128 + h * 32 + l] >> (2 * s)) & 3;
+  const int sc = int(reinterpret_cast<const int8_t*>(b)[192 + h * 8 + (rr >> 4)]);
+  return __fmul_rn(__fmul_rn(d, float(sc)), float(((hi << 4) | lo) - 32));
+}
+
+template <int TYPE> __global__ void dequant_kernel(const uint8_t* blocks, int64_t count, float* out) {
+  constexpr int bytes = TYPE == 12 ? 144 : 210;
+  const int64_t block = blockIdx.x;
+  if (block >= count)
+    return;
+  const uint8_t* b = blocks + block * bytes;
+  const int r = threadIdx.x;
+  out[block * 256 + r] = TYPE == 12 ? dequant_q4k_element(b, r) : dequant_q6k_element(b, r);
+}
+
+template <int TYPE> __global__ void embedding_kernel(const uint8_t* table, int blocksPerRow, const int32_t* tokens, float* out) {
+  constexpr int bytes = TYPE == 12 ? 144 : 210;
+  const int64_t row = blockIdx.y, token = tokens[row];
+  const int block = blockIdx.x, r = threadIdx.x;
+  const uint8_t* b = table + (token * blocksPerRow + block) * bytes;
+  out[(row * blocksPerRow + block) * 256 + r] = TYPE == 12 ? dequant_q4k_element(b, r) : dequant_q6k_element(b, r);
+}
+
+__device__ __forceinline__ const infdev_query& query_of_row(const infdev_query* queries, uint32_t row) {  // batch.hpp:19-23
+  while (row >= queries->start + queries->count)
+    ++queries;
+  return *queries;
+}
+
+__device__ __forceinline__ const infdev_query& query_of_logit(const infdev_query* queries, uint32_t row) {  // batch.hpp:25-29
+  while (!queries->samples || row >= queries->logit + queries->samples)
+    ++queries;
+  return *queries;
+}
+
+__global__ void gather_tokens_kernel(const infdev_query* queries, int queryCount, const int32_t* requestData, uint32_t capacity,
+                                     const int32_t* proposals, uint32_t mode, int32_t* rowTokens) {
+  const int q = blockIdx.x;
+  if (q >= queryCount)
+    return;
+  const infdev_query info = queries[q];
+  for (uint32_t p = threadIdx.x; p < info.count; p += blockDim.x) {
+    const uint32_t row = info.start + p;
+    int32_t token;
+    if (mode == 2)
+      token = proposals[row];
+    else if (info.state != 0xffffffffu && p)
+      token = proposals[p * 8 + info.state / info.count];
+    else
+      token = requestData[size_t(info.slot) * capacity + info.position + p];
+    rowTokens[row] = token;
+  }
+}
+
+template <bool GATHER>
+__global__ void __launch_bounds__(256) rms_norm_kernel(const float* x, const float* w, const infdev_query* queries, int dim, float* y) {
+  const int row = blockIdx.x;
+  const float* src = x + size_t(row) * dim;
+  if (GATHER) {
+    const infdev_query& info = query_of_logit(queries, row);
+    src = x + size_t(info.start + info.count - info.samples + (row - info.logit)) * dim;
+  }
+  __shared__ float sums[9];
+  float sum = 0.f;
+  for (int d = threadIdx.x * 4; d < dim; d += 1024) {
+    const float4 v = *reinterpret_cast<const float4*>(src + d);
+    sum += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  sum = warp_sum(sum);
+  if ((threadIdx.x & 31) == 0)
+    sums[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < 8 ? sums[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0)
+      sums[8] = rsqrtf(v / float(dim) + 1.0e-6f);
+  }
+  __syncthreads();
+  const float scale = sums[8];
+  for (int d = threadIdx.x * 4; d < dim; d += 1024) {
+    const float4 v = *reinterpret_cast<const float4*>(src + d), g = *reinterpret_cast<const float4*>(w + d);
+    *reinterpret_cast<float4*>(y + size_t(row) * dim + d) = make_float4(v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w);
+  }
+}
+
+}  // namespace
+
+cudaError_t dequant_launch(int type, const void* blocks, int64_t count, float* out, cudaStream_t stream) {
+  if (count <= 0)
+    return cudaSuccess;
+  if (type == 12)
+    dequant_kernel<12><<<unsigned(count), 256, 0, stream>>>(static_cast<const uint8_t*>(blocks), count, out);
+  else
+    dequant_kernel<14><<<unsigned(count), 256, 0, stream>>>(static_cast<const uint8_t*>(blocks), count, out);
+  return cudaGetLastError();
+}
+
+cudaError_t embedding_launch(int type, const void* table, int64_t k, const int32_t* tokens, int64_t rows, float* out, cudaStream_t stream) {
+  if (rows <= 0)
+    return cudaSuccess;
+  const dim3 grid(unsigned(k / 256), unsigned(rows));
+  if (type == 12)
+    embedding_kernel<12><<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(table), int(k / 256), tokens, out);
+  else
+    embedding_kernel<14><<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(table), int(k / 256), tokens, out);
+  return cudaGetLastError();
+}
+
+cudaError_t gather_tokens_launch(const infdev_query* queries, int queryCount, const int32_t* requestData, uint32_t capacity,
+                                 const int32_t* proposals, uint32_t mode, int32_t* rowTokens, cudaStream_t stream) {
+  if (queryCount <= 0)
+    return cudaSuccess;
+  gather_tokens_kernel<<<queryCount, 128, 0, stream>>>(queries, queryCount, requestData, capacity, proposals, mode, rowTokens);
+  return cudaGetLastError();
+}
+
+cudaError_t rms_norm_launch(const float* x, const float* w, const infdev_query* queries, int64_t rows, int64_t dim, float* y, cudaStream_t stream) {
+  if (rows <= 0)
+    return cudaSuccess;
+  if (queries)
+    rms_norm_kernel<true><<<unsigned(rows), 256, 0, stream>>>(x, w, queries, int(dim), y);
+  else
+    rms_norm_kernel<false><<<unsigned(rows), 256, 0, stream>>>(x, w, nullptr, int(dim), y);
+  return cudaGetLastError();
+}
+
+}  // namespace infdev
