@@ -1,0 +1,202 @@
+// Gated delta-rule (GDN) layer kernels.
+//
+// gdn_ba_kernel     <- gdn_ba_prepare_4096x32 (native_ops.metal:89-113)
+// gdn_conv_kernel   <- gdn_causal_conv_silu   (fused_kernels.metal:202-232)
+// delta_rule_kernel <- delta_rule_decode (delta_rule.metal:256-363) for every query length, fused with
+//                      gated_rms_norm_128 (fused_kernels.metal:234-254).
+//
+// The recurrence keeps the whole 128x128 fp32 state of one (sequence, value head) in the registers of one
+// CTA (256 threads x 64 values): it is read from HBM once, updated for every token of the query, and
+// written once (or once per token for speculative queries, whose every row must stay selectable). The
+// reference makes two passes over the state in device memory per token (delta_rule.metal:320-333, 351-360).
+#include "common.cuh"
+#include "ops.h"
+
+namespace infdev {
+namespace {
+
+constexpr int kChannels = 8192, kHeadDim = 128, kValueHeads = 32, kKeyHeads = 16;
+constexpr uint32_t kUnbound = 0xffffffffu;
+
+__device__ __forceinline__ const infdev_query& query_of_row(const infdev_query* queries, uint32_t row) {
+  while (row >= queries->start + queries->count)
+    ++queries;
+  return *queries;
+}
+
+// grid (32 heads, rows), 64 threads: warp 0 -> beta, warp 1 -> g.
+__global__ void __launch_bounds__(64) gdn_ba_kernel(const float* x, const float* wBeta, const float* wAlpha, const float* A, const float* dt,
+                                                    float* beta, float* g) {
+  const int head = blockIdx.x, row = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float* w = (warp ? wAlpha : wBeta) + size_t(head) * 4096;
+  const float* src = x + size_t(row) * 4096;
+  float sum = 0.f;
+  for (int k = lane * 4; k < 4096; k += 128) {
+    const float4 a = *reinterpret_cast<const float4*>(src + k), b = *reinterpret_cast<const float4*>(w + k);
+    sum += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+  }
+  sum = warp_sum(sum);
+  if (lane == 0) {
+    if (warp == 0)
+      beta[row * kValueHeads + head] = 1.0f / (1.0f + expf(-sum));
+    else
+      g[row * kValueHeads + head] = A[head] * logf(1.0f + expf(sum + dt[head]));
+  }
+}
+
+// One thread per (row, channel). State layout: conv taps fp32 [8192][4] at record + stateOffset.
+__global__ void __launch_bounds__(256) gdn_conv_kernel(const float* mixed, const float* w, const infdev_query* queries, int rows,
+                                                       uint64_t stateOffset, uint64_t stateBytes, float* q, float* k, float* v) {
+  const int64_t tid = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t row = tid / kChannels, c = tid % kChannels;
+  if (row >= rows)
+    return;
+  const infdev_query& info = query_of_row(queries, uint32_t(row));
+  const int64_t p = row - info.start;
+  const bool speculative = info.state != kUnbound;
+  const float* prev = reinterpret_cast<const float*>(info.previous + stateOffset);
+  float context[4], acc = 0.f;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int64_t position = p - 3 + r;
+    context[r] = position >= 0 ? mixed[(info.start + position) * kChannels + c] : info.previous ? prev[c * 4 + position + 4] : 0.f;
+    acc = fmaf(context[r], w[c * 4 + r], acc);
+  }
+  const float value = silu_f(acc);
+  if (c < 2048)
+    q[row * 2048 + c] = value;
+  else if (c < 4096)
+    k[row * 2048 + c - 2048] = value;
+  else
+    v[row * 4096 + c - 4096] = value;
+  if (speculative || p + 1 == info.count) {
+    float* state = reinterpret_cast<float*>(info.next + stateOffset + (speculative ? uint64_t(p) * stateBytes : 0)) + c * 4;
+    *reinterpret_cast<float4*>(state) = make_float4(context[0], context[1], context[2], context[3]);
+  }
+}
+
+// grid (32 value heads, queries), 256 threads. Thread (part = tid/32, lane) owns S[k][4*lane .. 4*lane+3]
+// for k = part + 8*i, i < 16.
+__global__ void __launch_bounds__(256) delta_rule_kernel(const float* q, const float* k, const float* v, const float* g, const float* beta,
+                                                         const float* z, const float* normWeight, const infdev_query* queries,
+                                                         uint64_t stateOffset, uint64_t stateBytes, float* out) {
+  const infdev_query info = queries[blockIdx.y];
+  const int head = blockIdx.x, keyHead = head % kKeyHeads, tid = threadIdx.x, part = tid >> 5, lane = tid & 31;
+  const bool speculative = info.state != kUnbound;
+  __shared__ float qs[kHeadDim], ks[kHeadDim], red[12], partialPred[8][kHeadDim], partialQ[8][kHeadDim], delta[kHeadDim], scalars[4];
+
+  float4 S[16];
+  if (info.previous) {
+    const float4* src = reinterpret_cast<const float4*>(info.previous + stateOffset) + size_t(head) * kHeadDim * 32;
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      S[i] = src[(part + 8 * i) * 32 + lane];
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      S[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+
+  for (uint32_t t = 0; t < info.count; ++t) {
+    const size_t row = info.start + t;
+    // L2-normalise q (scaled by 1/sqrt(128)) and k; q.k of the normalised vectors (delta_rule.metal:281-311).
+    float qv = 0.f, kv = 0.f;
+    if (tid < kHeadDim) {
+      qv = q[(row * kKeyHeads + keyHead) * kHeadDim + tid];
+      kv = k[(row * kKeyHeads + keyHead) * kHeadDim + tid];
+      const float a = warp_sum(qv * qv), b = warp_sum(kv * kv), c = warp_sum(qv * kv);
+      if (lane == 0) {
+        red[part] = a;
+        red[4 + part] = b;
+        red[8 + part] = c;
+      }
+    }
+    __syncthreads();
+    if (tid < kHeadDim) {
+      const float qn = rsqrtf(red[0] + red[1] + red[2] + red[3] + 1.0e-6f) * 0.08838834764831845f;
+      const float kn = rsqrtf(red[4] + red[5] + red[6] + red[7] + 1.0e-6f);
+      qs[tid] = qv * qn;
+      ks[tid] = kv * kn;
+      if (tid == 0) {
+        scalars[0] = (red[8] + red[9] + red[10] + red[11]) * qn * kn;
+        scalars[1] = expf(g[row * kValueHeads + head]);
+        scalars[2] = beta[row * kValueHeads + head];
+      }
+    }
+    __syncthreads();
+    const float decay = scalars[1];
+    float4 pred = make_float4(0.f, 0.f, 0.f, 0.f), qstate = pred;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float kk = ks[part + 8 * i], qq = qs[part + 8 * i];
+      S[i].x *= decay, S[i].y *= decay, S[i].z *= decay, S[i].w *= decay;
+      pred.x = fmaf(S[i].x, kk, pred.x), pred.y = fmaf(S[i].y, kk, pred.y), pred.z = fmaf(S[i].z, kk, pred.z), pred.w = fmaf(S[i].w, kk, pred.w);
+      qstate.x = fmaf(S[i].x, qq, qstate.x), qstate.y = fmaf(S[i].y, qq, qstate.y), qstate.z = fmaf(S[i].z, qq, qstate.z),
+      qstate.w = fmaf(S[i].w, qq, qstate.w);
+    }
+    *reinterpret_cast<float4*>(&partialPred[part][lane * 4]) = pred;
+    *reinterpret_cast<float4*>(&partialQ[part][lane * 4]) = qstate;
+    __syncthreads();
+    float o = 0.f;
+    if (tid < kHeadDim) {
+      float p = 0.f, s = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        p += partialPred[w][tid];
+        s += partialQ[w][tid];
+      }
+      const float d = (v[(row * kValueHeads + head) * kHeadDim + tid] - p) * scalars[2];
+      delta[tid] = d;
+      o = s + d * scalars[0];
+      const float ss = warp_sum(o * o);
+      if (lane == 0)
+        red[part] = ss;
+    }
+    __syncthreads();
+    if (tid < kHeadDim) {
+      const size_t at = (row * kValueHeads + head) * kHeadDim + tid;
+      if (z) {  // gated_rms_norm_128
+        const float scale = rsqrtf((red[0] + red[1] + red[2] + red[3]) / float(kHeadDim) + 1.0e-6f);
+        out[at] = o * scale * normWeight[tid] * silu_f(z[at]);
+      } else
+        out[at] = o;
+    }
+    const float4 d4 = *reinterpret_cast<const float4*>(&delta[lane * 4]);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float kk = ks[part + 8 * i];
+      S[i].x = fmaf(kk, d4.x, S[i].x), S[i].y = fmaf(kk, d4.y, S[i].y), S[i].z = fmaf(kk, d4.z, S[i].z), S[i].w = fmaf(kk, d4.w, S[i].w);
+    }
+    if (speculative || t + 1 == info.count) {
+      float4* dst = reinterpret_cast<float4*>(info.next + stateOffset + (speculative ? uint64_t(t) * stateBytes : 0)) + size_t(head) * kHeadDim * 32;
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        dst[(part + 8 * i) * 32 + lane] = S[i];
+    }
+    __syncthreads();  // qs/ks/delta/red are rewritten by the next token
+  }
+}
+
+}  // namespace
+
+cudaError_t gdn_prepare_launch(const float* x, const float* mixed, const float* wBeta, const float* wAlpha, const float* A, const float* dt,
+                               const float* convWeight, const infdev_query* queries, int64_t rows, uint64_t stateOffset, uint64_t stateBytes,
+                               float* q, float* k, float* v, float* beta, float* g, cudaStream_t stream) {
+  if (rows <= 0)
+    return cudaSuccess;
+  gdn_ba_kernel<<<dim3(kValueHeads, unsigned(rows)), 64, 0, stream>>>(x, wBeta, wAlpha, A, dt, beta, g);
+  gdn_conv_kernel<<<unsigned(rows * kChannels / 256), 256, 0, stream>>>(mixed, convWeight, queries, int(rows), stateOffset, stateBytes, q, k, v);
+  return cudaGetLastError();
+}
+
+cudaError_t delta_rule_launch(const float* q, const float* k, const float* v, const float* g, const float* beta, const float* z,
+                              const float* normWeight, const infdev_query* queries, int queryCount, uint64_t stateOffset, uint64_t stateBytes,
+                              float* out, cudaStream_t stream) {
+  if (queryCount <= 0)
+    return cudaSuccess;
+  delta_rule_kernel<<<dim3(kValueHeads, unsigned(queryCount)), 256, 0, stream>>>(q, k, v, g, beta, z, normWeight, queries, stateOffset, stateBytes,
+                                                                                  out);
+  return cudaGetLastError();
+}
+
+}  // namespace infdev

@@ -108,10 +108,11 @@ __device__ __forceinline__ void q4k_unit(const uint8_t* pA, const uint8_t* pB, i
       a[1] = hfma2_u32((wB & 0x000f000fu) | k1024, sLB, nLB);
       a[2] = hfma2_u32((vA & 0x000f000fu) | k1024, sLA, nLA);
       a[3] = hfma2_u32((vB & 0x000f000fu) | k1024, sLB, nLB);
-      uint2 b = xhi[i * 32 + lane];
+      const int at = (lane + j) & 31;
+      uint2 b = xhi[i * 32 + at];
       mma_16816(acc0, a, b.x, b.y);
       if (XSPLIT == 2) {
-        b = xlo[i * 32 + lane];
+        b = xlo[i * 32 + at];
         mma_16816(acc0, a, b.x, b.y);
       }
       // high nibbles in place: (1024 + 16 q) * sc/16 - 64 * sc
@@ -119,10 +120,10 @@ __device__ __forceinline__ void q4k_unit(const uint8_t* pA, const uint8_t* pB, i
       a[1] = hfma2_u32((wB & 0x00f000f0u) | k1024, mHB, nHB);
       a[2] = hfma2_u32((vA & 0x00f000f0u) | k1024, mHA, nHA);
       a[3] = hfma2_u32((vB & 0x00f000f0u) | k1024, mHB, nHB);
-      b = xhi[(i + 1) * 32 + lane];
+      b = xhi[(i + 1) * 32 + at];
       mma_16816(acc1, a, b.x, b.y);
       if (XSPLIT == 2) {
-        b = xlo[(i + 1) * 32 + lane];
+        b = xlo[(i + 1) * 32 + at];
         mma_16816(acc1, a, b.x, b.y);
       }
     }
@@ -270,52 +271,57 @@ template <class Q, int NMAT, int XSPLIT> __global__ void __launch_bounds__(kThre
     const int chunkBlocks = min(kChunkBlocks, blocksPerRow - chunk * kChunkBlocks);
     const int groups = (chunkBlocks + kStageBlocks - 1) / kStageBlocks;
     const int k0 = chunk * kChunkBlocks * 256;
-    // Stage the activations of this K chunk in B-fragment order (hi / lo fp16 split).
-    for (int idx = tid; idx < chunkBlocks * 16 * 32; idx += kConsumerWarps * kWarp) {
-      const int l = idx & 31, i = (idx >> 5) & 15, sb = idx >> 9, row = l >> 2, tt = l & 3;
-      int k;
-      if (Q::kMinTerm) {
-        const int cs = i >> 3, j = (i >> 1) & 3, h = i & 1, c = tt + 4 * cs;
-        k = 256 * sb + 64 * (c >> 1) + 32 * h + 16 * (c & 1) + 4 * j;
-      } else {
-        k = 256 * sb + 16 * i + 4 * tt;
-      }
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (row < p.m)
-        v = *reinterpret_cast<const float4*>(p.x + size_t(row) * p.ldx + k0 + k);
-      uint2 hi;
-      float4 r;
-      if (Q::kMinTerm) {  // A pairs bytes (0,2) and (1,3) of a quant word
-        hi.x = pack_half2(v.x, v.z);
-        hi.y = pack_half2(v.y, v.w);
-        const float2 f0 = __half22float2(*reinterpret_cast<__half2*>(&hi.x)), f1 = __half22float2(*reinterpret_cast<__half2*>(&hi.y));
-        r = make_float4(v.x - f0.x, v.z - f0.y, v.y - f1.x, v.w - f1.y);
-      } else {
-        hi.x = pack_half2(v.x, v.y);
-        hi.y = pack_half2(v.z, v.w);
-        const float2 f0 = __half22float2(*reinterpret_cast<__half2*>(&hi.x)), f1 = __half22float2(*reinterpret_cast<__half2*>(&hi.y));
-        r = make_float4(v.x - f0.x, v.y - f0.y, v.z - f1.x, v.w - f1.y);
-      }
-      fragHi[idx] = hi;
-      if (XSPLIT == 2)
-        fragLo[idx] = make_uint2(pack_half2(r.x, r.y), pack_half2(r.z, r.w));
-    }
-    if (Q::kMinTerm) {
-      for (int idx = tid; idx < chunkBlocks * 32; idx += kConsumerWarps * kWarp) {
-        const int l = idx & 31, sb = idx >> 5, row = l >> 2, tt = l & 3;
-        float s0 = 0.f, s1 = 0.f;
-        if (row < p.m) {
-          const float* src = p.x + size_t(row) * p.ldx + k0 + 256 * sb + 64 * tt;
-          for (int e = 0; e < 32; ++e) {
-            s0 += src[e];
-            s1 += src[32 + e];
+    // Stage the activations of this K chunk in B-fragment order (hi / lo fp16 split). A warp takes a
+    // 64-value span of all 8 rows at a time: lane (row = lane/4, jj = lane%4) loads four float4 at
+    // 16*e + 4*jj, so each row contributes whole 64-byte pieces. Q4_K fragments are stored rotated by jj
+    // inside their 32-entry line, which makes both these writes and the MMA-time reads conflict-free.
+    if (!(p.debug & 1))
+      for (int span = warp; span < chunkBlocks * 4; span += kConsumerWarps) {
+        const int row = lane >> 2, jj = lane & 3, sb = span >> 2, tq = span & 3;
+        float4 v[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          v[e] = row < p.m ? *reinterpret_cast<const float4*>(p.x + size_t(row) * p.ldx + k0 + 64 * span + 16 * e + 4 * jj)
+                           : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          uint2 hi;
+          float4 r;
+          int slot;
+          if (Q::kMinTerm) {  // A pairs bytes (0,2) and (1,3) of a quant word
+            const int c = 2 * tq + (e & 1), i = ((c >> 2) * 4 + jj) * 2 + (e >> 1);
+            slot = (sb * 16 + i) * 32 + ((row * 4 + (c & 3) + jj) & 31);
+            hi.x = pack_half2(v[e].x, v[e].z);
+            hi.y = pack_half2(v[e].y, v[e].w);
+            const float2 f0 = __half22float2(*reinterpret_cast<__half2*>(&hi.x)), f1 = __half22float2(*reinterpret_cast<__half2*>(&hi.y));
+            r = make_float4(v[e].x - f0.x, v[e].z - f0.y, v[e].y - f1.x, v[e].w - f1.y);
+          } else {
+            slot = (sb * 16 + tq * 4 + e) * 32 + lane;
+            hi.x = pack_half2(v[e].x, v[e].y);
+            hi.y = pack_half2(v[e].z, v[e].w);
+            const float2 f0 = __half22float2(*reinterpret_cast<__half2*>(&hi.x)), f1 = __half22float2(*reinterpret_cast<__half2*>(&hi.y));
+            r = make_float4(v[e].x - f0.x, v[e].y - f0.y, v[e].z - f1.x, v[e].w - f1.y);
+          }
+          fragHi[slot] = hi;
+          if (XSPLIT == 2)
+            fragLo[slot] = make_uint2(pack_half2(r.x, r.y), pack_half2(r.z, r.w));
+        }
+        if (Q::kMinTerm) {  // sums of the two 32-value sub-blocks of this span, for the min term
+          float s[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            s[e] = (v[e].x + v[e].y) + (v[e].z + v[e].w);
+            s[e] += __shfl_xor_sync(0xffffffffu, s[e], 1);
+            s[e] += __shfl_xor_sync(0xffffffffu, s[e], 2);
+          }
+          const float s0 = s[0] + s[1], s1 = s[2] + s[3];
+          if (jj == 0) {
+            const uint32_t hi = pack_half2(s0, s1);
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+            fragSum[sb * 32 + row * 4 + tq] = make_uint2(hi, pack_half2(s0 - f.x, s1 - f.y));
           }
         }
-        const uint32_t hi = pack_half2(s0, s1);
-        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hi));
-        fragSum[idx] = make_uint2(hi, pack_half2(s0 - f.x, s1 - f.y));
       }
-    }
     named_barrier(1, kConsumerWarps * kWarp);
 
     for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++tileCounter) {
@@ -335,7 +341,7 @@ template <class Q, int NMAT, int XSPLIT> __global__ void __launch_bounds__(kThre
             continue;
           }
           const int count = min(kStageBlocks, chunkBlocks - grp * kStageBlocks);
-          if (warp < count) {
+          if (warp < count && !(p.debug & 2)) {
             const uint8_t* base = ring + size_t(slot) * Q::kStageBytes + warp * Q::kBlockBytes;
             const int sb = grp * kStageBlocks + warp;
             if (Q::kMinTerm)

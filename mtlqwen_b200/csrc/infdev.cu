@@ -12,7 +12,7 @@
 #include "ops.h"
 
 struct infdev_ctx {
-  int device = 0, sms = 0, xsplit = 2;
+  int device = 0, sms = 0, xsplit = 2, debug = 0;
   cudaStream_t stream = nullptr;
   cudaEvent_t done = nullptr;
   int* status = nullptr;      // device status word written by kernels that abort a bounded wait
@@ -72,6 +72,8 @@ infdev_ctx* infdev_create(int device, char* error) {
   ctx->sms = prop.multiProcessorCount;
   if (const char* env = std::getenv("INFENG_XSPLIT"))
     ctx->xsplit = std::atoi(env) == 1 ? 1 : 2;
+  if (const char* env = std::getenv("INFENG_GEMV_DEBUG"))
+    ctx->debug = std::atoi(env);
   if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess ||
       (e = cudaEventCreateWithFlags(&ctx->done, cudaEventDisableTiming)) != cudaSuccess ||
       (e = cudaMalloc(reinterpret_cast<void**>(&ctx->status), sizeof(int))) != cudaSuccess ||
@@ -302,6 +304,7 @@ static int linear_common(infdev_ctx* ctx, int type, bool pair, int count, const 
   p.ldx = int(k);
   p.k = int(k);
   p.status = ctx->status;
+  p.debug = ctx->debug;
   // More than 8 activation rows: 8-row slices re-use the weights out of L2.
   for (int64_t row = 0; row < m; row += 8) {
     p.x = x + row * k;

@@ -20,6 +20,7 @@ struct GemvParams {
   const float* x;  // [m][ldx] fp32, rows 16-byte aligned
   int ldx, m, k;
   int* status;
+  int debug;  // probe switches: 1 skips activation staging, 2 skips the MMA units
 };
 
 cudaError_t gemv_launch(int type, bool pair, int xsplit, const GemvParams& p, int sms, cudaStream_t stream);
