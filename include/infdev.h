@@ -34,8 +34,7 @@ enum { INFDEV_F32 = 0, INFDEV_F16 = 1, INFDEV_Q4_K = 12, INFDEV_Q6_K = 14 };
 
 /* Per-query ragged metadata, the CUDA form of GpuQuery (backend/metal/kernel/batch.hpp:11-16).
  * previous/next are device addresses of the slot's state record (0 = fresh sequence); state is the first
- * candidate-state row of a speculative query or 0xffffffff. `seed`/`stream` are additions: the Philox key
- * of the slot and the absolute index of the first token this query samples. */
+ * candidate-state row of a speculative query or 0xffffffff. `seed` is an addition: the Philox key of the slot. */
 typedef struct infdev_query {
   uint64_t previous, next;
   uint32_t start, count, position, slot, state, logit, samples;
@@ -109,6 +108,56 @@ int infdev_embedding(infdev_ctx* ctx, int type, const void* table, int64_t k, co
 int infdev_rms_norm(infdev_ctx* ctx, const float* x, const float* w, int64_t rows, int64_t dim, float* y);
 /* rms_norm_gather (native_ops.metal:12-15): row i of y normalises the i-th sampled row of the pass. */
 int infdev_rms_norm_gather(infdev_ctx* ctx, const float* x, const float* w, const infdev_query* queries, int queryCount, int64_t count, float* y);
+
+
+/* ---- gated delta rule (GDN) ---- */
+/* gdn_ba_prepare_4096x32 (native_ops.metal:89-113) and gdn_causal_conv_silu (fused_kernels.metal:202-232) in
+ * one call. x: normalised hidden [rows,4096]; mixed: qkv projection [rows,8192]; wBeta/wAlpha f32 [32,4096];
+ * ssmA, ssmDt [32]; convWeight f32 [8192,4]. stateOffset: byte offset of this layer's conv taps inside a
+ * state record; stateBytes: size of one record (stride between candidate rows). Outputs q,k [rows,16,128]
+ * (the reference stores each twice for 32 heads; consumers use head % 16), v [rows,32,128], beta, g [rows,32]. */
+int infdev_gdn_prepare(infdev_ctx* ctx, const float* x, const float* mixed, const float* wBeta, const float* wAlpha, const float* ssmA,
+                       const float* ssmDt, const float* convWeight, const infdev_query* queries, int queryCount, int64_t rows,
+                       uint64_t stateOffset, uint64_t stateBytes, float* q, float* k, float* v, float* beta, float* g);
+/* delta_rule_decode / delta_rule_prefill (delta_rule.metal:73-363) for every query length, followed by
+ * gated_rms_norm_128 (fused_kernels.metal:234-254) when z is non-null (z [rows,4096], normWeight [128]).
+ * stateOffset here addresses the layer's recurrent state S fp32 [32][128][128] inside a record. */
+int infdev_delta_rule(infdev_ctx* ctx, const float* q, const float* k, const float* v, const float* g, const float* beta, const float* z,
+                      const float* normWeight, const infdev_query* queries, int queryCount, uint64_t stateOffset, uint64_t stateBytes, float* out);
+
+/* ---- attention ---- */
+/* init_rope (native_ops.metal:115-120): cos/sin table fp32 [positions,32,2] for theta = 1e7, evaluated on
+ * the host in double precision and uploaded. */
+int infdev_rope_table(infdev_ctx* ctx, int64_t positions, float* table);
+/* attention_prepare (attention.metal:14-50) plus the K/V cache append of attention_scan (:126-133).
+ * qg [rows,16,512] (q | gate per head), k,v [rows,4,256]; q out [rows,16,256]. The cache of one layer is
+ * [physical block][4][blockTokens][256] fp16; table[slot*tableStride + logical block] = physical block
+ * (the role of SparseKV::map, device.cpp:178-198). blockTokens must be a multiple of 16. */
+int infdev_attention_prepare(infdev_ctx* ctx, const float* qg, const float* k, const float* v, const float* qNorm, const float* kNorm,
+                             const float* rope, const infdev_query* queries, int queryCount, int64_t rows, const int32_t* table,
+                             int32_t tableStride, int32_t blockTokens, float* q, void* cacheK, void* cacheV);
+/* attention_scan + attention_reduce (attention.metal:103-216): causal GQA over the cache, times
+ * sigmoid(gate). partials: scratch of infdev_attention_scratch_bytes(rows, maxSplits) bytes. */
+int infdev_attention(infdev_ctx* ctx, const float* q, const float* qg, const void* cacheK, const void* cacheV, const infdev_query* queries,
+                     int queryCount, int64_t rows, const int32_t* table, int32_t tableStride, int32_t blockTokens, uint32_t maxSplits,
+                     float* partials, float* out);
+size_t infdev_attention_scratch_bytes(int64_t rows, uint32_t maxSplits);
+
+/* ---- sampling, packing, verification ---- */
+/* sample_logits (native_ops.metal:122-224): logits fp32 [count,vocab]; mode 0 target, 1 MTP drafting. */
+int infdev_sample(infdev_ctx* ctx, const float* logits, int64_t vocab, infdev_query* queries, int queryCount, int64_t count, uint32_t mode,
+                  int32_t* tokens);
+/* The packing loop of forward() (forward.cpp:171-191) on the device. in[i].samples carries the slot's
+ * requested-token count. meta[4] receives rows, logit rows, flags (1 sequential, 2 prefill), packed count. */
+int infdev_pack_queries(infdev_ctx* ctx, const infdev_query* in, int count, int drafting, uint32_t draftWidth, const uint64_t* statePrevious,
+                        const uint64_t* stateNext, uint64_t candidateBase, uint64_t stateBytes, infdev_query* out, uint32_t* meta);
+/* The acceptance loop of Engine::schedule (engine.cpp:205-216) on the device. stops: all slots' stop tokens,
+ * stopOffsets[slot..slot+1] their range. accepted[i] per query. */
+int infdev_verify_drafts(infdev_ctx* ctx, const infdev_query* queries, int count, const int32_t* sampled, const int32_t* proposed,
+                         uint32_t draftWidth, const int32_t* stops, const uint32_t* stopOffsets, uint32_t* accepted);
+/* Copies each speculative query's accepted candidate state row to the slot's next state (engine.cpp:217-218). */
+int infdev_commit_states(infdev_ctx* ctx, const infdev_query* queries, int count, const uint32_t* accepted, const uint64_t* stateNext,
+                         uint64_t candidateBase, uint64_t stateBytes);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,230 @@
+// Gated GQA attention over the paged fp16 K/V pool.
+//
+// attention_prepare_kernel <- attention_prepare (attention.metal:14-50) + the cache append that the
+//                             reference does inside attention_scan (:126-133)
+// attention_scan_kernel    <- attention_scan   (attention.metal:103-183)
+// attention_reduce_kernel  <- attention_reduce (attention.metal:185-216)
+//
+// K/V pool of one layer: [physical block][4 kv heads][blockTokens][256] fp16, so the 16 tokens of a tile of
+// one kv head are 8 KB contiguous. A per-slot block table maps logical to physical blocks (the reference
+// reaches the same effect through Metal sparse-buffer page mappings, device.cpp:147-198).
+//
+// Split-K: the reference uses max(1, 8/rows) splits (forward.cpp:92), which leaves a 148-SM part idle on a
+// long single-row context and makes the reduction order depend on the batch. Here the number of splits of a
+// row depends only on how many tokens that row attends to, so a sequence gets the same arithmetic whether
+// it runs alone or batched. One CTA serves the four query heads that share a kv head, so K and V are read
+// once per group.
+#include "common.cuh"
+#include "ops.h"
+
+namespace infdev {
+namespace {
+
+constexpr int kQHeads = 16, kKvHeads = 4, kDim = 256, kGroup = kQHeads / kKvHeads, kTile = 16;
+constexpr int kPartialStride = kDim + 4;  // 260 floats keeps every record 16-byte aligned for the float4 stores
+
+__device__ __forceinline__ const infdev_query& query_of_row(const infdev_query* queries, uint32_t row) {
+  while (row >= queries->start + queries->count)
+    ++queries;
+  return *queries;
+}
+
+// Splits of a row that attends to `attended` tokens: 256-token pieces, at most maxSplits, each a multiple of
+// the 16-token tile.
+__device__ __forceinline__ void split_range(uint32_t attended, uint32_t maxSplits, uint32_t split, uint32_t& begin, uint32_t& end, uint32_t& count) {
+  count = min(maxSplits, (attended + 255u) / 256u);
+  const uint32_t per = (((attended + count - 1) / count) + kTile - 1) / kTile * kTile;
+  begin = min(attended, split * per);
+  end = min(attended, begin + per);
+}
+
+// grid (rows * 20), 256 threads: heads 0..15 are queries, 16..19 keys (which also store the value head).
+__global__ void __launch_bounds__(256) attention_prepare_kernel(const float* qg, const float* rawK, const float* rawV, const float* qNorm,
+                                                                const float* kNorm, const float* rope, const infdev_query* queries,
+                                                                const int32_t* table, int tableStride, int blockTokens, float* q, __half* cacheK,
+                                                                __half* cacheV) {
+  const int row = blockIdx.x / 20, head = blockIdx.x % 20, lane = threadIdx.x;
+  const bool query = head < kQHeads;
+  const int local = query ? head : head - kQHeads;
+  const float* source = query ? qg + (size_t(row) * kQHeads + local) * kDim * 2 : rawK + (size_t(row) * kKvHeads + local) * kDim;
+  const float* weight = query ? qNorm : kNorm;
+  const float value = source[lane];
+  __shared__ float partial[8], scale;
+  const float sum = warp_sum(value * value);
+  if ((lane & 31) == 0)
+    partial[lane >> 5] = sum;
+  __syncthreads();
+  if (lane == 0) {
+    float total = 0.f;
+    for (int i = 0; i < 8; ++i)
+      total += partial[i];
+    scale = rsqrtf(total / float(kDim) + 1.0e-6f);
+  }
+  __syncthreads();
+  const infdev_query& info = query_of_row(queries, row);
+  const uint32_t position = info.position + row - info.start;
+  float result = value * scale * weight[lane];
+  if (lane < 64) {
+    const int other = lane < 32 ? lane + 32 : lane - 32, pair = lane & 31;
+    const float paired = source[other] * scale * weight[other];
+    const float2 cs = *reinterpret_cast<const float2*>(rope + (size_t(position) * 32 + pair) * 2);
+    result = result * cs.x + (lane < 32 ? -paired : paired) * cs.y;
+  }
+  if (query) {
+    q[(size_t(row) * kQHeads + local) * kDim + lane] = result;
+  } else {
+    const size_t block = table[size_t(info.slot) * tableStride + position / blockTokens];
+    const size_t at = ((block * kKvHeads + local) * blockTokens + position % blockTokens) * kDim + lane;
+    cacheK[at] = __float2half_rn(result);
+    cacheV[at] = __float2half_rn(rawV[(size_t(row) * kKvHeads + local) * kDim + lane]);
+  }
+}
+
+// grid (maxSplits, 4 kv heads, rows), 128 threads. Warp w scores tokens 4w..4w+3 of each 16-token tile, then
+// accumulates the values for query head w of the group.
+__global__ void __launch_bounds__(128) attention_scan_kernel(const float* q, const __half* cacheK, const __half* cacheV,
+                                                             const infdev_query* queries, const int32_t* table, int tableStride, int blockTokens,
+                                                             uint32_t maxSplits, float* partials) {
+  const uint32_t split = blockIdx.x, kvHead = blockIdx.y, row = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const infdev_query& info = query_of_row(queries, row);
+  const uint32_t attended = info.position + (row - info.start) + 1;
+  uint32_t begin, end, count;
+  split_range(attended, maxSplits, split, begin, end, count);
+  if (split >= count)
+    return;
+  __shared__ float scores[kGroup][kTile];
+  // q of the four heads, the 8 dims of this lane: dims lane*8 .. lane*8+7
+  float qv[kGroup][8];
+#pragma unroll
+  for (int h = 0; h < kGroup; ++h) {
+    const float4* src = reinterpret_cast<const float4*>(q + (size_t(row) * kQHeads + kvHead * kGroup + h) * kDim + lane * 8);
+    const float4 a = src[0], b = src[1];
+    qv[h][0] = a.x, qv[h][1] = a.y, qv[h][2] = a.z, qv[h][3] = a.w, qv[h][4] = b.x, qv[h][5] = b.y, qv[h][6] = b.z, qv[h][7] = b.w;
+  }
+  float runningMax = -1.0e30f, runningNorm = 0.f, numerator[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const int32_t* slotTable = table + size_t(info.slot) * tableStride;
+  for (uint32_t tile = begin; tile < end; tile += kTile) {
+    const size_t block = slotTable[tile / blockTokens];
+    const size_t base = ((block * kKvHeads + kvHead) * blockTokens + tile % blockTokens) * kDim;
+    // scores of 4 tokens x 4 heads per warp
+    float s[4][kGroup];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(cacheK + base + (warp * 4 + i) * kDim + lane * 8);
+      const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+      float kf[8];
+#pragma unroll
+      for (int d = 0; d < 4; ++d) {
+        const float2 f = __half22float2(h2[d]);
+        kf[2 * d] = f.x, kf[2 * d + 1] = f.y;
+      }
+#pragma unroll
+      for (int h = 0; h < kGroup; ++h) {
+        float acc = 0.f;
+#pragma unroll
+        for (int d = 0; d < 8; ++d)
+          acc = fmaf(qv[h][d], kf[d], acc);
+        s[i][h] = acc;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int h = 0; h < kGroup; ++h)
+        s[i][h] = warp_sum(s[i][h]);
+    if (lane < 16) {
+      const int i = lane >> 2, h = lane & 3;
+      float value = 0.f;
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < kGroup; ++b)
+          if (a == i && b == h)
+            value = s[a][b];
+      const uint32_t token = tile + warp * 4 + i;
+      scores[h][warp * 4 + i] = token < end ? value * (1.0f / 16.0f) : -INFINITY;
+    }
+    __syncthreads();
+    // online softmax for head `warp`; lane owns dims lane*8..+7
+    float tileMax = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kTile; ++i)
+      tileMax = fmaxf(tileMax, scores[warp][i]);
+    const float nextMax = fmaxf(runningMax, tileMax), rescale = expf(runningMax - nextMax);
+    runningNorm *= rescale;
+#pragma unroll
+    for (int d = 0; d < 8; ++d)
+      numerator[d] *= rescale;
+    const uint32_t live = min(uint32_t(kTile), end - tile);
+    for (uint32_t i = 0; i < live; ++i) {
+      const float weight = expf(scores[warp][i] - nextMax);
+      runningNorm += weight;
+      const uint4 raw = *reinterpret_cast<const uint4*>(cacheV + base + i * kDim + lane * 8);
+      const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+      for (int d = 0; d < 4; ++d) {
+        const float2 f = __half22float2(h2[d]);
+        numerator[2 * d] = fmaf(weight, f.x, numerator[2 * d]);
+        numerator[2 * d + 1] = fmaf(weight, f.y, numerator[2 * d + 1]);
+      }
+    }
+    runningMax = nextMax;
+    __syncthreads();
+  }
+  float* dst = partials + ((size_t(row) * kQHeads + kvHead * kGroup + warp) * maxSplits + split) * kPartialStride;
+  *reinterpret_cast<float4*>(dst + lane * 8) = make_float4(numerator[0], numerator[1], numerator[2], numerator[3]);
+  *reinterpret_cast<float4*>(dst + lane * 8 + 4) = make_float4(numerator[4], numerator[5], numerator[6], numerator[7]);
+  if (lane == 0) {
+    dst[kDim] = runningMax;
+    dst[kDim + 1] = runningNorm;
+  }
+}
+
+// grid (rows * 16), 256 threads: merge the splits, normalise, multiply by sigmoid(gate).
+__global__ void __launch_bounds__(256) attention_reduce_kernel(const float* partials, const float* qg, const infdev_query* queries,
+                                                               uint32_t maxSplits, float* out) {
+  const uint32_t headRow = blockIdx.x, row = headRow / kQHeads, dim = threadIdx.x;
+  const infdev_query& info = query_of_row(queries, row);
+  const uint32_t attended = info.position + (row - info.start) + 1;
+  uint32_t begin, end, count;
+  split_range(attended, maxSplits, 0, begin, end, count);
+  const float* src = partials + size_t(headRow) * maxSplits * kPartialStride;
+  float maximum = -1.0e30f;
+  for (uint32_t s = 0; s < count; ++s)
+    maximum = fmaxf(maximum, src[s * kPartialStride + kDim]);
+  float norm = 0.f, numerator = 0.f;
+  for (uint32_t s = 0; s < count; ++s) {
+    const float w = expf(src[s * kPartialStride + kDim] - maximum);
+    norm += src[s * kPartialStride + kDim + 1] * w;
+    numerator += src[s * kPartialStride + dim] * w;
+  }
+  const float gate = qg[size_t(headRow) * kDim * 2 + kDim + dim];
+  out[size_t(headRow) * kDim + dim] = (numerator / norm) / (1.0f + expf(-gate));
+}
+
+}  // namespace
+
+cudaError_t attention_prepare_launch(const float* qg, const float* rawK, const float* rawV, const float* qNorm, const float* kNorm, const float* rope,
+                                     const infdev_query* queries, const int32_t* table, int tableStride, int blockTokens, int64_t rows, float* q,
+                                     void* cacheK, void* cacheV, cudaStream_t stream) {
+  if (rows <= 0)
+    return cudaSuccess;
+  attention_prepare_kernel<<<unsigned(rows * 20), 256, 0, stream>>>(qg, rawK, rawV, qNorm, kNorm, rope, queries, table, tableStride, blockTokens, q,
+                                                                     static_cast<__half*>(cacheK), static_cast<__half*>(cacheV));
+  return cudaGetLastError();
+}
+
+cudaError_t attention_launch(const float* q, const float* qg, const void* cacheK, const void* cacheV, const infdev_query* queries,
+                             const int32_t* table, int tableStride, int blockTokens, int64_t rows, uint32_t maxSplits, float* partials, float* out,
+                             cudaStream_t stream) {
+  if (rows <= 0)
+    return cudaSuccess;
+  attention_scan_kernel<<<dim3(maxSplits, kKvHeads, unsigned(rows)), 128, 0, stream>>>(q, static_cast<const __half*>(cacheK),
+                                                                                       static_cast<const __half*>(cacheV), queries, table,
+                                                                                       tableStride, blockTokens, maxSplits, partials);
+  attention_reduce_kernel<<<unsigned(rows * kQHeads), 256, 0, stream>>>(partials, qg, queries, maxSplits, out);
+  return cudaGetLastError();
+}
+
+}  // namespace infdev

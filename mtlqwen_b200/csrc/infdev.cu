@@ -1,6 +1,7 @@
 // C-ABI device layer: context, memory, stream, and the typed kernel entry points declared in
 // include/infdev.h. This file holds no math; it validates arguments and launches.
 #include <chrono>
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -8,6 +9,7 @@
 #include <string>
 #include <thread>
 #include <unordered_map>
+#include <vector>
 #include "kernels.h"
 #include "ops.h"
 
@@ -359,6 +361,104 @@ int infdev_rms_norm_gather(infdev_ctx* ctx, const float* x, const float* w, cons
   Bind bind(ctx);
   (void)queryCount;
   return check(ctx, infdev::rms_norm_launch(x, w, queries, count, 4096, y, ctx->stream), "rms_norm_gather");
+}
+
+// ---- gated delta rule --------------------------------------------------------------------------
+
+int infdev_gdn_prepare(infdev_ctx* ctx, const float* x, const float* mixed, const float* wBeta, const float* wAlpha, const float* ssmA,
+                       const float* ssmDt, const float* convWeight, const infdev_query* queries, int queryCount, int64_t rows,
+                       uint64_t stateOffset, uint64_t stateBytes, float* q, float* k, float* v, float* beta, float* g) {
+  Bind bind(ctx);
+  (void)queryCount;
+  if (stateOffset % 16 || stateBytes % 16)
+    return fail(ctx, INFDEV_E_ARGUMENT, "gdn_prepare: state offsets must be multiples of 16 bytes");
+  return check(ctx,
+               infdev::gdn_prepare_launch(x, mixed, wBeta, wAlpha, ssmA, ssmDt, convWeight, queries, rows, stateOffset, stateBytes, q, k, v, beta, g,
+                                          ctx->stream),
+               "gdn_prepare");
+}
+
+int infdev_delta_rule(infdev_ctx* ctx, const float* q, const float* k, const float* v, const float* g, const float* beta, const float* z,
+                      const float* normWeight, const infdev_query* queries, int queryCount, uint64_t stateOffset, uint64_t stateBytes, float* out) {
+  Bind bind(ctx);
+  if (stateOffset % 16 || stateBytes % 16)
+    return fail(ctx, INFDEV_E_ARGUMENT, "delta_rule: state offsets must be multiples of 16 bytes");
+  return check(ctx, infdev::delta_rule_launch(q, k, v, g, beta, z, normWeight, queries, queryCount, stateOffset, stateBytes, out, ctx->stream),
+               "delta_rule");
+}
+
+// ---- attention ---------------------------------------------------------------------------------
+
+int infdev_rope_table(infdev_ctx* ctx, int64_t positions, float* table) {
+  Bind bind(ctx);
+  std::vector<float> host(size_t(positions) * 64);
+  for (int64_t p = 0; p < positions; ++p)
+    for (int d = 0; d < 32; ++d) {
+      const double angle = double(p) / std::pow(1.0e7, double(d) / 32.0);
+      host[(p * 32 + d) * 2] = float(std::cos(angle));
+      host[(p * 32 + d) * 2 + 1] = float(std::sin(angle));
+    }
+  int r = check(ctx, cudaMemcpyAsync(table, host.data(), host.size() * 4, cudaMemcpyHostToDevice, ctx->stream), "rope_table");
+  return r ? r : check(ctx, cudaStreamSynchronize(ctx->stream), "rope_table");
+}
+
+int infdev_attention_prepare(infdev_ctx* ctx, const float* qg, const float* k, const float* v, const float* qNorm, const float* kNorm,
+                             const float* rope, const infdev_query* queries, int queryCount, int64_t rows, const int32_t* table,
+                             int32_t tableStride, int32_t blockTokens, float* q, void* cacheK, void* cacheV) {
+  Bind bind(ctx);
+  (void)queryCount;
+  if (blockTokens <= 0 || blockTokens % 16)
+    return fail(ctx, INFDEV_E_ARGUMENT, "attention: blockTokens must be a positive multiple of 16");
+  return check(ctx,
+               infdev::attention_prepare_launch(qg, k, v, qNorm, kNorm, rope, queries, table, tableStride, blockTokens, rows, q, cacheK, cacheV,
+                                                ctx->stream),
+               "attention_prepare");
+}
+
+size_t infdev_attention_scratch_bytes(int64_t rows, uint32_t maxSplits) { return size_t(rows) * 16 * maxSplits * 260 * sizeof(float); }
+
+int infdev_attention(infdev_ctx* ctx, const float* q, const float* qg, const void* cacheK, const void* cacheV, const infdev_query* queries,
+                     int queryCount, int64_t rows, const int32_t* table, int32_t tableStride, int32_t blockTokens, uint32_t maxSplits,
+                     float* partials, float* out) {
+  Bind bind(ctx);
+  (void)queryCount;
+  if (blockTokens <= 0 || blockTokens % 16 || maxSplits < 1 || maxSplits > 64)
+    return fail(ctx, INFDEV_E_ARGUMENT, "attention: blockTokens must be a multiple of 16 and maxSplits in 1..64");
+  return check(ctx,
+               infdev::attention_launch(q, qg, cacheK, cacheV, queries, table, tableStride, blockTokens, rows, maxSplits, partials, out, ctx->stream),
+               "attention");
+}
+
+// ---- sampling, packing, verification -----------------------------------------------------------
+
+int infdev_sample(infdev_ctx* ctx, const float* logits, int64_t vocab, infdev_query* queries, int queryCount, int64_t count, uint32_t mode,
+                  int32_t* tokens) {
+  Bind bind(ctx);
+  (void)queryCount;
+  return check(ctx, infdev::sample_launch(logits, int(vocab), queries, count, mode, tokens, ctx->stream), "sample");
+}
+
+int infdev_pack_queries(infdev_ctx* ctx, const infdev_query* in, int count, int drafting, uint32_t draftWidth, const uint64_t* statePrevious,
+                        const uint64_t* stateNext, uint64_t candidateBase, uint64_t stateBytes, infdev_query* out, uint32_t* meta) {
+  Bind bind(ctx);
+  return check(ctx,
+               infdev::pack_queries_launch(in, count, drafting, draftWidth, statePrevious, stateNext, candidateBase, stateBytes, out, meta, ctx->stream),
+               "pack_queries");
+}
+
+int infdev_verify_drafts(infdev_ctx* ctx, const infdev_query* queries, int count, const int32_t* sampled, const int32_t* proposed,
+                         uint32_t draftWidth, const int32_t* stops, const uint32_t* stopOffsets, uint32_t* accepted) {
+  Bind bind(ctx);
+  if (count > 32)
+    return fail(ctx, INFDEV_E_ARGUMENT, "verify_drafts: at most 32 queries");
+  return check(ctx, infdev::verify_drafts_launch(queries, count, sampled, proposed, draftWidth, stops, stopOffsets, accepted, ctx->stream),
+               "verify_drafts");
+}
+
+int infdev_commit_states(infdev_ctx* ctx, const infdev_query* queries, int count, const uint32_t* accepted, const uint64_t* stateNext,
+                         uint64_t candidateBase, uint64_t stateBytes) {
+  Bind bind(ctx);
+  return check(ctx, infdev::commit_states_launch(queries, count, accepted, stateNext, candidateBase, stateBytes, ctx->stream), "commit_states");
 }
 
 }  // extern "C"

@@ -12,4 +12,26 @@ cudaError_t gather_tokens_launch(const infdev_query* queries, int queryCount, co
                                  const int32_t* proposals, uint32_t mode, int32_t* rowTokens, cudaStream_t stream);
 cudaError_t rms_norm_launch(const float* x, const float* w, const infdev_query* queries, int64_t rows, int64_t dim, float* y, cudaStream_t stream);
 
+cudaError_t gdn_prepare_launch(const float* x, const float* mixed, const float* wBeta, const float* wAlpha, const float* A, const float* dt,
+                               const float* convWeight, const infdev_query* queries, int64_t rows, uint64_t stateOffset, uint64_t stateBytes,
+                               float* q, float* k, float* v, float* beta, float* g, cudaStream_t stream);
+cudaError_t delta_rule_launch(const float* q, const float* k, const float* v, const float* g, const float* beta, const float* z,
+                              const float* normWeight, const infdev_query* queries, int queryCount, uint64_t stateOffset, uint64_t stateBytes,
+                              float* out, cudaStream_t stream);
+cudaError_t attention_prepare_launch(const float* qg, const float* rawK, const float* rawV, const float* qNorm, const float* kNorm, const float* rope,
+                                     const infdev_query* queries, const int32_t* table, int tableStride, int blockTokens, int64_t rows, float* q,
+                                     void* cacheK, void* cacheV, cudaStream_t stream);
+cudaError_t attention_launch(const float* q, const float* qg, const void* cacheK, const void* cacheV, const infdev_query* queries,
+                             const int32_t* table, int tableStride, int blockTokens, int64_t rows, uint32_t maxSplits, float* partials, float* out,
+                             cudaStream_t stream);
+cudaError_t sample_launch(const float* logits, int vocab, infdev_query* queries, int64_t count, uint32_t mode, int32_t* tokens,
+                          cudaStream_t stream);
+cudaError_t pack_queries_launch(const infdev_query* in, int count, int drafting, uint32_t draftWidth, const uint64_t* statePrevious,
+                                const uint64_t* stateNext, uint64_t candidateBase, uint64_t stateBytes, infdev_query* out, uint32_t* meta,
+                                cudaStream_t stream);
+cudaError_t verify_drafts_launch(const infdev_query* queries, int count, const int32_t* sampled, const int32_t* proposed, uint32_t draftWidth,
+                                 const int32_t* stops, const uint32_t* stopOffsets, uint32_t* accepted, cudaStream_t stream);
+cudaError_t commit_states_launch(const infdev_query* queries, int count, const uint32_t* accepted, const uint64_t* stateNext,
+                                 uint64_t candidateBase, uint64_t stateBytes, cudaStream_t stream);
+
 }  // namespace infdev

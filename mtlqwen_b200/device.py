@@ -34,7 +34,7 @@ def library():
   if _lib is not None:
     return _lib
   lib = ctypes.CDLL(str(_build.build()))
-  vp, i64, i32, u32, f32p = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_uint32, ctypes.c_void_p
+  vp, i64, i32, u32, f32p, u64 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint64
   proto = {
     "infdev_create": (vp, (i32, ctypes.c_char_p)),
     "infdev_destroy": (None, (vp, )),
@@ -65,6 +65,16 @@ def library():
     "infdev_embedding": (i32, (vp, i32, vp, i64, vp, i64, f32p)),
     "infdev_rms_norm": (i32, (vp, f32p, f32p, i64, i64, f32p)),
     "infdev_rms_norm_gather": (i32, (vp, f32p, f32p, vp, i32, i64, f32p)),
+    "infdev_gdn_prepare": (i32, (vp, f32p, f32p, f32p, f32p, f32p, f32p, f32p, vp, i32, i64, u64, u64, f32p, f32p, f32p, f32p, f32p)),
+    "infdev_delta_rule": (i32, (vp, f32p, f32p, f32p, f32p, f32p, f32p, f32p, vp, i32, u64, u64, f32p)),
+    "infdev_rope_table": (i32, (vp, i64, f32p)),
+    "infdev_attention_prepare": (i32, (vp, f32p, f32p, f32p, f32p, f32p, f32p, vp, i32, i64, vp, i32, i32, f32p, vp, vp)),
+    "infdev_attention": (i32, (vp, f32p, f32p, vp, vp, vp, i32, i64, vp, i32, i32, u32, f32p, f32p)),
+    "infdev_attention_scratch_bytes": (ctypes.c_size_t, (i64, u32)),
+    "infdev_sample": (i32, (vp, f32p, i64, vp, i32, i64, u32, vp)),
+    "infdev_pack_queries": (i32, (vp, vp, i32, i32, u32, vp, vp, u64, u64, vp, vp)),
+    "infdev_verify_drafts": (i32, (vp, vp, i32, vp, vp, u32, vp, vp, vp)),
+    "infdev_commit_states": (i32, (vp, vp, i32, vp, vp, u64, u64)),
   }
   for name, (restype, argtypes) in proto.items():
     function = getattr(lib, name)
@@ -182,3 +192,30 @@ class Device:
 
   def rms_norm(self, x, w, rows, dim, y):
     self.check(self.lib.infdev_rms_norm(self.ctx, x.ptr, w.ptr, rows, dim, y.ptr))
+
+  def gdn_prepare(self, x, mixed, w_beta, w_alpha, ssm_a, ssm_dt, conv_w, queries, nq, rows, state_offset, state_bytes, q, k, v, beta, g):
+    self.check(self.lib.infdev_gdn_prepare(self.ctx, x.ptr, mixed.ptr, w_beta.ptr, w_alpha.ptr, ssm_a.ptr, ssm_dt.ptr, conv_w.ptr, queries.ptr, nq,
+                                           rows, state_offset, state_bytes, q.ptr, k.ptr, v.ptr, beta.ptr, g.ptr))
+
+  def delta_rule(self, q, k, v, g, beta, z, norm_w, queries, nq, state_offset, state_bytes, out):
+    self.check(self.lib.infdev_delta_rule(self.ctx, q.ptr, k.ptr, v.ptr, g.ptr, beta.ptr, z.ptr if z is not None else None,
+                                          norm_w.ptr if norm_w is not None else None, queries.ptr, nq, state_offset, state_bytes, out.ptr))
+
+  def rope_table(self, positions):
+    table = self.empty((positions, 32, 2))
+    self.check(self.lib.infdev_rope_table(self.ctx, positions, table.ptr))
+    return table
+
+  def attention_prepare(self, qg, k, v, q_norm, k_norm, rope, queries, nq, rows, table, table_stride, block_tokens, q, cache_k, cache_v):
+    self.check(self.lib.infdev_attention_prepare(self.ctx, qg.ptr, k.ptr, v.ptr, q_norm.ptr, k_norm.ptr, rope.ptr, queries.ptr, nq, rows, table.ptr,
+                                                 table_stride, block_tokens, q.ptr, cache_k.ptr, cache_v.ptr))
+
+  def attention(self, q, qg, cache_k, cache_v, queries, nq, rows, table, table_stride, block_tokens, max_splits, partials, out):
+    self.check(self.lib.infdev_attention(self.ctx, q.ptr, qg.ptr, cache_k.ptr, cache_v.ptr, queries.ptr, nq, rows, table.ptr, table_stride,
+                                         block_tokens, max_splits, partials.ptr, out.ptr))
+
+  def attention_scratch_bytes(self, rows, max_splits):
+    return int(self.lib.infdev_attention_scratch_bytes(rows, max_splits))
+
+  def sample(self, logits, vocab, queries, nq, count, mode, tokens):
+    self.check(self.lib.infdev_sample(self.ctx, logits.ptr, vocab, queries.ptr, nq, count, mode, tokens.ptr))

@@ -48,3 +48,9 @@ def test_gate_up_is_silu_times_up():
   g, u = oracle.linear(wg, oracle.Q4_K, n, k, x), oracle.linear(wu, oracle.Q4_K, n, k, x)
   want = g / (1 + np.exp(-g)) * u
   assert np.allclose(oracle.gate_up(wg, wu, oracle.Q4_K, n, k, x), want, rtol=1e-5, atol=1e-7)
+
+
+def test_philox_known_answer():
+  """Philox4x32-10 with zero key and counter: the first known-answer vector of the Random123 distribution."""
+  assert oracle.philox(0, 0) == [0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8]
+  assert 0.0 <= oracle.uniform(5, 9) < 1.0 and oracle.uniform(5, 9) == oracle.uniform(5, 9) != oracle.uniform(5, 10)
