@@ -136,12 +136,19 @@ int infdev_rope_table(infdev_ctx* ctx, int64_t positions, float* table);
 int infdev_attention_prepare(infdev_ctx* ctx, const float* qg, const float* k, const float* v, const float* qNorm, const float* kNorm,
                              const float* rope, const infdev_query* queries, int queryCount, int64_t rows, const int32_t* table,
                              int32_t tableStride, int32_t blockTokens, float* q, void* cacheK, void* cacheV);
+/* With qg == NULL only the K/V store runs: mtp_store_kv (attention.metal:53-100, drafter_store_kv<256>). */
 /* attention_scan + attention_reduce (attention.metal:103-216): causal GQA over the cache, times
  * sigmoid(gate). partials: scratch of infdev_attention_scratch_bytes(rows, maxSplits) bytes. */
 int infdev_attention(infdev_ctx* ctx, const float* q, const float* qg, const void* cacheK, const void* cacheV, const infdev_query* queries,
                      int queryCount, int64_t rows, const int32_t* table, int32_t tableStride, int32_t blockTokens, uint32_t maxSplits,
                      float* partials, float* out);
 size_t infdev_attention_scratch_bytes(int64_t rows, uint32_t maxSplits);
+
+/* mtp_fuse (native_ops.metal:43-87): y [rows,8192] = [rmsnorm(embedding) * enorm | rmsnorm(h) * hnorm]; h is
+ * the slot's stored seed, the previous row's hidden or the same row's hidden by mode (2, 1, 0); mode 1 also
+ * stores the next seed. seedOffset: byte offset of the seed (fp32 [4096]) inside a state record. */
+int infdev_mtp_fuse(infdev_ctx* ctx, const float* embedding, const float* hidden, const infdev_query* queries, int queryCount, const float* enorm,
+                    const float* hnorm, int64_t rows, uint32_t mode, uint64_t seedOffset, uint64_t stateBytes, float* y);
 
 /* ---- sampling, packing, verification ---- */
 /* sample_logits (native_ops.metal:122-224): logits fp32 [count,vocab]; mode 0 target, 1 MTP drafting. */

@@ -45,6 +45,8 @@ __global__ void __launch_bounds__(256) attention_prepare_kernel(const float* qg,
                                                                 __half* cacheV) {
   const int row = blockIdx.x / 20, head = blockIdx.x % 20, lane = threadIdx.x;
   const bool query = head < kQHeads;
+  if (query && !qg)  // K/V store only (mtp_store_kv, attention.metal:53-100)
+    return;
   const int local = query ? head : head - kQHeads;
   const float* source = query ? qg + (size_t(row) * kQHeads + local) * kDim * 2 : rawK + (size_t(row) * kKvHeads + local) * kDim;
   const float* weight = query ? qNorm : kNorm;

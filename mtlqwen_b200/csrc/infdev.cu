@@ -429,6 +429,14 @@ int infdev_attention(infdev_ctx* ctx, const float* q, const float* qg, const voi
                "attention");
 }
 
+int infdev_mtp_fuse(infdev_ctx* ctx, const float* embedding, const float* hidden, const infdev_query* queries, int queryCount, const float* enorm,
+                    const float* hnorm, int64_t rows, uint32_t mode, uint64_t seedOffset, uint64_t stateBytes, float* y) {
+  Bind bind(ctx);
+  (void)queryCount;
+  return check(ctx, infdev::mtp_fuse_launch(embedding, hidden, queries, enorm, hnorm, rows, mode, seedOffset, stateBytes, y, ctx->stream),
+               "mtp_fuse");
+}
+
 // ---- sampling, packing, verification -----------------------------------------------------------
 
 int infdev_sample(infdev_ctx* ctx, const float* logits, int64_t vocab, infdev_query* queries, int queryCount, int64_t count, uint32_t mode,

@@ -119,7 +119,64 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float* x, const flo
   }
 }
 
+// mtp_fuse (native_ops.metal:43-87): y[row] = [rmsnorm(embedding[row]) * enorm | rmsnorm(h) * hnorm], 8192 wide.
+// h by mode: 2 = the slot's MTP seed (the target's hidden state of the last committed position, kept at the end
+// of the state record); 1 = seed for a query's first row, else the target hidden of the previous row; 0 = the
+// hidden of the same row (previous MTP step). A fresh sequence's first row has no predecessor: h = 0.
+// Mode 1 also stores the target hidden of each candidate row (speculative) or of the last row as the next seed.
+__global__ void __launch_bounds__(256) mtp_fuse_kernel(const float* embedding, const float* hidden, const infdev_query* queries, const float* enorm,
+                                                       const float* hnorm, uint32_t mode, uint64_t seedOffset, uint64_t stateBytes, float* y) {
+  const uint32_t row = blockIdx.x, tid = threadIdx.x;
+  const infdev_query& info = query_of_row(queries, row);
+  const uint32_t token = row - info.start;
+  const float* seed = reinterpret_cast<const float*>(info.previous + seedOffset);
+  const float* h = mode == 2 ? seed : (mode == 1 && !token) ? seed : hidden + size_t(mode == 1 ? row - 1 : row) * 4096;
+  const bool initial = !info.previous && token == 0 && mode != 0;
+  __shared__ float sums[18];
+  float es = 0.f, hs = 0.f;
+  for (int d = tid; d < 4096; d += 256) {
+    const float ev = embedding[size_t(row) * 4096 + d], hv = initial ? 0.f : h[d];
+    es += ev * ev;
+    hs += hv * hv;
+  }
+  es = warp_sum(es);
+  hs = warp_sum(hs);
+  if ((tid & 31) == 0) {
+    sums[tid >> 5] = es;
+    sums[8 + (tid >> 5)] = hs;
+  }
+  __syncthreads();
+  if (tid < 32) {
+    es = warp_sum(tid < 8 ? sums[tid] : 0.f);
+    hs = warp_sum(tid < 8 ? sums[8 + tid] : 0.f);
+    if (tid == 0) {
+      sums[16] = rsqrtf(es / 4096.f + 1.0e-6f);
+      sums[17] = rsqrtf(hs / 4096.f + 1.0e-6f);
+    }
+  }
+  __syncthreads();
+  const bool speculative = info.state != 0xffffffffu;
+  float* nextSeed = nullptr;
+  if (mode == 1 && (speculative || token + 1 == info.count))
+    nextSeed = reinterpret_cast<float*>(info.next + (speculative ? uint64_t(token) * stateBytes : 0) + seedOffset);
+  for (int d = tid; d < 4096; d += 256) {
+    const float hv = initial ? 0.f : h[d];
+    y[size_t(row) * 8192 + d] = embedding[size_t(row) * 4096 + d] * sums[16] * enorm[d];
+    y[size_t(row) * 8192 + 4096 + d] = hv * sums[17] * hnorm[d];
+    if (nextSeed)
+      nextSeed[d] = hidden[size_t(row) * 4096 + d];
+  }
+}
+
 }  // namespace
+
+cudaError_t mtp_fuse_launch(const float* embedding, const float* hidden, const infdev_query* queries, const float* enorm, const float* hnorm,
+                            int64_t rows, uint32_t mode, uint64_t seedOffset, uint64_t stateBytes, float* y, cudaStream_t stream) {
+  if (rows <= 0)
+    return cudaSuccess;
+  mtp_fuse_kernel<<<unsigned(rows), 256, 0, stream>>>(embedding, hidden, queries, enorm, hnorm, mode, seedOffset, stateBytes, y);
+  return cudaGetLastError();
+}
 
 cudaError_t dequant_launch(int type, const void* blocks, int64_t count, float* out, cudaStream_t stream) {
   if (count <= 0)

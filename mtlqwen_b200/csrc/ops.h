@@ -12,6 +12,8 @@ cudaError_t gather_tokens_launch(const infdev_query* queries, int queryCount, co
                                  const int32_t* proposals, uint32_t mode, int32_t* rowTokens, cudaStream_t stream);
 cudaError_t rms_norm_launch(const float* x, const float* w, const infdev_query* queries, int64_t rows, int64_t dim, float* y, cudaStream_t stream);
 
+cudaError_t mtp_fuse_launch(const float* embedding, const float* hidden, const infdev_query* queries, const float* enorm, const float* hnorm,
+                            int64_t rows, uint32_t mode, uint64_t seedOffset, uint64_t stateBytes, float* y, cudaStream_t stream);
 cudaError_t gdn_prepare_launch(const float* x, const float* mixed, const float* wBeta, const float* wAlpha, const float* A, const float* dt,
                                const float* convWeight, const infdev_query* queries, int64_t rows, uint64_t stateOffset, uint64_t stateBytes,
                                float* q, float* k, float* v, float* beta, float* g, cudaStream_t stream);

@@ -1,0 +1,129 @@
+// Host-side engine types: the CUDA build of model/qwen35/qwen35.hpp. Same roles and field meanings as the
+// reference (Engine, Sequence, Weights, Scratch, PhysicalBlock, HybridCheckpoint, Batch; qwen35.hpp:20-116),
+// with the layer count and vocabulary read from the GGUF file instead of being compile-time constants so
+// that reduced models can be checked against the CPU oracle.
+#pragma once
+#include <array>
+#include <atomic>
+#include <condition_variable>
+#include <filesystem>
+#include <list>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <unordered_map>
+#include <utility>
+#include <vector>
+#include "cuda_device.hpp"
+
+namespace infeng::qwen35 {
+
+inline constexpr uint32_t hiddenSize = 4096, intermediateSize = 12288, fullAttentionInterval = 4;
+inline constexpr uint32_t maxDraftTokens = 7, maxBatchSequences = 8, maxBatchTokens = 128;
+inline constexpr uint32_t maxLogitRows = maxBatchSequences * (maxDraftTokens + 1);
+inline constexpr uint32_t checkpointTokens = 512, maxCheckpoints = 8, maxAttentionSplits = 32;
+inline constexpr uint32_t unbound = UINT32_MAX;
+inline constexpr uint64_t seedBytes = hiddenSize * sizeof(float);  // MTP seed (last target hidden) at the end of a state record
+
+enum class Drafter : uint8_t { none, mtp, dflash };
+
+struct Weight : Tensor {
+  uint32_t n = 0, k = 0, type = 0;
+};
+using Weights = std::unordered_map<std::string, Weight>;
+
+// Fixed scratch for one pass of up to maxBatchTokens rows (Scratch, qwen35.hpp:41-46); all fp32.
+struct Scratch {
+  Tensor hidden, norm, temporary, mlpGate;
+  Tensor mixed, gate, q, k, v, attnQ, attnPartials;
+  Tensor gdnB, gdnG;
+  Tensor fused, targetLogits, rowTokens;
+};
+
+struct PhysicalBlock {
+  uint32_t refs = 0;
+  uint64_t touch = 0;
+};
+
+// A published 512-token prefix: chained hash, the shared recurrent-state arena and the K/V bindings.
+struct HybridCheckpoint {
+  uint64_t hash = 0;
+  Tensor arena;
+  std::vector<uint32_t> bindings;
+};
+
+struct Sequence;
+
+struct Batch {
+  infdev_query* queries = nullptr;  // raw scheduler records in host-visible memory, read by the device pack kernel
+  // The same records finished on the host (start, samples, logit, state addresses): target frame, then drafter frame.
+  std::array<infdev_query, 2 * maxBatchSequences> finished{};
+  uint32_t size = 0, candidateRows = 0;
+};
+
+struct Engine {
+  std::atomic_uint32_t owners{1};  // one API handle and one reference per live sequence
+  Device device;
+  uint32_t maxContext, draftWidth = 0;
+  uint32_t targetLayers = 0, kvLayers = 0, gdnLayers = 0, vocab = 0, blockTokens = 128;
+  uint64_t stateBytes = 0;
+  std::unique_ptr<PagedKV> kv;
+  Weights weights;
+  Tensor weightData, rope;
+  Drafter drafter = Drafter::none;
+  Tensor candidateStates;
+  Scratch workspace;
+  Tensor requestData, queryInput, queryData, passMeta, stateAddresses;
+  Tensor draftTokens, outputTokens;
+  uint64_t seeds[maxBatchSequences]{};
+  std::vector<PhysicalBlock> blocks;
+  std::list<HybridCheckpoint> checkpointCache;
+  std::array<Sequence*, maxBatchSequences> sequences{};
+  std::array<std::pair<Tensor, Tensor>, maxBatchSequences> statePool;
+  std::mutex mutex;
+  std::condition_variable condition;
+  std::thread worker;
+  bool closing = false;
+  uint64_t clock = 0;
+  uint64_t parameterCount = 0, modelBytes = 0;
+  // step counters for roofline reporting
+  std::atomic_uint64_t passes{0}, passRows{0}, passMicros{0};
+
+  Engine(const std::filesystem::path& weights, uint32_t maxContext, const std::filesystem::path& draftWeights);
+  ~Engine();
+  void loadModel(const std::filesystem::path& weights, const std::filesystem::path& draftWeights);
+
+  bool reserve(const Batch& batch);
+  void bind(Sequence& sequence, uint32_t physical);
+  void restorePrefix(Sequence& sequence);
+  void publishPrefix(Sequence& sequence);
+  void schedule();
+};
+
+struct Sequence {
+  Engine& engine;
+  int32_t* request;
+  uint32_t requested = 0;
+  std::vector<uint32_t> bindings;
+  std::vector<int32_t> stops;
+  bool error = false;
+  uint64_t drafted = 0, accepted = 0, prefixHash = 0;
+  uint32_t kvValid = 0;
+  uint32_t slot;
+  float temperature, topP;
+  int32_t topK;
+  bool speculative, active = false, busy = false;
+  Sequence(Engine&, const int32_t* stops, uint32_t stopCount, float temperature, float topP, int32_t topK, bool speculative);
+  ~Sequence();
+};
+
+// Result of finishing the per-query records of a pass on the host (the device does the same in
+// infdev_pack_queries; the host needs the counts for launch geometry and the logit offsets to read tokens).
+struct PassShape {
+  uint32_t rows = 0, logits = 0, queries = 0;
+  bool sequential = false, prefill = false;
+};
+
+PassShape forward(Engine& engine, Batch& batch, bool drafting = false);
+
+}  // namespace infeng::qwen35

@@ -1,0 +1,408 @@
+// Engine lifetime, the continuous-batching scheduler thread, K/V block reservation, the prefix-checkpoint
+// cache, the commit of sampled tokens, and the infeng_* C ABI. CUDA build of runtime/engine.cpp: the
+// behaviour (batch composition, 512-token checkpoint boundaries, LRU block eviction, acceptance rule,
+// error codes) follows the reference; the Metal device underneath is replaced by infdev.
+#include <algorithm>
+#include <chrono>
+#include <cstdlib>
+#include <cstring>
+#include <stdexcept>
+#include "../../include/infeng.h"
+#include "runtime.hpp"
+
+namespace infeng::qwen35 {
+namespace {
+
+// Chains one 512-token block into a prefix hash (hashCheckpoint, engine.cpp:9-16).
+uint64_t hashCheckpoint(uint64_t hash, const int32_t* tokens) {
+  hash ^= 0x9e3779b97f4a7c15ull;
+  for (uint32_t i = 0; i < checkpointTokens; ++i) {
+    hash ^= uint32_t(tokens[i]) + 0x9e3779b9u + (hash << 6) + (hash >> 2);
+    hash *= 0x100000001b3ull;
+  }
+  return hash;
+}
+
+uint32_t environment(const char* name, uint32_t fallback) {
+  const char* text = std::getenv(name);
+  return text && *text ? uint32_t(std::strtoul(text, nullptr, 10)) : fallback;
+}
+
+int deviceIndex() {
+  if (const char* text = std::getenv("INFENG_DEVICE"))
+    return std::atoi(text);
+  if (const char* text = std::getenv("LOCAL_RANK"))
+    return std::atoi(text);
+  return 0;
+}
+
+}  // namespace
+
+// Binds the next logical block of a sequence to a physical block (Engine::bind, engine.cpp:18-22).
+void Engine::bind(Sequence& sequence, uint32_t physical) {
+  kv->map(sequence.slot * kv->tableStride() + uint32_t(sequence.bindings.size()), physical);
+  sequence.bindings.push_back(physical);
+  ++blocks[physical].refs;
+}
+
+// Makes sure every block the batch will touch is bound, evicting the least recently used unreferenced block
+// when a sequence grows; false if no block can be freed (Engine::reserve, engine.cpp:24-46).
+bool Engine::reserve(const Batch& batch) {
+  for (uint32_t i = 0; i < batch.size; ++i) {
+    const infdev_query& query = batch.queries[i];
+    Sequence& sequence = *sequences[query.slot];
+    const uint32_t first = sequence.kvValid / blockTokens, last = (sequence.kvValid + query.count - 1) / blockTokens;
+    for (uint32_t logical = first; logical <= last; ++logical) {
+      if (logical == sequence.bindings.size()) {
+        uint32_t victim = 0;
+        uint64_t oldest = UINT64_MAX;
+        bool found = false;
+        for (uint32_t b = 0; b < blocks.size(); ++b)
+          if (!blocks[b].refs && (!found || blocks[b].touch < oldest)) {
+            victim = b;
+            oldest = blocks[b].touch;
+            found = true;
+          }
+        if (!found)
+          return false;
+        kv->ensure(victim + 1);
+        // A checkpoint that references the evicted block can no longer be restored.
+        checkpointCache.remove_if([victim](const HybridCheckpoint& checkpoint) {
+          return std::find(checkpoint.bindings.begin(), checkpoint.bindings.end(), victim) != checkpoint.bindings.end();
+        });
+        bind(sequence, victim);
+      }
+      blocks[sequence.bindings[logical]].touch = ++clock;
+    }
+  }
+  return true;
+}
+
+// Finds the deepest published prefix of the request and adopts its state arena and K/V bindings
+// (Engine::restorePrefix, engine.cpp:48-68). The match is by chained hash only.
+void Engine::restorePrefix(Sequence& sequence) {
+  uint64_t hash = 0;
+  auto best = checkpointCache.end();
+  const uint32_t fullBlocks = (sequence.requested - 1) / checkpointTokens;
+  for (uint32_t index = 0; index < fullBlocks; ++index) {
+    hash = hashCheckpoint(hash, sequence.request + uint64_t(index) * checkpointTokens);
+    for (auto entry = checkpointCache.begin(); entry != checkpointCache.end(); ++entry)
+      if (entry->hash == hash) {
+        best = entry;
+        break;
+      }
+  }
+  if (best == checkpointCache.end())
+    return;
+  checkpointCache.splice(checkpointCache.end(), checkpointCache, best);
+  sequence.prefixHash = best->hash;
+  const uint64_t touch = ++clock;
+  statePool[sequence.slot].first = best->arena;
+  for (uint32_t physical : best->bindings) {
+    bind(sequence, physical);
+    blocks[physical].touch = touch;
+  }
+  sequence.kvValid = uint32_t(best->bindings.size()) * blockTokens;
+}
+
+// Publishes the sequence's state at every 512-token boundary (Engine::publishPrefix, engine.cpp:70-83).
+void Engine::publishPrefix(Sequence& sequence) {
+  if (sequence.kvValid % checkpointTokens)
+    return;
+  sequence.prefixHash = hashCheckpoint(sequence.prefixHash, sequence.request + sequence.kvValid - checkpointTokens);
+  for (auto entry = checkpointCache.begin(); entry != checkpointCache.end(); ++entry)
+    if (entry->hash == sequence.prefixHash) {
+      checkpointCache.splice(checkpointCache.end(), checkpointCache, entry);
+      return;
+    }
+  if (checkpointCache.size() == maxCheckpoints)
+    checkpointCache.pop_front();
+  checkpointCache.push_back({sequence.prefixHash, statePool[sequence.slot].first, sequence.bindings});
+}
+
+Engine::Engine(const std::filesystem::path& path, uint32_t context, const std::filesystem::path& draftPath)
+    : device(deviceIndex()), maxContext(context) {
+  blockTokens = environment("INFENG_BLOCK_TOKENS", 128);
+  if (!blockTokens || blockTokens % 16 || checkpointTokens % blockTokens)
+    throw std::runtime_error("INFENG_BLOCK_TOKENS must be a multiple of 16 that divides 512");
+  device.commitTimeoutMs = environment("INFENG_COMMIT_TIMEOUT_MS", 120000);
+  // The reference sizes the physical pool for one sequence of maximum context (engine.cpp:86); INFENG_KV_BLOCKS overrides.
+  const uint32_t perSlot = (context + blockTokens - 1) / blockTokens;
+  blocks.resize(environment("INFENG_KV_BLOCKS", perSlot));
+  loadModel(path, draftPath);
+  requestData = device.empty(uint64_t(maxBatchSequences) * (maxContext + 1) * sizeof(int32_t), true);
+  draftTokens = device.empty((maxDraftTokens + 1) * maxBatchSequences * sizeof(int32_t), true);
+  outputTokens = device.empty(maxLogitRows * sizeof(int32_t), true);
+  queryInput = device.empty(maxBatchSequences * sizeof(infdev_query), true);
+  stateAddresses = device.empty(2 * maxBatchSequences * sizeof(uint64_t), true);
+  queryData = device.empty(2 * maxBatchSequences * sizeof(infdev_query));
+  passMeta = device.empty(8 * sizeof(uint32_t));
+  for (auto& states : statePool)
+    states = {device.empty(stateBytes), device.empty(stateBytes)};
+  uint64_t seed = environment("INFENG_SEED", 0);
+  if (!std::getenv("INFENG_SEED"))
+    seed = uint64_t(std::chrono::high_resolution_clock::now().time_since_epoch().count());
+  for (uint32_t i = 0; i < maxBatchSequences; ++i)
+    seeds[i] = ++seed;
+  kv = std::make_unique<PagedKV>(device, maxBatchSequences, perSlot, uint32_t(blocks.size()), kvLayers + (drafter == Drafter::mtp ? 1 : 0), blockTokens);
+  device.check(device.commit());
+  worker = std::thread(&Engine::schedule, this);
+}
+
+Engine::~Engine() {
+  {
+    std::lock_guard<std::mutex> lock(mutex);
+    closing = true;
+  }
+  condition.notify_all();
+  if (worker.joinable())
+    worker.join();
+}
+
+Sequence::Sequence(Engine& owner, const int32_t* stopTokens, uint32_t stopCount, float samplingTemperature, float samplingTopP, int32_t samplingTopK,
+                   bool useSpeculation)
+    : engine(owner), temperature(samplingTemperature), topP(samplingTopP), topK(samplingTopK), speculative(useSpeculation) {
+  std::lock_guard<std::mutex> lock(engine.mutex);
+  stops.assign(stopTokens, stopTokens + stopCount);
+  slot = uint32_t(std::find(engine.sequences.begin(), engine.sequences.end(), nullptr) - engine.sequences.begin());
+  if (slot == maxBatchSequences)
+    throw std::runtime_error("maximum live sequence count reached");
+  request = engine.requestData.contents<int32_t>() + uint64_t(slot) * (engine.maxContext + 1);
+  engine.sequences[slot] = this;
+  ++engine.owners;
+}
+
+Sequence::~Sequence() {
+  std::unique_lock<std::mutex> lock(engine.mutex);
+  active = false;
+  engine.condition.wait(lock, [&] { return !busy; });
+  for (uint32_t physical : bindings)
+    --engine.blocks[physical].refs;
+  engine.sequences[slot] = nullptr;
+}
+
+// The scheduler thread (Engine::schedule, engine.cpp:142-230). Each iteration packs every ready sequence into
+// one pass of at most 128 rows: decodes take one row (plus the draft rows when speculating), prefills share
+// what is left and never cross a 512-token boundary; then reserve K/V, run the drafting and target passes,
+// block on the commit, and publish tokens.
+void Engine::schedule() {
+  std::unique_lock<std::mutex> lock(mutex);
+  auto ready = [](Sequence* sequence) { return sequence && sequence->active; };
+  while (true) {
+    condition.wait(lock, [&] { return closing || std::any_of(sequences.begin(), sequences.end(), ready); });
+    if (closing)
+      return;
+    Batch batch;
+    batch.queries = queryInput.contents<infdev_query>();
+    std::array<infdev_query*, maxBatchSequences> prefills{};
+    uint32_t prefillCount = 0, remaining = maxBatchTokens;
+    for (Sequence* sequence : sequences) {
+      if (!ready(sequence))
+        continue;
+      sequence->busy = true;
+      if (!sequence->kvValid)
+        restorePrefix(*sequence);
+      // The output state must not be an arena that a checkpoint still shares.
+      if (statePool[sequence->slot].second.buffer.use_count() > 1)
+        statePool[sequence->slot].second = device.empty(stateBytes);
+      infdev_query& query = batch.queries[batch.size++];
+      query = infdev_query{};
+      query.count = 1;
+      query.position = sequence->kvValid;
+      query.slot = sequence->slot;
+      query.state = unbound;
+      query.samples = sequence->requested;  // finished into a sample count by the pack step
+      query.temperature = sequence->temperature;
+      query.topP = sequence->topP;
+      query.topK = sequence->topK;
+      query.seed = seeds[sequence->slot];
+      const uint32_t pending = sequence->requested - sequence->kvValid;
+      const uint32_t boundary = std::min(maxContext, (sequence->kvValid / checkpointTokens + 1) * checkpointTokens);
+      const uint32_t room = boundary - sequence->kvValid;
+      if (pending > 1) {
+        query.count = std::min(pending, room);
+        prefills[prefillCount++] = &query;
+        continue;
+      }
+      if (sequence->speculative && room > draftWidth) {
+        query.count += draftWidth;
+        query.state = batch.candidateRows;
+        batch.candidateRows += query.count;
+      }
+      remaining -= query.count;
+    }
+    for (uint32_t i = 0; i < prefillCount; ++i) {
+      infdev_query& query = *prefills[i];
+      query.count = std::min(query.count, remaining / (prefillCount - i));
+      remaining -= query.count;
+    }
+    bool success = reserve(batch);
+    lock.unlock();
+    PassShape shape;
+    if (success) {
+      try {
+        if (stateBytes * batch.candidateRows > candidateStates.bytes)
+          candidateStates = device.empty(stateBytes * batch.candidateRows);
+        const auto started = std::chrono::steady_clock::now();
+        if (batch.candidateRows)
+          forward(*this, batch, true);
+        shape = forward(*this, batch);
+        device.check(device.commit());
+        passMicros += uint64_t(std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - started).count());
+        passRows += shape.rows;
+        ++passes;
+      } catch (const std::exception&) {
+        success = false;  // a device failure is reported to every sequence of the batch like a capacity failure
+      }
+    }
+    lock.lock();
+    const int32_t *sampled = outputTokens.contents<int32_t>(), *proposed = draftTokens.contents<int32_t>();
+    bool copied = false;
+    for (uint32_t i = 0; i < batch.size; ++i) {
+      const infdev_query& query = success ? batch.finished[i] : batch.queries[i];
+      Sequence& sequence = *sequences[query.slot];
+      sequence.busy = false;
+      sequence.error = !success;
+      sequence.active &= success;
+      if (!sequence.active)
+        continue;
+      const bool speculative = query.state != unbound;
+      uint32_t accepted = 0;
+      bool stopped = false;
+      for (uint32_t s = 0; s < query.samples && !stopped; ++s) {
+        const int32_t token = sampled[query.logit + s];
+        sequence.request[sequence.requested++] = token;
+        stopped = std::find(sequence.stops.begin(), sequence.stops.end(), token) != sequence.stops.end();
+        if (!speculative || s == draftWidth || token != proposed[(s + 1) * maxBatchSequences + query.state / query.count])
+          break;
+        ++accepted;
+      }
+      if (speculative) {
+        device.copy(candidateStates.view(query.state + accepted, 1, stateBytes), statePool[query.slot].second);
+        copied = true;
+      }
+      sequence.kvValid += speculative ? 1 + accepted : query.count;
+      sequence.drafted += speculative ? draftWidth : 0;
+      sequence.accepted += accepted;
+      std::swap(statePool[query.slot].first, statePool[query.slot].second);
+      sequence.active = sequence.kvValid < maxContext && !stopped;
+      publishPrefix(sequence);
+    }
+    if (copied)
+      device.commit();
+    condition.notify_all();
+  }
+}
+
+}  // namespace infeng::qwen35
+
+using namespace infeng::qwen35;
+
+// infeng_engine and infeng_sequence are the opaque names of Engine and Sequence in the C header.
+struct infeng_engine : Engine {
+  using Engine::Engine;
+};
+struct infeng_sequence : Sequence {
+  using Sequence::Sequence;
+};
+
+namespace {
+void report(char* error, const std::exception& exception) {
+  if (error) {
+    std::strncpy(error, exception.what(), 1023);
+    error[1023] = 0;
+  }
+}
+}  // namespace
+
+extern "C" {
+
+infeng_engine* infeng_engine_create(const char* weights, const char* draftWeights, const char* kernels, uint32_t context, char* error) {
+  (void)kernels;  // the Metal build compiles its kernel sources from this directory; the CUDA kernels are linked in
+  try {
+    if (!context || context > 65536)
+      throw std::runtime_error("context must be between 1 and 65536");
+    return new infeng_engine(weights, context, draftWeights ? draftWeights : "");
+  } catch (const std::exception& exception) {
+    report(error, exception);
+    return nullptr;
+  }
+}
+
+void infeng_engine_release(infeng_engine* engine) {
+  if (--engine->owners == 0)
+    delete engine;
+}
+
+infeng_sequence* infeng_sequence_create(infeng_engine* engine, const int32_t* stops, uint32_t stopCount, float temperature, float topP, int32_t topK,
+                                        uint32_t speculative, char* error) {
+  try {
+    return new infeng_sequence(*engine, stops, stopCount, temperature, topP, topK, speculative != 0 && engine->drafter != Drafter::none);
+  } catch (const std::exception& exception) {
+    report(error, exception);
+    return nullptr;
+  }
+}
+
+void infeng_sequence_release(infeng_sequence* sequence) {
+  infeng_engine* engine = static_cast<infeng_engine*>(&sequence->engine);
+  delete sequence;
+  infeng_engine_release(engine);
+}
+
+int32_t infeng_sequence_append(infeng_sequence* sequence, const int32_t* tokens, uint32_t count) {
+  Engine& engine = sequence->engine;
+  std::lock_guard<std::mutex> lock(engine.mutex);
+  if (count == UINT32_MAX) {  // cancel
+    sequence->active = false;
+    engine.condition.notify_all();
+    return 0;
+  }
+  if (sequence->active || sequence->busy)
+    return -3;
+  if ((!count && sequence->requested == sequence->kvValid) || uint64_t(sequence->requested) + count > engine.maxContext)
+    return -4;
+  std::copy_n(tokens, count, sequence->request + sequence->requested);
+  sequence->requested += count;
+  sequence->error = false;
+  sequence->active = true;
+  engine.condition.notify_all();
+  return int32_t(sequence->requested);
+}
+
+int32_t infeng_sequence_read(infeng_sequence* sequence, uint32_t cursor) {
+  Engine& engine = sequence->engine;
+  std::unique_lock<std::mutex> lock(engine.mutex);
+  engine.condition.wait(lock, [&] { return cursor < sequence->requested || (!sequence->active && !sequence->busy); });
+  if (sequence->error)
+    return -5;
+  return cursor < sequence->requested ? sequence->request[cursor] : -1;
+}
+
+uint64_t infeng_engine_info(infeng_engine* engine, uint32_t field) {
+  switch (field) {
+    case 0: return engine->parameterCount;
+    case 1: return engine->modelBytes;
+    case 2: return engine->kv->mappedBytes();
+    case 3: return uint64_t(engine->drafter);
+    case 4: return engine->draftWidth;
+    case 5: return engine->passes.load();
+    case 6: return engine->passRows.load();
+    case 7: return engine->passMicros.load();
+    case 8: return engine->targetLayers;
+    case 9: return engine->vocab;
+    default: return 0;
+  }
+}
+
+uint64_t infeng_sequence_info(infeng_sequence* sequence, uint32_t field) {
+  std::lock_guard<std::mutex> lock(sequence->engine.mutex);
+  switch (field) {
+    case 0: return sequence->drafted;
+    case 1: return sequence->accepted;
+    case 2: return sequence->kvValid;
+    default: return 0;
+  }
+}
+
+}  // extern "C"
