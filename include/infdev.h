@@ -55,6 +55,8 @@ infdev_ctx* infdev_create(int device, char* error /* >= 1024 bytes, may be null 
 void infdev_destroy(infdev_ctx* ctx);
 const char* infdev_error(infdev_ctx* ctx);
 int infdev_sm_count(infdev_ctx* ctx);
+/* Number of kernels this context has launched so far (for launch accounting in benchmarks). */
+uint64_t infdev_launch_count(infdev_ctx* ctx);
 /* hostVisible != 0: pinned host memory mapped into the device (Metal "shared" storage, device.cpp:82-85);
  * the returned pointer is valid on both sides. Otherwise device memory, zero-filled. */
 void* infdev_alloc(infdev_ctx* ctx, size_t bytes, int hostVisible);

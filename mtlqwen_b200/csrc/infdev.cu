@@ -1,5 +1,6 @@
 // C-ABI device layer: context, memory, stream, and the typed kernel entry points declared in
 // include/infdev.h. This file holds no math; it validates arguments and launches.
+#include <atomic>
 #include <chrono>
 #include <cmath>
 #include <cstdio>
@@ -15,6 +16,7 @@
 
 struct infdev_ctx {
   int device = 0, sms = 0, xsplit = 2, debug = 0;
+  std::atomic<uint64_t> launches{0};  // kernels launched through this context
   cudaStream_t stream = nullptr;
   cudaEvent_t done = nullptr;
   int* status = nullptr;      // device status word written by kernels that abort a bounded wait
@@ -108,6 +110,8 @@ void infdev_destroy(infdev_ctx* ctx) {
 const char* infdev_error(infdev_ctx* ctx) { return ctx ? ctx->error.c_str() : "null context"; }
 
 int infdev_sm_count(infdev_ctx* ctx) { return ctx->sms; }
+
+uint64_t infdev_launch_count(infdev_ctx* ctx) { return ctx->launches.load(); }
 
 void* infdev_alloc(infdev_ctx* ctx, size_t bytes, int hostVisible) {
   Bind bind(ctx);
@@ -274,6 +278,7 @@ int infdev_dequant(infdev_ctx* ctx, int type, const void* blocks, int64_t count,
   Bind bind(ctx);
   if (type != INFDEV_Q4_K && type != INFDEV_Q6_K)
     return fail(ctx, INFDEV_E_ARGUMENT, "dequant: type must be Q4_K or Q6_K");
+  ctx->launches += 1;
   return check(ctx, infdev::dequant_launch(type, blocks, count, out, ctx->stream), "dequant");
 }
 
@@ -317,6 +322,7 @@ static int linear_common(infdev_ctx* ctx, int type, bool pair, int count, const 
     }
     if (int r = check(ctx, infdev::gemv_launch(type, pair, ctx->xsplit, p, ctx->sms, ctx->stream), "gemv launch"))
       return r;
+    ++ctx->launches;
   }
   return INFDEV_OK;
 }
@@ -339,6 +345,7 @@ int infdev_gate_up(infdev_ctx* ctx, int type, const void* wg, const void* wu, in
 int infdev_gather_tokens(infdev_ctx* ctx, const infdev_query* queries, int queryCount, const int32_t* requestData, uint32_t capacity,
                          const int32_t* proposals, uint32_t mode, int32_t* rowTokens) {
   Bind bind(ctx);
+  ctx->launches += 1;
   return check(ctx, infdev::gather_tokens_launch(queries, queryCount, requestData, capacity, proposals, mode, rowTokens, ctx->stream),
                "gather_tokens");
 }
@@ -347,6 +354,7 @@ int infdev_embedding(infdev_ctx* ctx, int type, const void* table, int64_t k, co
   Bind bind(ctx);
   if ((type != INFDEV_Q4_K && type != INFDEV_Q6_K) || k % 256)
     return fail(ctx, INFDEV_E_ARGUMENT, "embedding: table must be Q4_K or Q6_K with k a multiple of 256");
+  ctx->launches += 1;
   return check(ctx, infdev::embedding_launch(type, table, k, rowTokens, rows, out, ctx->stream), "embedding");
 }
 
@@ -354,12 +362,14 @@ int infdev_rms_norm(infdev_ctx* ctx, const float* x, const float* w, int64_t row
   Bind bind(ctx);
   if (dim % 4 || !aligned16(x) || !aligned16(w) || !aligned16(y))
     return fail(ctx, INFDEV_E_ARGUMENT, "rms_norm: dim must be a multiple of 4 and buffers 16-byte aligned");
+  ctx->launches += 1;
   return check(ctx, infdev::rms_norm_launch(x, w, nullptr, rows, dim, y, ctx->stream), "rms_norm");
 }
 
 int infdev_rms_norm_gather(infdev_ctx* ctx, const float* x, const float* w, const infdev_query* queries, int queryCount, int64_t count, float* y) {
   Bind bind(ctx);
   (void)queryCount;
+  ctx->launches += 1;
   return check(ctx, infdev::rms_norm_launch(x, w, queries, count, 4096, y, ctx->stream), "rms_norm_gather");
 }
 
@@ -372,6 +382,7 @@ int infdev_gdn_prepare(infdev_ctx* ctx, const float* x, const float* mixed, cons
   (void)queryCount;
   if (stateOffset % 16 || stateBytes % 16)
     return fail(ctx, INFDEV_E_ARGUMENT, "gdn_prepare: state offsets must be multiples of 16 bytes");
+  ctx->launches += 2;
   return check(ctx,
                infdev::gdn_prepare_launch(x, mixed, wBeta, wAlpha, ssmA, ssmDt, convWeight, queries, rows, stateOffset, stateBytes, q, k, v, beta, g,
                                           ctx->stream),
@@ -383,6 +394,7 @@ int infdev_delta_rule(infdev_ctx* ctx, const float* q, const float* k, const flo
   Bind bind(ctx);
   if (stateOffset % 16 || stateBytes % 16)
     return fail(ctx, INFDEV_E_ARGUMENT, "delta_rule: state offsets must be multiples of 16 bytes");
+  ctx->launches += 1;
   return check(ctx, infdev::delta_rule_launch(q, k, v, g, beta, z, normWeight, queries, queryCount, stateOffset, stateBytes, out, ctx->stream),
                "delta_rule");
 }
@@ -409,6 +421,7 @@ int infdev_attention_prepare(infdev_ctx* ctx, const float* qg, const float* k, c
   (void)queryCount;
   if (blockTokens <= 0 || blockTokens % 16)
     return fail(ctx, INFDEV_E_ARGUMENT, "attention: blockTokens must be a positive multiple of 16");
+  ctx->launches += 1;
   return check(ctx,
                infdev::attention_prepare_launch(qg, k, v, qNorm, kNorm, rope, queries, table, tableStride, blockTokens, rows, q, cacheK, cacheV,
                                                 ctx->stream),
@@ -424,6 +437,7 @@ int infdev_attention(infdev_ctx* ctx, const float* q, const float* qg, const voi
   (void)queryCount;
   if (blockTokens <= 0 || blockTokens % 16 || maxSplits < 1 || maxSplits > 64)
     return fail(ctx, INFDEV_E_ARGUMENT, "attention: blockTokens must be a multiple of 16 and maxSplits in 1..64");
+  ctx->launches += 2;
   return check(ctx,
                infdev::attention_launch(q, qg, cacheK, cacheV, queries, table, tableStride, blockTokens, rows, maxSplits, partials, out, ctx->stream),
                "attention");
@@ -433,6 +447,7 @@ int infdev_mtp_fuse(infdev_ctx* ctx, const float* embedding, const float* hidden
                     const float* hnorm, int64_t rows, uint32_t mode, uint64_t seedOffset, uint64_t stateBytes, float* y) {
   Bind bind(ctx);
   (void)queryCount;
+  ctx->launches += 1;
   return check(ctx, infdev::mtp_fuse_launch(embedding, hidden, queries, enorm, hnorm, rows, mode, seedOffset, stateBytes, y, ctx->stream),
                "mtp_fuse");
 }
@@ -443,12 +458,14 @@ int infdev_sample(infdev_ctx* ctx, const float* logits, int64_t vocab, infdev_qu
                   int32_t* tokens) {
   Bind bind(ctx);
   (void)queryCount;
+  ctx->launches += 1;
   return check(ctx, infdev::sample_launch(logits, int(vocab), queries, count, mode, tokens, ctx->stream), "sample");
 }
 
 int infdev_pack_queries(infdev_ctx* ctx, const infdev_query* in, int count, int drafting, uint32_t draftWidth, const uint64_t* statePrevious,
                         const uint64_t* stateNext, uint64_t candidateBase, uint64_t stateBytes, infdev_query* out, uint32_t* meta) {
   Bind bind(ctx);
+  ctx->launches += 1;
   return check(ctx,
                infdev::pack_queries_launch(in, count, drafting, draftWidth, statePrevious, stateNext, candidateBase, stateBytes, out, meta, ctx->stream),
                "pack_queries");
@@ -459,6 +476,7 @@ int infdev_verify_drafts(infdev_ctx* ctx, const infdev_query* queries, int count
   Bind bind(ctx);
   if (count > 32)
     return fail(ctx, INFDEV_E_ARGUMENT, "verify_drafts: at most 32 queries");
+  ctx->launches += 1;
   return check(ctx, infdev::verify_drafts_launch(queries, count, sampled, proposed, draftWidth, stops, stopOffsets, accepted, ctx->stream),
                "verify_drafts");
 }
@@ -466,6 +484,7 @@ int infdev_verify_drafts(infdev_ctx* ctx, const infdev_query* queries, int count
 int infdev_commit_states(infdev_ctx* ctx, const infdev_query* queries, int count, const uint32_t* accepted, const uint64_t* stateNext,
                          uint64_t candidateBase, uint64_t stateBytes) {
   Bind bind(ctx);
+  ctx->launches += 1;
   return check(ctx, infdev::commit_states_launch(queries, count, accepted, stateNext, candidateBase, stateBytes, ctx->stream), "commit_states");
 }
 

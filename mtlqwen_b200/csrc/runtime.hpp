@@ -87,7 +87,8 @@ struct Engine {
   uint64_t clock = 0;
   uint64_t parameterCount = 0, modelBytes = 0;
   // step counters for roofline reporting
-  std::atomic_uint64_t passes{0}, passRows{0}, passMicros{0};
+  std::atomic_uint64_t passes{0}, passRows{0}, passMicros{0}, passDeviceNanos{0};
+  void* passEvents[2] = {nullptr, nullptr};  // CUDA events bracketing each pass on the stream
 
   Engine(const std::filesystem::path& weights, uint32_t maxContext, const std::filesystem::path& draftWeights);
   ~Engine();

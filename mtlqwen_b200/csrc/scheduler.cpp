@@ -146,6 +146,8 @@ Engine::Engine(const std::filesystem::path& path, uint32_t context, const std::f
     seeds[i] = ++seed;
   kv = std::make_unique<PagedKV>(device, maxBatchSequences, perSlot, uint32_t(blocks.size()), kvLayers + (drafter == Drafter::mtp ? 1 : 0), blockTokens);
   device.check(device.commit());
+  passEvents[0] = infdev_event_create(device.ctx);
+  passEvents[1] = infdev_event_create(device.ctx);
   worker = std::thread(&Engine::schedule, this);
 }
 
@@ -157,6 +159,8 @@ Engine::~Engine() {
   condition.notify_all();
   if (worker.joinable())
     worker.join();
+  infdev_event_destroy(device.ctx, passEvents[0]);
+  infdev_event_destroy(device.ctx, passEvents[1]);
 }
 
 Sequence::Sequence(Engine& owner, const int32_t* stopTokens, uint32_t stopCount, float samplingTemperature, float samplingTopP, int32_t samplingTopK,
@@ -244,10 +248,13 @@ void Engine::schedule() {
         if (stateBytes * batch.candidateRows > candidateStates.bytes)
           candidateStates = device.empty(stateBytes * batch.candidateRows);
         const auto started = std::chrono::steady_clock::now();
+        infdev_event_record(device.ctx, passEvents[0]);
         if (batch.candidateRows)
           forward(*this, batch, true);
         shape = forward(*this, batch);
+        infdev_event_record(device.ctx, passEvents[1]);
         device.check(device.commit());
+        passDeviceNanos += uint64_t(double(infdev_event_elapsed_ms(device.ctx, passEvents[0], passEvents[1])) * 1.0e6);
         passMicros += uint64_t(std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - started).count());
         passRows += shape.rows;
         ++passes;
@@ -391,6 +398,8 @@ uint64_t infeng_engine_info(infeng_engine* engine, uint32_t field) {
     case 7: return engine->passMicros.load();
     case 8: return engine->targetLayers;
     case 9: return engine->vocab;
+    case 10: return engine->passDeviceNanos.load();
+    case 11: return infdev_launch_count(engine->device.ctx);
     default: return 0;
   }
 }

@@ -40,6 +40,7 @@ def library():
     "infdev_destroy": (None, (vp, )),
     "infdev_error": (ctypes.c_char_p, (vp, )),
     "infdev_sm_count": (i32, (vp, )),
+    "infdev_launch_count": (u64, (vp, )),
     "infdev_alloc": (vp, (vp, ctypes.c_size_t, i32)),
     "infdev_free": (None, (vp, vp)),
     "infdev_upload": (i32, (vp, vp, vp, ctypes.c_size_t)),
@@ -138,6 +139,10 @@ class Device:
   @property
   def sm_count(self):
     return self.lib.infdev_sm_count(self.ctx)
+
+  @property
+  def launch_count(self):
+    return int(self.lib.infdev_launch_count(self.ctx))
 
   def commit(self, timeout_ms=60000):
     self.check(self.lib.infdev_commit(self.ctx, timeout_ms))

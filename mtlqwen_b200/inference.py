@@ -107,9 +107,11 @@ class InferenceEngine:
     return _lib().infeng_engine_info(self.handle, 2)
 
   def step_counters(self):
-    """Passes run, packed rows processed and microseconds spent in passes since the engine started."""
+    """Passes run, packed rows processed, host microseconds and device nanoseconds spent in passes, and kernels
+    launched since the engine started."""
     return {"passes": _lib().infeng_engine_info(self.handle, 5), "rows": _lib().infeng_engine_info(self.handle, 6),
-            "micros": _lib().infeng_engine_info(self.handle, 7)}
+            "micros": _lib().infeng_engine_info(self.handle, 7), "device_ns": _lib().infeng_engine_info(self.handle, 10),
+            "launches": _lib().infeng_engine_info(self.handle, 11)}
 
   def close(self):
     if getattr(self, "handle", 0): _lib().infeng_engine_release(self.handle)
