@@ -87,22 +87,24 @@ class ClockSampler:
             "reasons": sorted(reasons), "samples": len(inside)}
 
 
-def gemv_roofline(device_index):
+def gemv_roofline(device_index, copies=24, replays=20, xsplit=None, qtype=None, n=12288, k=4096, m=8):
   """The dominant kernel alone: Q4_K GEMV 12288 x 4096 with 8 activation rows (BASELINE config 1), launched over a
   ring of 24 distinct weight copies (680 MB, larger than L2) and timed with CUDA events on the launching stream."""
   from mtlqwen_b200 import device as D
   from mtlqwen_b200 import synth
   dev = D.Device(device_index)
-  n, k, m, copies, replays = 12288, 4096, 8, 24, 20
-  base = synth.weight(D.Q4_K, n, k, 1235)
+  qtype = qtype or D.Q4_K
+  if xsplit:
+    dev.set_xsplit(xsplit)
+  base = synth.weight(qtype, n, k, 1235)
   ring = [dev.array(base) for _ in range(copies)]
   x, y = dev.array(synth.activations(m, k, 1236)), dev.empty((m, n))
   for w in ring:  # warm-up, also builds the kernel's attributes before capture
-    dev.linear(D.Q4_K, w, n, k, x, m, y)
+    dev.linear(qtype, w, n, k, x, m, y)
   dev.commit()
   dev.check(dev.lib.infdev_graph_begin(dev.ctx))
   for w in ring:
-    dev.linear(D.Q4_K, w, n, k, x, m, y)
+    dev.linear(qtype, w, n, k, x, m, y)
   graph = dev.lib.infdev_graph_end(dev.ctx)
   for _ in range(10):
     dev.check(dev.lib.infdev_graph_launch(dev.ctx, graph))
@@ -277,7 +279,18 @@ def main():
   parser.add_argument("--steps", type=int, default=128)
   parser.add_argument("--warmup", type=int, default=16)
   parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
+  parser.add_argument("--kernel-only", default=None, choices=("q4k", "q6k"),
+                      help="run only the isolated GEMV kernel on a small ring (the case profiled with ncu) and print its rate")
+  parser.add_argument("--xsplit", type=int, default=None, choices=(1, 2))
   args = parser.parse_args()
+  if args.kernel_only:
+    q6 = args.kernel_only == "q6k"
+    n = 65536 if q6 else 12288
+    algorithmic, seconds, launches = gemv_roofline(int(os.environ.get("LOCAL_RANK", 0)), copies=2 if q6 else 8, replays=2, xsplit=args.xsplit,
+                                                   qtype=14 if q6 else 12, n=n)
+    print(json.dumps({"kernel": args.kernel_only, "n": n, "k": 4096, "m": 8, "us_per_launch": seconds * 1e6, "GBs": algorithmic / seconds / 1e9,
+                      "launches": launches}))
+    return
   args.warmup = max(args.warmup, 3)
   rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
   if args.impl == "reference":

@@ -27,16 +27,16 @@
 namespace infdev {
 namespace {
 
-constexpr int kConsumerWarps = 8;
+constexpr int kConsumerWarps = 8;   // one warp per super-block of a stage
 constexpr int kThreads = (kConsumerWarps + 1) * kWarp;
 constexpr int kChunkBlocks = 16;   // super-blocks of K staged per pass (4096 values)
-constexpr int kStageBlocks = 8;    // super-blocks per ring stage (one per consumer warp)
-constexpr int kStages = 3;
-constexpr int kTileRows = 16;
+constexpr int kStageBlocks = kGemvStageBlocks;  // super-blocks per ring stage (one per consumer warp)
+constexpr int kMaxStages = 8;
+constexpr int kTileRows = kGemvTileRows;
 
 struct Q4K {
   static constexpr int kBlockBytes = 144;
-  static constexpr int kRowStride = kStageBlocks * kBlockBytes + 64;  // == 64 mod 128: conflict-free 16-byte reads
+  static constexpr int kRowStride = kStageBlocks * kBlockBytes;  // rows of a TMA box are dense in shared memory
   static constexpr bool kMinTerm = true;
   static constexpr int kStageBytes = kTileRows * kRowStride;
 };
@@ -49,15 +49,27 @@ struct Q6K {
 };
 
 struct Smem {
-  uint64_t full[kStages], empty[kStages];
+  uint64_t full[kMaxStages], empty[kMaxStages];
   int abort;
 };
+constexpr int kControlBytes = 256;
+static_assert(sizeof(Smem) <= kControlBytes, "control block overlaps the activation fragments");
 
-template <class Q, int NMAT, int XSPLIT> constexpr size_t smem_bytes() {
+template <class Q, int NMAT, int XSPLIT> constexpr size_t fixed_bytes() {
   size_t frag = size_t(kChunkBlocks) * 16 * 32 * 8 * XSPLIT;
   size_t sums = Q::kMinTerm ? size_t(kChunkBlocks) * 32 * 8 : 0;
   size_t partial = size_t(2) * NMAT * kConsumerWarps * 128 * 4;
-  return 128 + frag + sums + partial + size_t(kStages) * Q::kStageBytes;
+  return kControlBytes + frag + sums + partial;
+}
+
+// As many ring stages as fit beside the fragments in the 227 KB a CTA may use.
+template <class Q, int NMAT, int XSPLIT> constexpr int stage_count() {
+  int stages = int((size_t(227) * 1024 - fixed_bytes<Q, NMAT, XSPLIT>()) / Q::kStageBytes);
+  return stages > kMaxStages ? kMaxStages : stages;
+}
+
+template <class Q, int NMAT, int XSPLIT> constexpr size_t smem_bytes() {
+  return fixed_bytes<Q, NMAT, XSPLIT>() + size_t(stage_count<Q, NMAT, XSPLIT>()) * Q::kStageBytes;
 }
 
 __device__ __forceinline__ uint32_t lds_u32_unaligned(const uint8_t* p) {
@@ -70,15 +82,12 @@ __device__ __forceinline__ uint32_t lds_u32_unaligned(const uint8_t* p) {
 // 16*(c%2) + [0,16) , high nibbles the same + 32; GGUF layout as read by dequant_tile,
 // quant_linear.metal:39-46). MMA i = (chunk select, word j, nibble h) consumes bytes 0..3 of word j.
 template <int XSPLIT>
-__device__ __forceinline__ void q4k_unit(const uint8_t* pA, const uint8_t* pB, int lane, const uint2* xhi, const uint2* xlo, const uint2* xsum,
-                                         float (&total)[4]) {
+__device__ __forceinline__ void q4k_unit(const uint8_t* pA, const uint8_t* pB, int lane, int cs, const uint2* xhi, const uint2* xlo,
+                                         const uint2* xsum, float (&total)[4]) {
   const int t = lane & 3;
   const uint4 hA = *reinterpret_cast<const uint4*>(pA), hB = *reinterpret_cast<const uint4*>(pB);
-  uint4 qA[2], qB[2];
-  qA[0] = *reinterpret_cast<const uint4*>(pA + 16 + 16 * t);
-  qA[1] = *reinterpret_cast<const uint4*>(pA + 80 + 16 * t);
-  qB[0] = *reinterpret_cast<const uint4*>(pB + 16 + 16 * t);
-  qB[1] = *reinterpret_cast<const uint4*>(pB + 80 + 16 * t);
+  // This warp's half of the unit: quant chunk t + 4*cs of both rows.
+  const uint4 qA = *reinterpret_cast<const uint4*>(pA + 16 + 64 * cs + 16 * t), qB = *reinterpret_cast<const uint4*>(pB + 16 + 64 * cs + 16 * t);
   // 6-bit scales / mins of the 8 sub-blocks, four per word (scale_min_k4, quant_linear.metal:12-20).
   const uint32_t scA[2] = {hA.y & 0x3f3f3f3fu, (hA.w & 0x0f0f0f0fu) | ((hA.y >> 2) & 0x30303030u)};
   const uint32_t mnA[2] = {hA.z & 0x3f3f3f3fu, ((hA.w >> 4) & 0x0f0f0f0fu) | ((hA.z >> 2) & 0x30303030u)};
@@ -86,22 +95,27 @@ __device__ __forceinline__ void q4k_unit(const uint8_t* pA, const uint8_t* pB, i
   const uint32_t mnB[2] = {hB.z & 0x3f3f3f3fu, ((hB.w >> 4) & 0x0f0f0f0fu) | ((hB.z >> 2) & 0x30303030u)};
   const int shift = (t >> 1) * 16;
   constexpr uint32_t k1024 = 0x64006400u, kNeg1024 = 0xE400E400u, kSixteenth = 0x2C002C00u, kNeg64 = 0xD400D400u;
-  float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+  // Independent accumulator chains: consecutive MMAs never wait on each other's results.
+  float acc[8][4];
 #pragma unroll
-  for (int cs = 0; cs < 2; ++cs) {
+  for (int c = 0; c < 8; ++c)
+    acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f;
+  {
     // Sub-blocks of chunk t+4cs: low nibbles -> 2*(c/2), high -> 2*(c/2)+1; their scales are bytes
     // 2*(t/2), 2*(t/2)+1 of the cs-th scale word.
-    const uint32_t pairA = (scA[cs] >> shift) & 0xffffu, pairB = (scB[cs] >> shift) & 0xffffu;
+    const uint32_t pairA = ((cs ? scA[1] : scA[0]) >> shift) & 0xffffu, pairB = ((cs ? scB[1] : scB[0]) >> shift) & 0xffffu;
     const uint32_t sLA = hsub2_u32(__byte_perm(pairA, 0x64u, 0x4040), k1024), sHA = hsub2_u32(__byte_perm(pairA, 0x64u, 0x4141), k1024);
     const uint32_t sLB = hsub2_u32(__byte_perm(pairB, 0x64u, 0x4040), k1024), sHB = hsub2_u32(__byte_perm(pairB, 0x64u, 0x4141), k1024);
     const uint32_t nLA = hmul2_u32(sLA, kNeg1024), nLB = hmul2_u32(sLB, kNeg1024);
     const uint32_t mHA = hmul2_u32(sHA, kSixteenth), mHB = hmul2_u32(sHB, kSixteenth);
     const uint32_t nHA = hmul2_u32(sHA, kNeg64), nHB = hmul2_u32(sHB, kNeg64);
-    const uint32_t wordsA[4] = {qA[cs].x, qA[cs].y, qA[cs].z, qA[cs].w}, wordsB[4] = {qB[cs].x, qB[cs].y, qB[cs].z, qB[cs].w};
+    const uint32_t wordsA[4] = {qA.x, qA.y, qA.z, qA.w}, wordsB[4] = {qB.x, qB.y, qB.z, qB.w};
+    xhi += cs * 8 * 32;  // fragments of MMAs 8*cs .. 8*cs+7
+    xlo += cs * 8 * 32;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const uint32_t wA = wordsA[j], wB = wordsB[j], vA = wA >> 8, vB = wB >> 8;
-      const int i = (cs * 4 + j) * 2;
+      const int i = j * 2;
       uint32_t a[4];
       // low nibbles: (1024 + q) * sc - 1024 * sc, exact in fp16
       a[0] = hfma2_u32((wA & 0x000f000fu) | k1024, sLA, nLA);
@@ -110,10 +124,10 @@ __device__ __forceinline__ void q4k_unit(const uint8_t* pA, const uint8_t* pB, i
       a[3] = hfma2_u32((vB & 0x000f000fu) | k1024, sLB, nLB);
       const int at = (lane + j) & 31;
       uint2 b = xhi[i * 32 + at];
-      mma_16816(acc0, a, b.x, b.y);
+      mma_16816(acc[i & 7], a, b.x, b.y);
       if (XSPLIT == 2) {
         b = xlo[i * 32 + at];
-        mma_16816(acc0, a, b.x, b.y);
+        mma_16816(acc[i & 7], a, b.x, b.y);
       }
       // high nibbles in place: (1024 + 16 q) * sc/16 - 64 * sc
       a[0] = hfma2_u32((wA & 0x00f000f0u) | k1024, mHA, nHA);
@@ -121,17 +135,17 @@ __device__ __forceinline__ void q4k_unit(const uint8_t* pA, const uint8_t* pB, i
       a[2] = hfma2_u32((vA & 0x00f000f0u) | k1024, mHA, nHA);
       a[3] = hfma2_u32((vB & 0x00f000f0u) | k1024, mHB, nHB);
       b = xhi[(i + 1) * 32 + at];
-      mma_16816(acc1, a, b.x, b.y);
+      mma_16816(acc[(i + 1) & 7], a, b.x, b.y);
       if (XSPLIT == 2) {
         b = xlo[(i + 1) * 32 + at];
-        mma_16816(acc1, a, b.x, b.y);
+        mma_16816(acc[(i + 1) & 7], a, b.x, b.y);
       }
     }
   }
   // min term: sum_j m_j * (sum of the activations of sub-block j); k 0..7 carry the hi half of the sums,
   // k 8..15 the lo half, against the same mins.
   float accm[4] = {0.f, 0.f, 0.f, 0.f};
-  {
+  if (cs == 0) {
     const uint32_t wordA = (t & 2) ? mnA[1] : mnA[0], wordB = (t & 2) ? mnB[1] : mnB[0];
     const uint32_t pA2 = (wordA >> ((t & 1) * 16)) & 0xffffu, pB2 = (wordB >> ((t & 1) * 16)) & 0xffffu;
     uint32_t a[4];
@@ -141,10 +155,14 @@ __device__ __forceinline__ void q4k_unit(const uint8_t* pA, const uint8_t* pB, i
     mma_16816(accm, a, b.x, b.y);
   }
   const float2 dA = __half22float2(*reinterpret_cast<const __half2*>(&hA.x)), dB = __half22float2(*reinterpret_cast<const __half2*>(&hB.x));
-  total[0] += dA.x * (acc0[0] + acc1[0]) - dA.y * accm[0];
-  total[1] += dA.x * (acc0[1] + acc1[1]) - dA.y * accm[1];
-  total[2] += dB.x * (acc0[2] + acc1[2]) - dB.y * accm[2];
-  total[3] += dB.x * (acc0[3] + acc1[3]) - dB.y * accm[3];
+  float sum[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e)
+    sum[e] = ((acc[0][e] + acc[1][e]) + (acc[2][e] + acc[3][e])) + ((acc[4][e] + acc[5][e]) + (acc[6][e] + acc[7][e]));
+  total[0] += dA.x * sum[0] - dA.y * accm[0];
+  total[1] += dA.x * sum[1] - dA.y * accm[1];
+  total[2] += dB.x * sum[2] - dB.y * accm[2];
+  total[3] += dB.x * sum[3] - dB.y * accm[3];
 }
 
 // ---- Q6_K: one 16-row x 256-k unit -------------------------------------------------------------
@@ -153,12 +171,11 @@ __device__ __forceinline__ void q4k_unit(const uint8_t* pA, const uint8_t* pB, i
 // in qh[32*hh + l] >> 2s, and scale sc[r/16]. MMA gi covers elements [16gi, 16gi+16); lane t supplies
 // elements 16gi + 4t + {0,1,2,3}. Blocks are only 2-byte aligned, so words are fetched as two halves.
 template <int XSPLIT>
-__device__ __forceinline__ void q6k_unit(const uint8_t* pA, const uint8_t* pB, int lane, const uint2* xhi, const uint2* xlo, float (&total)[4]) {
+__device__ __forceinline__ void q6k_unit(const uint8_t* pA, const uint8_t* pB, int lane, int hh, const uint2* xhi, const uint2* xlo,
+                                         float (&total)[4]) {
   const int t = lane & 3;
   const float dA = load_half_bits(pA + 208), dB = load_half_bits(pB + 208);
   constexpr uint32_t k1056 = 0x64206420u;
-#pragma unroll
-  for (int hh = 0; hh < 2; ++hh)
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       const uint32_t hiA = lds_u32_unaligned(pA + 128 + 32 * hh + 16 * u + 4 * t), hiB = lds_u32_unaligned(pB + 128 + 32 * hh + 16 * u + 4 * t);
@@ -200,9 +217,10 @@ __device__ __forceinline__ int find_segment(const GemvParams& p, int tile) {
 }
 
 template <class Q, int NMAT, int XSPLIT> __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant__ GemvParams p) {
+  constexpr int kStages = stage_count<Q, NMAT, XSPLIT>();
   extern __shared__ __align__(128) uint8_t smemRaw[];
   Smem& ctl = *reinterpret_cast<Smem*>(smemRaw);
-  uint2* fragHi = reinterpret_cast<uint2*>(smemRaw + 128);
+  uint2* fragHi = reinterpret_cast<uint2*>(smemRaw + kControlBytes);
   uint2* fragLo = fragHi + (XSPLIT == 2 ? kChunkBlocks * 16 * 32 : 0);
   uint2* fragSum = fragHi + kChunkBlocks * 16 * 32 * XSPLIT;
   float* partial = reinterpret_cast<float*>(fragSum + (Q::kMinTerm ? kChunkBlocks * 32 : 0));
@@ -231,10 +249,9 @@ template <class Q, int NMAT, int XSPLIT> __global__ void __launch_bounds__(kThre
       const int chunkBlocks = min(kChunkBlocks, blocksPerRow - chunk * kChunkBlocks);
       const int groups = (chunkBlocks + kStageBlocks - 1) / kStageBlocks;
       for (int tile = blockIdx.x; tile < p.tiles && !*abortFlag; tile += gridDim.x) {
-        const GemvSeg& seg = p.seg[find_segment(p, tile)];
-        const size_t row0 = size_t(tile - seg.tile0) * kTileRows;
+        const int segment = find_segment(p, tile);
+        const size_t row0 = size_t(tile - p.seg[segment].tile0) * kTileRows;
         for (int mat = 0; mat < NMAT; ++mat) {
-          const uint8_t* w = mat ? seg.w2 : seg.w;
           for (int grp = 0; grp < groups; ++grp, ++it) {
             const uint32_t slot = it % kStages, round = it / kStages;
             bool ok = true;
@@ -248,14 +265,14 @@ template <class Q, int NMAT, int XSPLIT> __global__ void __launch_bounds__(kThre
               }
               break;
             }
-            const int count = min(kStageBlocks, chunkBlocks - grp * kStageBlocks);
-            const uint32_t bytes = uint32_t(count) * Q::kBlockBytes;
-            if (lane == 0)
-              mbar_arrive_expect_tx(&ctl.full[slot], bytes * kTileRows);
+            // One tiled copy moves the whole 16-row x 8-super-block slab; columns past the end of a row are zero-filled
+            // and still counted, so the transaction size is always the full box.
+            if (lane == 0) {
+              mbar_arrive_expect_tx(&ctl.full[slot], uint32_t(Q::kStageBytes));
+              tma_load_2d(ring + size_t(slot) * Q::kStageBytes, &p.map[segment][mat], (chunk * (kChunkBlocks / kStageBlocks) + grp) * Q::kBlockBytes,
+                          int(row0), &ctl.full[slot]);
+            }
             __syncwarp();
-            if (lane < kTileRows)
-              bulk_load(ring + size_t(slot) * Q::kStageBytes + lane * Q::kRowStride,
-                        w + (row0 + lane) * rowBytes + size_t(chunk * kChunkBlocks + grp * kStageBlocks) * Q::kBlockBytes, bytes, &ctl.full[slot]);
           }
         }
       }
@@ -344,11 +361,15 @@ template <class Q, int NMAT, int XSPLIT> __global__ void __launch_bounds__(kThre
           if (warp < count && !(p.debug & 2)) {
             const uint8_t* base = ring + size_t(slot) * Q::kStageBytes + warp * Q::kBlockBytes;
             const int sb = grp * kStageBlocks + warp;
-            if (Q::kMinTerm)
-              q4k_unit<XSPLIT>(base + g * Q::kRowStride, base + (g + 8) * Q::kRowStride, lane, fragHi + sb * 512, fragLo + sb * 512, fragSum + sb * 32,
-                               total[mat]);
-            else
-              q6k_unit<XSPLIT>(base + g * Q::kRowStride, base + (g + 8) * Q::kRowStride, lane, fragHi + sb * 512, fragLo + sb * 512, total[mat]);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              if (Q::kMinTerm)
+                q4k_unit<XSPLIT>(base + g * Q::kRowStride, base + (g + 8) * Q::kRowStride, lane, half, fragHi + sb * 512, fragLo + sb * 512,
+                                 fragSum + sb * 32, total[mat]);
+              else
+                q6k_unit<XSPLIT>(base + g * Q::kRowStride, base + (g + 8) * Q::kRowStride, lane, half, fragHi + sb * 512, fragLo + sb * 512,
+                                 total[mat]);
+            }
           }
           __syncwarp();
           if (lane == 0)

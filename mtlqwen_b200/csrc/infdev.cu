@@ -25,6 +25,7 @@ struct infdev_ctx {
   size_t flushBytes = 0;
   std::mutex mutex;
   std::unordered_map<void*, int> allocations;  // pointer -> hostVisible
+  std::unordered_map<std::string, CUtensorMap> tensorMaps;  // weight matrix -> tiled-TMA descriptor
   std::string error;
 };
 
@@ -47,6 +48,47 @@ struct Bind {  // makes the context's device current for the calling thread
 };
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encoder() {
+  static EncodeTiled function = [] {
+    void* entry = nullptr;
+    cudaDriverEntryPointQueryResult status;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &status) != cudaSuccess || status != cudaDriverEntryPointSuccess)
+      entry = nullptr;
+    return reinterpret_cast<EncodeTiled>(entry);
+  }();
+  return function;
+}
+
+// Descriptor of a packed weight matrix [n][k/256 super-blocks] viewed as 8-byte elements: inner dimension = bytes of a
+// row / 8, outer = n rows; box = 8 super-blocks x 16 rows. Cached per matrix: encoding costs about a microsecond.
+int weight_map(infdev_ctx* ctx, const void* w, int64_t n, int64_t k, int blockBytes, CUtensorMap* out) {
+  const std::string key = std::to_string(reinterpret_cast<uintptr_t>(w)) + ":" + std::to_string(n) + ":" + std::to_string(k) + ":" + std::to_string(blockBytes);
+  std::lock_guard<std::mutex> lock(ctx->mutex);
+  auto found = ctx->tensorMaps.find(key);
+  if (found != ctx->tensorMaps.end()) {
+    *out = found->second;
+    return INFDEV_OK;
+  }
+  EncodeTiled encode = encoder();
+  if (!encode)
+    return fail(ctx, INFDEV_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const uint64_t rowBytes = uint64_t(k / 256) * blockBytes;
+  const cuuint64_t dims[2] = {rowBytes / 8, cuuint64_t(n)}, strides[1] = {rowBytes};
+  const cuuint32_t box[2] = {cuuint32_t(infdev::kGemvStageBlocks * blockBytes / 8), cuuint32_t(infdev::kGemvTileRows)}, elementStrides[2] = {1, 1};
+  CUtensorMap map;
+  const CUresult result = encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(w), dims, strides, box, elementStrides,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (result != CUDA_SUCCESS)
+    return fail(ctx, INFDEV_E_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(int(result)));
+  ctx->tensorMaps.emplace(key, map);
+  *out = map;
+  return INFDEV_OK;
+}
 
 }  // namespace
 
@@ -147,6 +189,7 @@ void infdev_free(infdev_ctx* ctx, void* pointer) {
       return;
     hostVisible = found->second;
     ctx->allocations.erase(found);
+    ctx->tensorMaps.clear();  // descriptors may point into the freed range
   }
   // Work already queued on the stream may still use the buffer.
   cudaStreamSynchronize(ctx->stream);
@@ -305,6 +348,12 @@ static int linear_common(infdev_ctx* ctx, int type, bool pair, int count, const 
       return fail(ctx, INFDEV_E_ARGUMENT, "linear: n must be a positive multiple of 16 and weights 16-byte aligned");
     p.seg[i] = {static_cast<const uint8_t*>(w[i]), pair ? static_cast<const uint8_t*>(w2[i]) : nullptr, y[i], residual ? residual[i] : nullptr,
                 int(n[i]), int(n[i]), tiles};
+    const int blockBytes = type == INFDEV_Q4_K ? 144 : 210;
+    if (int r = weight_map(ctx, w[i], n[i], k, blockBytes, &p.map[i][0]))
+      return r;
+    if (pair)
+      if (int r = weight_map(ctx, w2[i], n[i], k, blockBytes, &p.map[i][1]))
+        return r;
     tiles += int(n[i] / 16);
   }
   p.tiles = tiles;

@@ -1,5 +1,6 @@
 // Internal launch interface between the C-ABI layer (infdev.cu) and the kernel files.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <cstdint>
 
@@ -15,6 +16,9 @@ struct GemvSeg {
 };
 
 struct GemvParams {
+  // Tiled-TMA descriptors of the weight matrices, [segment][matrix of a gate/up pair]: a 2-D view of the packed
+  // rows as 8-byte elements, box = 8 super-blocks x 16 rows.
+  alignas(64) CUtensorMap map[4][2];
   GemvSeg seg[4];
   int nseg, tiles;
   const float* x;  // [m][ldx] fp32, rows 16-byte aligned
@@ -22,6 +26,9 @@ struct GemvParams {
   int* status;
   int debug;  // probe switches: 1 skips activation staging, 2 skips the MMA units
 };
+
+// Box geometry shared by the host encoder and the kernel.
+constexpr int kGemvStageBlocks = 8, kGemvTileRows = 16;
 
 cudaError_t gemv_launch(int type, bool pair, int xsplit, const GemvParams& p, int sms, cudaStream_t stream);
 
