@@ -47,9 +47,9 @@ def ensure_model(path, layers=LAYERS, vocab=VOCAB):
   return path
 
 
-def prompts(vocab=VOCAB):
+def prompts(vocab=VOCAB, longest=4096):
   rng = np.random.default_rng(SEED + 4)
-  lengths = rng.integers(128, 4097, SEQUENCES)
+  lengths = rng.integers(128, longest + 1, SEQUENCES)
   return [[int(t) for t in rng.integers(0, vocab, int(n))] for n in lengths]
 
 
@@ -184,7 +184,7 @@ def run_ours(args, rank, world):
   os.environ.setdefault("INFENG_SEED", str(SEED))
   os.environ["INFENG_DEVICE"] = str(local)
   engine = InferenceEngine(path, max_context=8192)
-  texts = prompts()
+  texts = prompts(longest=args.prompt_max)
   sequences = [engine.sequence() for _ in range(SEQUENCES)]
   warmup, steps = args.warmup, args.steps
   need = warmup + steps + 1
@@ -217,8 +217,14 @@ def run_ours(args, rank, world):
     time.sleep(0.002)
   last = max(range(SEQUENCES), key=lambda i: stamps[i][warmup])
   first_index = len(stamps[last]) - 1  # the pass that just completed
+  if args.ncu_range:  # lets `ncu --profile-from-start off` see only the timed decode passes
+    from mtlqwen_b200 import device as D
+    profiler = D.library().infdev_profiler_range
+    profiler(None, 1)
   while len(stamps[last]) < first_index + steps + 1:
     time.sleep(0.002)
+  if args.ncu_range:
+    profiler(None, 0)
   finished.set()
   for thread in threads:
     thread.join()
@@ -282,6 +288,8 @@ def main():
   parser.add_argument("--kernel-only", default=None, choices=("q4k", "q6k"),
                       help="run only the isolated GEMV kernel on a small ring (the case profiled with ncu) and print its rate")
   parser.add_argument("--xsplit", type=int, default=None, choices=(1, 2))
+  parser.add_argument("--prompt-max", type=int, default=4096, help="upper bound of the ragged prompt lengths (profiling runs use a small one)")
+  parser.add_argument("--ncu-range", action="store_true", help="bracket the timed passes with cudaProfilerStart/Stop")
   args = parser.parse_args()
   if args.kernel_only:
     q6 = args.kernel_only == "q6k"

@@ -75,6 +75,8 @@ int infdev_event_record(infdev_ctx* ctx, void* event);
 float infdev_event_elapsed_ms(infdev_ctx* ctx, void* start, void* stop);
 /* Overwrites `bytes` of scratch (>= L2 size) so the next launch starts with a cold L2. */
 int infdev_flush_l2(infdev_ctx* ctx);
+/* cudaProfilerStart / cudaProfilerStop, so a profiler started with its capture off records only a chosen region. */
+int infdev_profiler_range(infdev_ctx* ctx, int on);
 /* Activation split of the tensor-core GEMV: 2 = hi+lo fp16 (fp32-accurate, default), 1 = hi only. */
 int infdev_set_xsplit(infdev_ctx* ctx, int xsplit);
 /* CUDA-graph capture of a pass on the context's stream (no reference counterpart: Metal re-encodes every

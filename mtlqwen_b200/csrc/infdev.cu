@@ -9,6 +9,7 @@
 #include <mutex>
 #include <string>
 #include <thread>
+#include <cuda_profiler_api.h>
 #include <unordered_map>
 #include <vector>
 #include "kernels.h"
@@ -279,6 +280,11 @@ int infdev_flush_l2(infdev_ctx* ctx) {
       return r;
   }
   return check(ctx, cudaMemsetAsync(ctx->flush, 1, ctx->flushBytes, ctx->stream), "infdev_flush_l2");
+}
+
+int infdev_profiler_range(infdev_ctx* ctx, int on) {  // ctx may be null: the switch is process-wide
+  const cudaError_t e = on ? cudaProfilerStart() : cudaProfilerStop();
+  return ctx ? check(ctx, e, "infdev_profiler_range") : (e == cudaSuccess ? INFDEV_OK : INFDEV_E_CUDA);
 }
 
 int infdev_set_xsplit(infdev_ctx* ctx, int xsplit) {

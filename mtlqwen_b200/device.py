@@ -54,6 +54,7 @@ def library():
     "infdev_event_elapsed_ms": (ctypes.c_float, (vp, vp, vp)),
     "infdev_flush_l2": (i32, (vp, )),
     "infdev_set_xsplit": (i32, (vp, i32)),
+    "infdev_profiler_range": (i32, (vp, i32)),
     "infdev_graph_begin": (i32, (vp, )),
     "infdev_graph_end": (vp, (vp, )),
     "infdev_graph_launch": (i32, (vp, vp)),
