@@ -147,6 +147,16 @@ int infdev_attention(infdev_ctx* ctx, const float* q, const float* qg, const voi
                      int queryCount, int64_t rows, const int32_t* table, int32_t tableStride, int32_t blockTokens, uint32_t maxSplits,
                      float* partials, float* out);
 size_t infdev_attention_scratch_bytes(int64_t rows, uint32_t maxSplits);
+/* No counterpart in the reference. The same attention as infdev_attention for callers that cannot allocate device
+ * memory at all (a server that handed every free byte to its K/V pool at start-up, or a decode loop that must not
+ * make a device-synchronising allocation call): the split-K partials live in an array built into the library
+ * (about 2 MiB per GPU, held until the process exits) instead of a caller buffer, and the call performs no
+ * cudaMalloc / cudaFree. Limits: at most 8 packed rows (one decode step of 8 sequences) and 16 splits per row;
+ * more rows are refused with INFDEV_E_ARGUMENT. The first call on a device looks up the array's device address;
+ * make that call before starting any stream capture. All calls share the one array, so two calls that overlap on
+ * the GPU (different streams or contexts of one process) race; calls on one stream are safe. */
+int infdev_attention_static(infdev_ctx* ctx, const float* q, const float* qg, const void* cacheK, const void* cacheV, const infdev_query* queries,
+                            int queryCount, int64_t rows, const int32_t* table, int32_t tableStride, int32_t blockTokens, float* out);
 
 /* mtp_fuse (native_ops.metal:43-87): y [rows,8192] = [rmsnorm(embedding) * enorm | rmsnorm(h) * hnorm]; h is
  * the slot's stored seed, the previous row's hidden or the same row's hidden by mode (2, 1, 0); mode 1 also

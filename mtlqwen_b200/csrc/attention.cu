@@ -14,6 +14,7 @@
 // row depends only on how many tokens that row attends to, so a sequence gets the same arithmetic whether
 // it runs alone or batched. One CTA serves the four query heads that share a kv head, so K and V are read
 // once per group.
+#include <mutex>
 #include "common.cuh"
 #include "ops.h"
 
@@ -228,5 +229,48 @@ cudaError_t attention_launch(const float* q, const float* qg, const void* cacheK
   attention_reduce_kernel<<<unsigned(rows * kQHeads), 256, 0, stream>>>(partials, qg, queries, maxSplits, out);
   return cudaGetLastError();
 }
+
+// ---- attention without any allocation -------------------------------------------------------------
+// Some users of this library cannot give the attention call a scratch buffer: a serving process that sized its
+// K/V pool to whatever device memory was free at start-up has nothing left for a later cudaMalloc, and a
+// latency-critical decode loop cannot afford an allocation call that synchronises the whole device. For them the
+// split-K partials of up to kStaticRows packed rows live in this file-scope array (about 2 MiB), which every GPU
+// that loads the library keeps until the process exits.
+constexpr int kStaticRows = 8, kStaticSplits = 16;
+static __device__ __align__(256) float staticPartials[size_t(kStaticRows) * kQHeads * kStaticSplits * kPartialStride];
+
+cudaError_t attention_static_launch(const float* q, const float* qg, const void* cacheK, const void* cacheV, const infdev_query* queries,
+                                    const int32_t* table, int tableStride, int blockTokens, int64_t rows, int device, float* out,
+                                    cudaStream_t stream) {
+  // In host code `staticPartials` is only a handle; the kernels need the device address, looked up once per
+  // device (with that device current, which the caller guarantees) and remembered.
+  static std::mutex guard;
+  static float* address[64] = {nullptr};
+  if (device < 0 || device >= 64 || rows > kStaticRows)
+    return cudaErrorInvalidValue;
+  if (rows <= 0)
+    return cudaSuccess;
+  float* partials;
+  {
+    std::lock_guard<std::mutex> lock(guard);
+    if (!address[device]) {
+      void* found = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&found, staticPartials);
+      if (e != cudaSuccess)
+        return e;
+      address[device] = static_cast<float*>(found);
+    }
+    partials = address[device];
+  }
+  // Nothing has to start at zero: the reduction reads exactly the (row, head, split) records that the scan of the
+  // same call wrote; whatever an earlier call left in the array is never read.
+  attention_scan_kernel<<<dim3(kStaticSplits, kKvHeads, unsigned(rows)), 128, 0, stream>>>(q, static_cast<const __half*>(cacheK),
+                                                                                          static_cast<const __half*>(cacheV), queries, table,
+                                                                                          tableStride, blockTokens, kStaticSplits, partials);
+  attention_reduce_kernel<<<unsigned(rows * kQHeads), 256, 0, stream>>>(partials, qg, queries, kStaticSplits, out);
+  return cudaGetLastError();
+}
+
+int attention_static_max_rows() { return kStaticRows; }
 
 }  // namespace infdev

@@ -507,6 +507,20 @@ int infdev_mtp_fuse(infdev_ctx* ctx, const float* embedding, const float* hidden
                "mtp_fuse");
 }
 
+int infdev_attention_static(infdev_ctx* ctx, const float* q, const float* qg, const void* cacheK, const void* cacheV, const infdev_query* queries,
+                            int queryCount, int64_t rows, const int32_t* table, int32_t tableStride, int32_t blockTokens, float* out) {
+  Bind bind(ctx);  // the symbol lookup of the first call on a device needs that device current
+  (void)queryCount;
+  if (blockTokens <= 0 || blockTokens % 16)
+    return fail(ctx, INFDEV_E_ARGUMENT, "attention_static: blockTokens must be a positive multiple of 16");
+  if (rows > infdev::attention_static_max_rows())
+    return fail(ctx, INFDEV_E_ARGUMENT, "attention_static: at most " + std::to_string(infdev::attention_static_max_rows()) +
+                                            " packed rows fit the built-in scratch; use infdev_attention with a caller-provided buffer");
+  ctx->launches += 2;
+  return check(ctx, infdev::attention_static_launch(q, qg, cacheK, cacheV, queries, table, tableStride, blockTokens, rows, ctx->device, out, ctx->stream),
+               "attention_static");
+}
+
 // ---- sampling, packing, verification -----------------------------------------------------------
 
 int infdev_sample(infdev_ctx* ctx, const float* logits, int64_t vocab, infdev_query* queries, int queryCount, int64_t count, uint32_t mode,

@@ -26,6 +26,10 @@ cudaError_t attention_prepare_launch(const float* qg, const float* rawK, const f
 cudaError_t attention_launch(const float* q, const float* qg, const void* cacheK, const void* cacheV, const infdev_query* queries,
                              const int32_t* table, int tableStride, int blockTokens, int64_t rows, uint32_t maxSplits, float* partials, float* out,
                              cudaStream_t stream);
+cudaError_t attention_static_launch(const float* q, const float* qg, const void* cacheK, const void* cacheV, const infdev_query* queries,
+                                    const int32_t* table, int tableStride, int blockTokens, int64_t rows, int device, float* out,
+                                    cudaStream_t stream);
+int attention_static_max_rows();
 cudaError_t sample_launch(const float* logits, int vocab, infdev_query* queries, int64_t count, uint32_t mode, int32_t* tokens,
                           cudaStream_t stream);
 cudaError_t pack_queries_launch(const infdev_query* in, int count, int drafting, uint32_t draftWidth, const uint64_t* statePrevious,

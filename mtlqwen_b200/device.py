@@ -73,6 +73,7 @@ def library():
     "infdev_attention_prepare": (i32, (vp, f32p, f32p, f32p, f32p, f32p, f32p, vp, i32, i64, vp, i32, i32, f32p, vp, vp)),
     "infdev_attention": (i32, (vp, f32p, f32p, vp, vp, vp, i32, i64, vp, i32, i32, u32, f32p, f32p)),
     "infdev_attention_scratch_bytes": (ctypes.c_size_t, (i64, u32)),
+    "infdev_attention_static": (i32, (vp, f32p, f32p, vp, vp, vp, i32, i64, vp, i32, i32, f32p)),
     "infdev_mtp_fuse": (i32, (vp, f32p, f32p, vp, i32, f32p, f32p, i64, u32, u64, u64, f32p)),
     "infdev_sample": (i32, (vp, f32p, i64, vp, i32, i64, u32, vp)),
     "infdev_pack_queries": (i32, (vp, vp, i32, i32, u32, vp, vp, u64, u64, vp, vp)),
