@@ -244,15 +244,12 @@ def run_ours(args, rank, world):
   peak, peak_kind = measured_peak()
 
   # whole job = all replicas; time = max over ranks
-  totals = [rows, tokens, launches]
-  worst = [device_seconds, wall]
+  from mtlqwen_b200 import replicas
+  total_rows, worst_device = replicas.combine(dist, rows, device_seconds)
+  total_tokens, worst_wall = replicas.combine(dist, tokens, wall)
+  total_launches, _ = replicas.combine(dist, launches, 0.0)
+  totals, worst = [total_rows, total_tokens, total_launches], [worst_device, worst_wall]
   if dist:
-    import torch
-    t = torch.tensor(totals, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.SUM)
-    w = torch.tensor(worst, dtype=torch.float64)
-    dist.all_reduce(w, op=dist.ReduceOp.MAX)
-    totals, worst = t.tolist(), w.tolist()
     dist.barrier()
   if rank != 0:
     return
