@@ -16,7 +16,9 @@
 #include "ops.h"
 
 struct infdev_ctx {
-  int device = 0, sms = 0, xsplit = 2, debug = 0;
+  int device = 0, sms = 0, xsplit = 2, debug = 0, umma = 0;
+  void* ummaActs = nullptr;  // prepared activations + sums for the tcgen05 path (K up to 16384)
+  float* ummaSums = nullptr;
   std::atomic<uint64_t> launches{0};  // kernels launched through this context
   cudaStream_t stream = nullptr;
   cudaEvent_t done = nullptr;
@@ -65,9 +67,10 @@ EncodeTiled encoder() {
 }
 
 // Descriptor of a packed weight matrix [n][k/256 super-blocks] viewed as 8-byte elements: inner dimension = bytes of a
-// row / 8, outer = n rows; box = 8 super-blocks x 16 rows. Cached per matrix: encoding costs about a microsecond.
-int weight_map(infdev_ctx* ctx, const void* w, int64_t n, int64_t k, int blockBytes, CUtensorMap* out) {
-  const std::string key = std::to_string(reinterpret_cast<uintptr_t>(w)) + ":" + std::to_string(n) + ":" + std::to_string(k) + ":" + std::to_string(blockBytes);
+// row / 8, outer = n rows; box = boxBlocks super-blocks x boxRows rows. Cached per matrix: encoding costs about a microsecond.
+int weight_map(infdev_ctx* ctx, const void* w, int64_t n, int64_t k, int blockBytes, int boxBlocks, int boxRows, CUtensorMap* out) {
+  const std::string key = std::to_string(reinterpret_cast<uintptr_t>(w)) + ":" + std::to_string(n) + ":" + std::to_string(k) + ":" + std::to_string(blockBytes) + ":" +
+                          std::to_string(boxBlocks) + ":" + std::to_string(boxRows);
   std::lock_guard<std::mutex> lock(ctx->mutex);
   auto found = ctx->tensorMaps.find(key);
   if (found != ctx->tensorMaps.end()) {
@@ -79,7 +82,7 @@ int weight_map(infdev_ctx* ctx, const void* w, int64_t n, int64_t k, int blockBy
     return fail(ctx, INFDEV_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   const uint64_t rowBytes = uint64_t(k / 256) * blockBytes;
   const cuuint64_t dims[2] = {rowBytes / 8, cuuint64_t(n)}, strides[1] = {rowBytes};
-  const cuuint32_t box[2] = {cuuint32_t(infdev::kGemvStageBlocks * blockBytes / 8), cuuint32_t(infdev::kGemvTileRows)}, elementStrides[2] = {1, 1};
+  const cuuint32_t box[2] = {cuuint32_t(boxBlocks * blockBytes / 8), cuuint32_t(boxRows)}, elementStrides[2] = {1, 1};
   CUtensorMap map;
   const CUresult result = encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(w), dims, strides, box, elementStrides,
                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -121,10 +124,14 @@ infdev_ctx* infdev_create(int device, char* error) {
     ctx->xsplit = std::atoi(env) == 1 ? 1 : 2;
   if (const char* env = std::getenv("INFENG_GEMV_DEBUG"))
     ctx->debug = std::atoi(env);
+  if (const char* env = std::getenv("INFENG_UMMA"))
+    ctx->umma = std::atoi(env);
   if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess ||
       (e = cudaEventCreateWithFlags(&ctx->done, cudaEventDisableTiming)) != cudaSuccess ||
       (e = cudaMalloc(reinterpret_cast<void**>(&ctx->status), sizeof(int))) != cudaSuccess ||
       (e = cudaMemset(ctx->status, 0, sizeof(int))) != cudaSuccess ||
+      (e = cudaMalloc(&ctx->ummaActs, size_t(64) * infdev::kUmmaActBytesPerBlock)) != cudaSuccess ||
+      (e = cudaMalloc(reinterpret_cast<void**>(&ctx->ummaSums), size_t(64) * 64 * sizeof(float))) != cudaSuccess ||
       (e = cudaHostAlloc(reinterpret_cast<void**>(&ctx->statusHost), sizeof(int), cudaHostAllocDefault)) != cudaSuccess) {
     std::string text = std::string("context setup: ") + cudaGetErrorString(e);
     delete ctx;
@@ -144,6 +151,8 @@ void infdev_destroy(infdev_ctx* ctx) {
   if (ctx->flush)
     cudaFree(ctx->flush);
   cudaFree(ctx->status);
+  cudaFree(ctx->ummaActs);
+  cudaFree(ctx->ummaSums);
   cudaFreeHost(ctx->statusHost);
   cudaEventDestroy(ctx->done);
   cudaStreamDestroy(ctx->stream);
@@ -287,6 +296,11 @@ int infdev_profiler_range(infdev_ctx* ctx, int on) {  // ctx may be null: the sw
   return ctx ? check(ctx, e, "infdev_profiler_range") : (e == cudaSuccess ? INFDEV_OK : INFDEV_E_CUDA);
 }
 
+int infdev_set_umma(infdev_ctx* ctx, int enabled) {
+  ctx->umma = enabled != 0;
+  return INFDEV_OK;
+}
+
 int infdev_set_xsplit(infdev_ctx* ctx, int xsplit) {
   if (xsplit != 1 && xsplit != 2)
     return fail(ctx, INFDEV_E_ARGUMENT, "xsplit must be 1 or 2");
@@ -346,6 +360,42 @@ static int linear_common(infdev_ctx* ctx, int type, bool pair, int count, const 
     return fail(ctx, INFDEV_E_ARGUMENT, "gate_up: k must not exceed 4096");
   if (!aligned16(x) || (k % 4))
     return fail(ctx, INFDEV_E_ARGUMENT, "linear: activations must be 16-byte aligned");
+  bool umma = ctx->umma && type == INFDEV_Q4_K && k % 2048 == 0 && k <= 16384;
+  for (int i = 0; i < count; ++i)
+    umma = umma && n[i] > 0 && n[i] % infdev::kUmmaTileRows == 0 && aligned16(w[i]) && (!pair || aligned16(w2[i]));
+  if (umma) {
+    // tcgen05 path: rows per tile 128, accumulators in tensor memory
+    infdev::UmmaParams u{};
+    u.nseg = count;
+    int tiles = 0;
+    for (int i = 0; i < count; ++i) {
+      u.seg[i] = {static_cast<const uint8_t*>(w[i]), pair ? static_cast<const uint8_t*>(w2[i]) : nullptr, y[i], residual ? residual[i] : nullptr,
+                  int(n[i]), int(n[i]), tiles};
+      if (int r = weight_map(ctx, w[i], n[i], k, 144, 1, infdev::kUmmaTileRows, &u.map[i][0]))
+        return r;
+      if (pair)
+        if (int r = weight_map(ctx, w2[i], n[i], k, 144, 1, infdev::kUmmaTileRows, &u.map[i][1]))
+          return r;
+      tiles += int(n[i] / infdev::kUmmaTileRows);
+    }
+    u.tiles = tiles;
+    u.k = int(k);
+    u.acts = static_cast<const uint8_t*>(ctx->ummaActs);
+    u.actSums = ctx->ummaSums;
+    u.status = ctx->status;
+    u.debug = ctx->debug;
+    for (int64_t row = 0; row < m; row += 8) {
+      u.m = int(m - row < 8 ? m - row : 8);
+      for (int i = 0; i < count; ++i) {
+        u.seg[i].y = y[i] + row * n[i];
+        u.seg[i].res = residual && residual[i] ? residual[i] + row * n[i] : nullptr;
+      }
+      if (int r = check(ctx, infdev::umma_launch(pair, u, x + row * k, int(k), ctx->sms, ctx->stream), "umma launch"))
+        return r;
+      ctx->launches += 2;
+    }
+    return INFDEV_OK;
+  }
   infdev::GemvParams p{};
   p.nseg = count;
   int tiles = 0;
@@ -355,10 +405,10 @@ static int linear_common(infdev_ctx* ctx, int type, bool pair, int count, const 
     p.seg[i] = {static_cast<const uint8_t*>(w[i]), pair ? static_cast<const uint8_t*>(w2[i]) : nullptr, y[i], residual ? residual[i] : nullptr,
                 int(n[i]), int(n[i]), tiles};
     const int blockBytes = type == INFDEV_Q4_K ? 144 : 210;
-    if (int r = weight_map(ctx, w[i], n[i], k, blockBytes, &p.map[i][0]))
+    if (int r = weight_map(ctx, w[i], n[i], k, blockBytes, infdev::kGemvStageBlocks, infdev::kGemvTileRows, &p.map[i][0]))
       return r;
     if (pair)
-      if (int r = weight_map(ctx, w2[i], n[i], k, blockBytes, &p.map[i][1]))
+      if (int r = weight_map(ctx, w2[i], n[i], k, blockBytes, infdev::kGemvStageBlocks, infdev::kGemvTileRows, &p.map[i][1]))
         return r;
     tiles += int(n[i] / 16);
   }

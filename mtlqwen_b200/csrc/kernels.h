@@ -30,6 +30,22 @@ struct GemvParams {
 // Box geometry shared by the host encoder and the kernel.
 constexpr int kGemvStageBlocks = 8, kGemvTileRows = 16;
 
+// ---- tcgen05 path (umma.cu) ----
+constexpr int kUmmaTileRows = 128, kUmmaActBytesPerBlock = 16 * 2 * 16 * 16 * 2;
+
+struct UmmaParams {
+  alignas(64) CUtensorMap map[4][2];  // box = one super-block (18 x 8 bytes) x 128 rows
+  GemvSeg seg[4];
+  int nseg, tiles;  // tiles of 128 rows
+  int m, k;
+  const uint8_t* acts;   // prepared activations: k/256 blocks of kUmmaActBytesPerBlock
+  const float* actSums;  // [k/256][8 sub-blocks][8 rows]
+  int* status;
+  int debug;  // probe switches: 1 no MMA issue, 2 no dequant arithmetic, 4 no prepare kernel
+};
+
+cudaError_t umma_launch(bool pair, const UmmaParams& p, const float* x, int ldx, int sms, cudaStream_t stream);
+
 cudaError_t gemv_launch(int type, bool pair, int xsplit, const GemvParams& p, int sms, cudaStream_t stream);
 
 }  // namespace infdev

@@ -1,0 +1,401 @@
+// Q4_K linear on the 5th-generation tensor cores (tcgen05) with TMEM operands.
+//
+// Replaces, for weight matrices whose row count is a multiple of 128 and whose K is a multiple of 2048, the
+// decode GEMVs linear_decode_q4_k[_add] (quant_linear.metal:245-327) and mlp_gate_up_q4_k_decode
+// (fused_kernels.metal:11-78). The mma.sync kernel in gemv.cu is bound by its instruction count (fragment
+// loads, HMMA issue, per-lane scale selection, cross-warp reduction); here
+//   * one thread owns one weight row: it reads the row's 144-byte super-block from a TMA-filled slab,
+//     builds the exact integers sc*q as fp16 pairs (one LOP3 + one HFMA2 per two weights, scales held as
+//     per-thread scalars) and writes them to tensor memory with tcgen05.st;
+//   * tcgen05.mma (kind::f16, M = 128 weight rows, N = 16 activation columns, K = 16) takes A from TMEM and
+//     B, the activations, from shared memory through a matrix descriptor. The activations were split
+//     hi + lo into fp16 beforehand (umma_prepare_kernel), already laid out as canonical no-swizzle K-major
+//     core matrices under the same K permutation that the nibble extraction produces;
+//   * every super-block accumulates into its own 16 TMEM columns, so the epilogue applies the fp32
+//     super-block scale d exactly: y = sum_sb d_sb * D_sb - dmin_sb * sum_j m_j * xsum_j, the latter added up
+//     on the CUDA cores by the row's thread;
+//   * accumulators are double-buffered per 8-super-block chunk, so the epilogue of one chunk overlaps the
+//     MMAs of the next.
+// Warp roles: 0 = TMA producer, 1 = MMA issuer (owns the TMEM allocation), 4..11 = dequant (two groups of
+// four, one TMEM lane quadrant each), 12..15 = epilogue. Every mbarrier wait is bounded; on a timeout the
+// kernel raises an abort flag, records a status code, and every role leaves its loops.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace infdev {
+namespace {
+
+constexpr int kRows = kUmmaTileRows;  // weight rows per tile = TMEM lanes
+constexpr int kActs = 16;             // MMA N: 8 activation rows padded to 16
+constexpr int kChunkSb = 8;           // super-blocks per accumulator buffer
+constexpr int kSlabBytes = kRows * 144;                  // 18,432
+constexpr int kActBytesPerSb = kUmmaActBytesPerBlock;    // 16 k-steps x (hi, lo) x [16 x 16] fp16 = 16,384
+constexpr int kStageBytes = kSlabBytes + kActBytesPerSb;  // 34,816
+constexpr int kStages = 5;
+constexpr int kThreads = 512;
+constexpr int kTmemCols = 512;
+constexpr uint32_t kColA = 0, kColD = 256;  // A: 2 x 128 columns; D: 2 x (8 super-blocks x 16 columns)
+
+struct Control {
+  uint64_t full[kStages], slotFree[kStages], aReady[2], aFree[2], dReady[2], dFree[2];
+  uint32_t tmemBase;
+  int abort;
+};
+constexpr int kControlBytes = 256;
+static_assert(sizeof(Control) <= kControlBytes, "control block too large");
+constexpr int kScaleBytes = 2 * kChunkSb * kRows * 4;  // d of every (buffer, super-block, row): 8,192
+constexpr int kMinBytes = 2 * 2 * kRows * 8 * 4;       // min-term partials [buffer][group][row][8]: 16,384
+constexpr size_t kSmemBytes = 1024 + kControlBytes + kScaleBytes + kMinBytes + size_t(kStages) * kStageBytes;
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(columns) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t base, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// D[128 x 16] (+)= A[128 x 16] (TMEM) * B[16 x 16] (shared memory descriptor)
+__device__ __forceinline__ void umma_ts(uint32_t d, uint32_t a, uint64_t bDesc, uint32_t iDesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(d),
+      "r"(a), "l"(bDesc), "r"(iDesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// 32 lanes x 32 consecutive columns, one 32-bit value per (lane, column)
+__device__ __forceinline__ void tmem_store32(uint32_t address, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+      "%28,%29,%30,%31,%32};" ::"r"(address),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]),
+      "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]),
+      "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_load8(uint32_t address, float (&v)[8]) {
+  uint32_t r[8];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(address)
+               : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major, no-swizzle operand: 8-row x 16-byte core matrices, the two K halves
+// `leading` bytes apart, successive 8-row groups `stride` bytes apart (descriptor version 1 = Blackwell).
+__device__ __forceinline__ uint64_t smem_descriptor(uint32_t address, uint32_t leading, uint32_t stride) {
+  return uint64_t((address & 0x3FFFFu) >> 4) | (uint64_t(leading >> 4) << 16) | (uint64_t(stride >> 4) << 32) | (uint64_t(1) << 46);
+}
+
+// kind::f16 instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = 16, M = 128.
+constexpr uint32_t kInstruction = (1u << 4) | (uint32_t(kActs >> 3) << 17) | (uint32_t(kRows >> 4) << 24);
+
+template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_constant__ UmmaParams p) {
+  extern __shared__ uint8_t smemRaw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
+  Control& ctl = *reinterpret_cast<Control*>(smem);
+  float* dScale = reinterpret_cast<float*>(smem + kControlBytes);                 // [2][8][128]
+  float* minPart = reinterpret_cast<float*>(smem + kControlBytes + kScaleBytes);  // [2][2][128][8]
+  uint8_t* ring = smem + kControlBytes + kScaleBytes + kMinBytes;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int chunks = p.k / (256 * kChunkSb);
+  volatile int* abortFlag = &ctl.abort;
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&ctl.full[s], 1);
+      mbar_init(&ctl.slotFree[s], 5);  // four dequant warps + the MMA commit
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&ctl.aReady[b], 4);
+      mbar_init(&ctl.aFree[b], 1);
+      mbar_init(&ctl.dReady[b], 1);
+      mbar_init(&ctl.dFree[b], 4);
+    }
+    ctl.abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1)
+    tmem_alloc(&ctl.tmemBase, kTmemCols);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = ctl.tmemBase;
+
+  if (warp == 0) {
+    // ---------------- producer: one weight slab + its activation fragments per super-block ----------------
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x) {
+      int segment = 0;
+      while (segment + 1 < p.nseg && tile >= p.seg[segment + 1].tile0)
+        ++segment;
+      const int row0 = (tile - p.seg[segment].tile0) * kRows;
+      for (int mat = 0; mat < NMAT && ok; ++mat)
+        for (int sb = 0; sb < chunks * kChunkSb && ok; ++sb, ++it) {
+          const uint32_t slot = it % kStages, round = it / kStages;
+          if (lane == 0) {
+            if (round > 0)
+              ok = mbar_wait_bounded(&ctl.slotFree[slot], (round - 1) & 1, abortFlag);
+            if (ok) {
+              uint8_t* stage = ring + size_t(slot) * kStageBytes;
+              mbar_arrive_expect_tx(&ctl.full[slot], kStageBytes);
+              tma_load_2d(stage, &p.map[segment][mat], sb * 18, row0, &ctl.full[slot]);
+              bulk_load(stage + kSlabBytes, p.acts + size_t(sb) * kActBytesPerSb, kActBytesPerSb, &ctl.full[slot]);
+            } else {
+              *abortFlag = 1;
+              atomicExch(p.status, kStatusBarrierTimeout);
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+        }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (lane 0) ----------------
+    if (lane == 0) {
+      uint32_t it = 0, unit = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x)
+        for (int mat = 0; mat < NMAT && ok; ++mat)
+          for (int chunk = 0; chunk < chunks && ok; ++chunk, ++unit) {
+            const uint32_t buffer = unit & 1;
+            if (unit >= 2)
+              ok = mbar_wait_bounded(&ctl.dFree[buffer], ((unit >> 1) - 1) & 1, abortFlag);
+            for (int j = 0; j < kChunkSb && ok; ++j, ++it) {
+              const uint32_t slot = it % kStages, aBuffer = it & 1;
+              ok = mbar_wait_bounded(&ctl.aReady[aBuffer], (it >> 1) & 1, abortFlag);
+              if (!ok)
+                break;
+              fence_after_sync();
+              const uint32_t actBase = smem_u32(ring + size_t(slot) * kStageBytes + kSlabBytes);
+              const uint32_t dColumn = tmem + kColD + buffer * (kChunkSb * kActs) + j * kActs;
+              if (!(p.debug & 1))
+#pragma unroll
+              for (int step = 0; step < 16; ++step) {
+                const uint32_t aColumn = tmem + kColA + aBuffer * 128 + step * 8;
+                umma_ts(dColumn, aColumn, smem_descriptor(actBase + (step * 2) * 512, 128, 256), kInstruction, step != 0);
+                umma_ts(dColumn, aColumn, smem_descriptor(actBase + (step * 2 + 1) * 512, 128, 256), kInstruction, 1);
+              }
+              umma_commit(&ctl.aFree[aBuffer]);
+              umma_commit(&ctl.slotFree[slot]);
+              if (j == kChunkSb - 1)
+                umma_commit(&ctl.dReady[buffer]);
+            }
+          }
+      if (!ok) {
+        *abortFlag = 1;
+        atomicExch(p.status, kStatusBarrierTimeout);
+      }
+    }
+  } else if (warp >= 4 && warp < 12) {
+    // ---------------- dequant: thread = weight row; group g takes the super-blocks with (index & 1) == g ----------------
+    const int group = (warp - 4) >> 2, quadrant = warp & 3, row = quadrant * 32 + lane;
+    constexpr uint32_t k1024 = 0x64006400u, kNeg1024 = 0xE400E400u, kSixteenth = 0x2C002C00u, kNeg64 = 0xD400D400u;
+    uint32_t it = 0, unit = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x)
+      for (int mat = 0; mat < NMAT && ok; ++mat)
+        for (int chunk = 0; chunk < chunks && ok; ++chunk, ++unit) {
+          const uint32_t buffer = unit & 1;
+          // the epilogue of the unit that last used this accumulator buffer also read its scale / min tables
+          if (unit >= 2)
+            ok = mbar_wait_bounded(&ctl.dFree[buffer], ((unit >> 1) - 1) & 1, abortFlag);
+          float minAcc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int j = 0; j < kChunkSb && ok; ++j, ++it) {
+            if ((it & 1) != uint32_t(group))
+              continue;
+            const uint32_t slot = it % kStages, round = it / kStages;
+            ok = mbar_wait_bounded(&ctl.full[slot], round & 1, abortFlag);
+            if (ok && it >= 2)
+              ok = mbar_wait_bounded(&ctl.aFree[it & 1], ((it >> 1) - 1) & 1, abortFlag);
+            if (!ok)
+              break;
+            fence_after_sync();
+            const uint8_t* block = ring + size_t(slot) * kStageBytes + row * 144;
+            const uint4 header = *reinterpret_cast<const uint4*>(block);
+            const float2 dm = __half22float2(*reinterpret_cast<const __half2*>(&header.x));
+            // 6-bit scales / mins, four per word (scale_min_k4, quant_linear.metal:12-20)
+            const uint32_t scales[2] = {header.y & 0x3f3f3f3fu, (header.w & 0x0f0f0f0fu) | ((header.y >> 2) & 0x30303030u)};
+            const uint32_t mins[2] = {header.z & 0x3f3f3f3fu, ((header.w >> 4) & 0x0f0f0f0fu) | ((header.z >> 2) & 0x30303030u)};
+            dScale[(buffer * kChunkSb + j) * kRows + row] = dm.x;
+            {  // min term: dmin * sum_sub m_sub * (sum of the 32 activations of the sub-block), for 8 activation rows
+              const float* sums = p.actSums + size_t(chunk * kChunkSb + j) * 64;  // [8 sub-blocks][8 rows]
+#pragma unroll
+              for (int sub = 0; sub < 8; ++sub) {
+                const float m = dm.y * float((mins[sub >> 2] >> (8 * (sub & 3))) & 0xffu);
+                const float4 lo = __ldg(reinterpret_cast<const float4*>(sums + sub * 8)), hi = __ldg(reinterpret_cast<const float4*>(sums + sub * 8 + 4));
+                minAcc[0] = fmaf(m, lo.x, minAcc[0]), minAcc[1] = fmaf(m, lo.y, minAcc[1]), minAcc[2] = fmaf(m, lo.z, minAcc[2]);
+                minAcc[3] = fmaf(m, lo.w, minAcc[3]), minAcc[4] = fmaf(m, hi.x, minAcc[4]), minAcc[5] = fmaf(m, hi.y, minAcc[5]);
+                minAcc[6] = fmaf(m, hi.z, minAcc[6]), minAcc[7] = fmaf(m, hi.w, minAcc[7]);
+              }
+              float4* mine = reinterpret_cast<float4*>(minPart + ((buffer * 2 + group) * kRows + row) * 8);
+              mine[0] = make_float4(minAcc[0], minAcc[1], minAcc[2], minAcc[3]);  // running total: final after the group's last super-block
+              mine[1] = make_float4(minAcc[4], minAcc[5], minAcc[6], minAcc[7]);
+            }
+            const uint32_t aAddress = tmem + (uint32_t(quadrant * 32) << 16) + kColA + (it & 1) * 128;
+            if (!(p.debug & 2))
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              // 32 quant bytes: low nibbles belong to sub-block 2t, high nibbles to sub-block 2t+1
+              const uint32_t pair = (scales[t >> 1] >> (16 * (t & 1))) & 0xffffu;
+              const uint32_t sL = hsub2_u32(__byte_perm(pair, 0x64u, 0x4040), k1024), sH = hsub2_u32(__byte_perm(pair, 0x64u, 0x4141), k1024);
+              const uint32_t nL = hmul2_u32(sL, kNeg1024), mH = hmul2_u32(sH, kSixteenth), nH = hmul2_u32(sH, kNeg64);
+              const uint4 q0 = *reinterpret_cast<const uint4*>(block + 16 + 32 * t), q1 = *reinterpret_cast<const uint4*>(block + 32 + 32 * t);
+              const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+              uint32_t v[32];
+#pragma unroll
+              for (int w = 0; w < 8; ++w) {
+                const uint32_t a = words[w], b = a >> 8;
+                v[2 * w] = hfma2_u32((a & 0x000f000fu) | k1024, sL, nL);           // (1024 + q) * sc - 1024 sc: bytes 0, 2, low nibble
+                v[2 * w + 1] = hfma2_u32((b & 0x000f000fu) | k1024, sL, nL);       // bytes 1, 3, low nibble
+                v[16 + 2 * w] = hfma2_u32((a & 0x00f000f0u) | k1024, mH, nH);      // (1024 + 16 q) * sc/16 - 64 sc: bytes 0, 2, high nibble
+                v[16 + 2 * w + 1] = hfma2_u32((b & 0x00f000f0u) | k1024, mH, nH);  // bytes 1, 3, high nibble
+              }
+              tmem_store32(aAddress + 32 * t, v);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+              mbar_arrive(&ctl.aReady[it & 1]);
+              mbar_arrive(&ctl.slotFree[slot]);
+            }
+          }
+        }
+    if (!ok && lane == 0) {
+      *abortFlag = 1;
+      atomicExch(p.status, kStatusBarrierTimeout);
+    }
+  } else if (warp >= 12) {
+    // ---------------- epilogue: thread = weight row ----------------
+    const int quadrant = warp & 3, row = quadrant * 32 + lane;
+    uint32_t unit = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x) {
+      int segment = 0;
+      while (segment + 1 < p.nseg && tile >= p.seg[segment + 1].tile0)
+        ++segment;
+      const GemvSeg& seg = p.seg[segment];
+      const size_t column = size_t(tile - seg.tile0) * kRows + row;
+      float total[NMAT][8];
+#pragma unroll
+      for (int mat = 0; mat < NMAT; ++mat) {
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+          total[mat][m] = 0.f;
+        for (int chunk = 0; chunk < chunks && ok; ++chunk, ++unit) {
+          const uint32_t buffer = unit & 1;
+          ok = mbar_wait_bounded(&ctl.dReady[buffer], (unit >> 1) & 1, abortFlag);
+          if (!ok)
+            break;
+          fence_after_sync();
+#pragma unroll
+          for (int j = 0; j < kChunkSb; ++j) {
+            float v[8];
+            tmem_load8(tmem + (uint32_t(quadrant * 32) << 16) + kColD + buffer * (kChunkSb * kActs) + j * kActs, v);
+            const float d = dScale[(buffer * kChunkSb + j) * kRows + row];
+#pragma unroll
+            for (int m = 0; m < 8; ++m)
+              total[mat][m] = fmaf(d, v[m], total[mat][m]);
+          }
+#pragma unroll
+          for (int g = 0; g < 2; ++g) {
+            const float4* part = reinterpret_cast<const float4*>(minPart + ((buffer * 2 + g) * kRows + row) * 8);
+            const float4 lo = part[0], hi = part[1];
+            total[mat][0] -= lo.x, total[mat][1] -= lo.y, total[mat][2] -= lo.z, total[mat][3] -= lo.w;
+            total[mat][4] -= hi.x, total[mat][5] -= hi.y, total[mat][6] -= hi.z, total[mat][7] -= hi.w;
+          }
+          fence_before_sync();
+          __syncwarp();
+          if (lane == 0)
+            mbar_arrive(&ctl.dFree[buffer]);
+        }
+      }
+      if (!ok)
+        break;
+#pragma unroll
+      for (int m = 0; m < 8; ++m)
+        if (m < p.m) {
+          const size_t at = size_t(m) * seg.ldy + column;
+          float value = NMAT == 2 ? silu_f(total[0][m]) * total[NMAT - 1][m] : total[0][m];
+          if (NMAT == 1 && seg.res)
+            value += seg.res[at];
+          seg.y[at] = value;
+        }
+    }
+    if (!ok && lane == 0) {
+      *abortFlag = 1;
+      atomicExch(p.status, kStatusBarrierTimeout);
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1)
+    tmem_dealloc(tmem, kTmemCols);
+}
+
+// Splits up to 8 activation rows into hi + lo fp16 and writes them, per 256-wide super-block, as the B operand of
+// the kernel above: [16 k-steps][hi, lo][2 row groups][2 K halves][8 rows][8 values]. K inside a step follows the
+// order in which the dequantiser emits weights: step s covers quant bytes of 64-group t = s / 4, nibble side
+// (s / 2) % 2, words 4 * (s % 2) .. +3; TMEM column c of a step holds the nibbles of bytes (c % 2, c % 2 + 2) of word c / 2.
+// Also writes the per-sub-block activation sums [super-block][8 sub-blocks][8 rows] used by the min term.
+// grid = k / 256 super-blocks, 256 threads.
+__global__ void __launch_bounds__(256) umma_prepare_kernel(const float* x, int ldx, int m, __half* acts, float* sums) {
+  const int sb = blockIdx.x, tid = threadIdx.x;
+  const int step = tid >> 4, kk = tid & 15;  // this thread's (k-step, position inside the step)
+  const int t = step >> 2, side = (step >> 1) & 1, half = step & 1, c = kk >> 1, upper = kk & 1;
+  const int word = 4 * half + (c >> 1), byte = (c & 1) + 2 * upper;
+  const int element = 64 * t + 32 * side + 4 * word + byte;
+  __half* out = acts + size_t(sb) * (kActBytesPerSb / 2) + size_t(step) * 2 * 256;
+  const int inner = (kk >> 3) * 64 + (kk & 7);  // K half, then position inside the 16-byte core-matrix row
+#pragma unroll
+  for (int n = 0; n < kActs; ++n) {
+    const float v = n < m ? x[size_t(n) * ldx + size_t(sb) * 256 + element] : 0.f;
+    const __half hi = __float2half_rn(v), lo = __float2half_rn(v - __half2float(hi));
+    const int at = (n >> 3) * 128 + inner + (n & 7) * 8;
+    out[at] = hi;
+    out[256 + at] = lo;
+  }
+  if (tid < 64) {
+    const int sub = tid >> 3, n = tid & 7;
+    float s = 0.f;
+    if (n < m)
+      for (int e = 0; e < 32; ++e)
+        s += x[size_t(n) * ldx + size_t(sb) * 256 + sub * 32 + e];
+    sums[size_t(sb) * 64 + tid] = s;
+  }
+}
+
+}  // namespace
+
+cudaError_t umma_launch(bool pair, const UmmaParams& p, const float* x, int ldx, int sms, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(umma_linear_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(umma_linear_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes));
+    if (e != cudaSuccess)
+      return e;
+    configured = true;
+  }
+  if (!(p.debug & 4))
+    umma_prepare_kernel<<<p.k / 256, 256, 0, stream>>>(x, ldx, p.m, reinterpret_cast<__half*>(const_cast<uint8_t*>(p.acts)), const_cast<float*>(p.actSums));
+  const int grid = p.tiles < sms ? p.tiles : sms;
+  if (pair)
+    umma_linear_kernel<2><<<grid, kThreads, kSmemBytes, stream>>>(p);
+  else
+    umma_linear_kernel<1><<<grid, kThreads, kSmemBytes, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace infdev

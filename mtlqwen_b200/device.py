@@ -54,6 +54,7 @@ def library():
     "infdev_event_elapsed_ms": (ctypes.c_float, (vp, vp, vp)),
     "infdev_flush_l2": (i32, (vp, )),
     "infdev_set_xsplit": (i32, (vp, i32)),
+    "infdev_set_umma": (i32, (vp, i32)),
     "infdev_profiler_range": (i32, (vp, i32)),
     "infdev_graph_begin": (i32, (vp, )),
     "infdev_graph_end": (vp, (vp, )),
@@ -174,6 +175,9 @@ class Device:
 
   def flush_l2(self):
     self.check(self.lib.infdev_flush_l2(self.ctx))
+
+  def set_umma(self, enabled):
+    self.check(self.lib.infdev_set_umma(self.ctx, int(enabled)))
 
   def set_xsplit(self, xsplit):
     self.check(self.lib.infdev_set_xsplit(self.ctx, xsplit))
