@@ -77,8 +77,9 @@ float infdev_event_elapsed_ms(infdev_ctx* ctx, void* start, void* stop);
 int infdev_flush_l2(infdev_ctx* ctx);
 /* cudaProfilerStart / cudaProfilerStop, so a profiler started with its capture off records only a chosen region. */
 int infdev_profiler_range(infdev_ctx* ctx, int on);
-/* Chooses between the tcgen05 kernel (1; Q4_K with n % 128 == 0 and k % 2048 == 0) and the mma.sync kernel (0,
- * default) for quantised linears. Environment: INFENG_UMMA. */
+/* Which quantised-linear kernel serves Q4_K matrices with n % 128 == 0 and k % 2048 == 0: 0 = always the mma.sync GEMV,
+ * 1 (default) = the tcgen05 / TMEM GEMM for more than 8 activation rows (prefill, speculative rows) and the GEMV for
+ * decode, 2 = tcgen05 for every row count. Environment: INFENG_UMMA. */
 int infdev_set_umma(infdev_ctx* ctx, int enabled);
 /* Activation split of the tensor-core GEMV: 2 = hi+lo fp16 (fp32-accurate, default), 1 = hi only. */
 int infdev_set_xsplit(infdev_ctx* ctx, int xsplit);

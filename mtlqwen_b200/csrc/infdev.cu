@@ -16,7 +16,7 @@
 #include "ops.h"
 
 struct infdev_ctx {
-  int device = 0, sms = 0, xsplit = 2, debug = 0, umma = 0;
+  int device = 0, sms = 0, xsplit = 2, debug = 0, umma = 1;  // umma: 0 never, 1 for more than 8 rows, 2 always
   void* ummaActs = nullptr;  // prepared activations + sums for the tcgen05 path (K up to 16384)
   float* ummaSums = nullptr;
   std::atomic<uint64_t> launches{0};  // kernels launched through this context
@@ -130,7 +130,7 @@ infdev_ctx* infdev_create(int device, char* error) {
       (e = cudaEventCreateWithFlags(&ctx->done, cudaEventDisableTiming)) != cudaSuccess ||
       (e = cudaMalloc(reinterpret_cast<void**>(&ctx->status), sizeof(int))) != cudaSuccess ||
       (e = cudaMemset(ctx->status, 0, sizeof(int))) != cudaSuccess ||
-      (e = cudaMalloc(&ctx->ummaActs, size_t(64) * infdev::kUmmaActBytesPerBlock)) != cudaSuccess ||
+      (e = cudaMalloc(&ctx->ummaActs, size_t(64) * infdev::kUmmaMaxActBytesPerBlock)) != cudaSuccess ||
       (e = cudaMalloc(reinterpret_cast<void**>(&ctx->ummaSums), size_t(64) * 64 * sizeof(float))) != cudaSuccess ||
       (e = cudaHostAlloc(reinterpret_cast<void**>(&ctx->statusHost), sizeof(int), cudaHostAllocDefault)) != cudaSuccess) {
     std::string text = std::string("context setup: ") + cudaGetErrorString(e);
@@ -297,7 +297,7 @@ int infdev_profiler_range(infdev_ctx* ctx, int on) {  // ctx may be null: the sw
 }
 
 int infdev_set_umma(infdev_ctx* ctx, int enabled) {
-  ctx->umma = enabled != 0;
+  ctx->umma = enabled < 0 ? 0 : enabled > 2 ? 2 : enabled;
   return INFDEV_OK;
 }
 
@@ -360,7 +360,7 @@ static int linear_common(infdev_ctx* ctx, int type, bool pair, int count, const 
     return fail(ctx, INFDEV_E_ARGUMENT, "gate_up: k must not exceed 4096");
   if (!aligned16(x) || (k % 4))
     return fail(ctx, INFDEV_E_ARGUMENT, "linear: activations must be 16-byte aligned");
-  bool umma = ctx->umma && type == INFDEV_Q4_K && k % 2048 == 0 && k <= 16384;
+  bool umma = (ctx->umma == 2 || (ctx->umma == 1 && m > 8)) && type == INFDEV_Q4_K && k % 2048 == 0 && k <= 16384;
   for (int i = 0; i < count; ++i)
     umma = umma && n[i] > 0 && n[i] % infdev::kUmmaTileRows == 0 && aligned16(w[i]) && (!pair || aligned16(w2[i]));
   if (umma) {
@@ -384,8 +384,9 @@ static int linear_common(infdev_ctx* ctx, int type, bool pair, int count, const 
     u.actSums = ctx->ummaSums;
     u.status = ctx->status;
     u.debug = ctx->debug;
-    for (int64_t row = 0; row < m; row += 8) {
-      u.m = int(m - row < 8 ? m - row : 8);
+    const int64_t slice = m <= 8 ? 8 : 128;  // exact decode mode up to 8 rows, fp16-weight GEMM mode up to 128 rows per launch
+    for (int64_t row = 0; row < m; row += slice) {
+      u.m = int(m - row < slice ? m - row : slice);
       for (int i = 0; i < count; ++i) {
         u.seg[i].y = y[i] + row * n[i];
         u.seg[i].res = residual && residual[i] ? residual[i] + row * n[i] : nullptr;

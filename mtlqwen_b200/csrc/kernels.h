@@ -31,7 +31,7 @@ struct GemvParams {
 constexpr int kGemvStageBlocks = 8, kGemvTileRows = 16;
 
 // ---- tcgen05 path (umma.cu) ----
-constexpr int kUmmaTileRows = 128, kUmmaActBytesPerBlock = 16 * 2 * 16 * 16 * 2;
+constexpr int kUmmaTileRows = 128, kUmmaMaxActBytesPerBlock = 16 * 128 * 16 * 2;  // prefill mode: 64 KB of fp16 activations per super-block
 
 struct UmmaParams {
   alignas(64) CUtensorMap map[4][2];  // box = one super-block (18 x 8 bytes) x 128 rows

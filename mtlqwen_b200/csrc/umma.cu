@@ -26,18 +26,25 @@ namespace infdev {
 namespace {
 
 constexpr int kRows = kUmmaTileRows;  // weight rows per tile = TMEM lanes
-constexpr int kActs = 16;             // MMA N: 8 activation rows padded to 16
-constexpr int kChunkSb = 8;           // super-blocks per accumulator buffer
-constexpr int kSlabBytes = kRows * 144;                  // 18,432
-constexpr int kActBytesPerSb = kUmmaActBytesPerBlock;    // 16 k-steps x (hi, lo) x [16 x 16] fp16 = 16,384
-constexpr int kStageBytes = kSlabBytes + kActBytesPerSb;  // 34,816
-constexpr int kStages = 5;
+constexpr int kChunkSb = 8;           // super-blocks per accumulator buffer (decode mode)
+constexpr int kSlabBytes = kRows * 144;  // 18,432
 constexpr int kThreads = 512;
+// Two modes, selected by the MMA N dimension:
+//  NACT = 16  decode: up to 8 activation rows; columns 0..7 carry their fp16 hi halves, columns 8..15 the lo halves, so
+//             one MMA per k-step yields both products. A holds the exact integers sc*q; one accumulator per super-block.
+//  NACT = 128 prefill: up to 128 activation rows in fp16 (hi only); A holds the dequantised weight d*sc*q - dmin*m
+//             rounded to fp16, one accumulator per tile (the GEMM of linear_prefill, quant_linear.metal:151-233).
+template <int NACT> struct Mode {
+  static constexpr int kActBytesPerSb = 16 * NACT * 16 * 2;             // 16 k-steps x [NACT x 16] fp16
+  static constexpr int kStageBytes = kSlabBytes + kActBytesPerSb;      // 26,624 / 83,968
+  static constexpr int kStages = NACT == 16 ? 7 : 2;
+  static constexpr uint32_t kInstruction = (1u << 4) | (uint32_t(NACT >> 3) << 17) | (uint32_t(kRows >> 4) << 24);
+};
 constexpr int kTmemCols = 512;
 constexpr uint32_t kColA = 0, kColD = 256;  // A: 2 x 128 columns; D: 2 x (8 super-blocks x 16 columns)
 
 struct Control {
-  uint64_t full[kStages], slotFree[kStages], aReady[2], aFree[2], dReady[2], dFree[2];
+  uint64_t full[8], slotFree[8], aReady[2], aFree[2], dReady[2], dFree[2];
   uint32_t tmemBase;
   int abort;
 };
@@ -45,7 +52,9 @@ constexpr int kControlBytes = 256;
 static_assert(sizeof(Control) <= kControlBytes, "control block too large");
 constexpr int kScaleBytes = 2 * kChunkSb * kRows * 4;  // d of every (buffer, super-block, row): 8,192
 constexpr int kMinBytes = 2 * 2 * kRows * 8 * 4;       // min-term partials [buffer][group][row][8]: 16,384
-constexpr size_t kSmemBytes = 1024 + kControlBytes + kScaleBytes + kMinBytes + size_t(kStages) * kStageBytes;
+template <int NACT> constexpr size_t smem_bytes() {
+  return 1024 + kControlBytes + kScaleBytes + kMinBytes + size_t(Mode<NACT>::kStages) * Mode<NACT>::kStageBytes;
+}
 
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t columns) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(columns) : "memory");
@@ -59,7 +68,7 @@ __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// D[128 x 16] (+)= A[128 x 16] (TMEM) * B[16 x 16] (shared memory descriptor)
+// D[128 x N] (+)= A[128 x 16] (TMEM) * B[16 x N] (shared memory descriptor)
 __device__ __forceinline__ void umma_ts(uint32_t d, uint32_t a, uint64_t bDesc, uint32_t iDesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
@@ -96,10 +105,12 @@ __device__ __forceinline__ uint64_t smem_descriptor(uint32_t address, uint32_t l
   return uint64_t((address & 0x3FFFFu) >> 4) | (uint64_t(leading >> 4) << 16) | (uint64_t(stride >> 4) << 32) | (uint64_t(1) << 46);
 }
 
-// kind::f16 instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = 16, M = 128.
-constexpr uint32_t kInstruction = (1u << 4) | (uint32_t(kActs >> 3) << 17) | (uint32_t(kRows >> 4) << 24);
+// (Mode<NACT>::kInstruction is the kind::f16 instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, M = 128.)
 
-template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_constant__ UmmaParams p) {
+template <int NMAT, int NACT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_constant__ UmmaParams p) {
+  using M = Mode<NACT>;
+  constexpr bool kDecode = NACT == 16;
+  constexpr int kStages = M::kStages, kStageBytes = M::kStageBytes;
   extern __shared__ uint8_t smemRaw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
   Control& ctl = *reinterpret_cast<Control*>(smem);
@@ -108,7 +119,9 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
   uint8_t* ring = smem + kControlBytes + kScaleBytes + kMinBytes;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int chunks = p.k / (256 * kChunkSb);
+  const int blocksPerRow = p.k / 256;
+  // A "unit" owns one accumulator buffer: 8 super-blocks in decode mode, a whole (tile, matrix) in prefill mode.
+  const int unitsPerMat = kDecode ? blocksPerRow / kChunkSb : 1, blocksPerUnit = kDecode ? kChunkSb : blocksPerRow;
   volatile int* abortFlag = &ctl.abort;
 
   if (tid == 0) {
@@ -142,7 +155,7 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
         ++segment;
       const int row0 = (tile - p.seg[segment].tile0) * kRows;
       for (int mat = 0; mat < NMAT && ok; ++mat)
-        for (int sb = 0; sb < chunks * kChunkSb && ok; ++sb, ++it) {
+        for (int sb = 0; sb < blocksPerRow && ok; ++sb, ++it) {
           const uint32_t slot = it % kStages, round = it / kStages;
           if (lane == 0) {
             if (round > 0)
@@ -151,7 +164,7 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
               uint8_t* stage = ring + size_t(slot) * kStageBytes;
               mbar_arrive_expect_tx(&ctl.full[slot], kStageBytes);
               tma_load_2d(stage, &p.map[segment][mat], sb * 18, row0, &ctl.full[slot]);
-              bulk_load(stage + kSlabBytes, p.acts + size_t(sb) * kActBytesPerSb, kActBytesPerSb, &ctl.full[slot]);
+              bulk_load(stage + kSlabBytes, p.acts + size_t(sb) * M::kActBytesPerSb, M::kActBytesPerSb, &ctl.full[slot]);
             } else {
               *abortFlag = 1;
               atomicExch(p.status, kStatusBarrierTimeout);
@@ -167,28 +180,27 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x)
         for (int mat = 0; mat < NMAT && ok; ++mat)
-          for (int chunk = 0; chunk < chunks && ok; ++chunk, ++unit) {
+          for (int chunk = 0; chunk < unitsPerMat && ok; ++chunk, ++unit) {
             const uint32_t buffer = unit & 1;
             if (unit >= 2)
               ok = mbar_wait_bounded(&ctl.dFree[buffer], ((unit >> 1) - 1) & 1, abortFlag);
-            for (int j = 0; j < kChunkSb && ok; ++j, ++it) {
+            for (int j = 0; j < blocksPerUnit && ok; ++j, ++it) {
               const uint32_t slot = it % kStages, aBuffer = it & 1;
               ok = mbar_wait_bounded(&ctl.aReady[aBuffer], (it >> 1) & 1, abortFlag);
               if (!ok)
                 break;
               fence_after_sync();
               const uint32_t actBase = smem_u32(ring + size_t(slot) * kStageBytes + kSlabBytes);
-              const uint32_t dColumn = tmem + kColD + buffer * (kChunkSb * kActs) + j * kActs;
+              // decode: 16 columns per super-block; prefill: one 128-column accumulator per unit
+              const uint32_t dColumn = tmem + kColD + buffer * 128 + (kDecode ? j * 16 : 0);
               if (!(p.debug & 1))
 #pragma unroll
-              for (int step = 0; step < 16; ++step) {
-                const uint32_t aColumn = tmem + kColA + aBuffer * 128 + step * 8;
-                umma_ts(dColumn, aColumn, smem_descriptor(actBase + (step * 2) * 512, 128, 256), kInstruction, step != 0);
-                umma_ts(dColumn, aColumn, smem_descriptor(actBase + (step * 2 + 1) * 512, 128, 256), kInstruction, 1);
-              }
+                for (int step = 0; step < 16; ++step)
+                  umma_ts(dColumn, tmem + kColA + aBuffer * 128 + step * 8, smem_descriptor(actBase + step * (NACT * 32), 128, 256), M::kInstruction,
+                          kDecode ? step != 0 : (j | step) != 0);
               umma_commit(&ctl.aFree[aBuffer]);
               umma_commit(&ctl.slotFree[slot]);
-              if (j == kChunkSb - 1)
+              if (j == blocksPerUnit - 1)
                 umma_commit(&ctl.dReady[buffer]);
             }
           }
@@ -197,7 +209,8 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
         atomicExch(p.status, kStatusBarrierTimeout);
       }
     }
-  } else if (warp >= 4 && warp < 12) {
+  }
+  else if (warp >= 4 && warp < 12) {
     // ---------------- dequant: thread = weight row; group g takes the super-blocks with (index & 1) == g ----------------
     const int group = (warp - 4) >> 2, quadrant = warp & 3, row = quadrant * 32 + lane;
     constexpr uint32_t k1024 = 0x64006400u, kNeg1024 = 0xE400E400u, kSixteenth = 0x2C002C00u, kNeg64 = 0xD400D400u;
@@ -205,13 +218,13 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x)
       for (int mat = 0; mat < NMAT && ok; ++mat)
-        for (int chunk = 0; chunk < chunks && ok; ++chunk, ++unit) {
+        for (int chunk = 0; chunk < unitsPerMat && ok; ++chunk, ++unit) {
           const uint32_t buffer = unit & 1;
-          // the epilogue of the unit that last used this accumulator buffer also read its scale / min tables
-          if (unit >= 2)
+          // decode: the epilogue of the unit that last used this accumulator buffer also read its scale / min tables
+          if (kDecode && unit >= 2)
             ok = mbar_wait_bounded(&ctl.dFree[buffer], ((unit >> 1) - 1) & 1, abortFlag);
           float minAcc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          for (int j = 0; j < kChunkSb && ok; ++j, ++it) {
+          for (int j = 0; j < blocksPerUnit && ok; ++j, ++it) {
             if ((it & 1) != uint32_t(group))
               continue;
             const uint32_t slot = it % kStages, round = it / kStages;
@@ -227,8 +240,9 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
             // 6-bit scales / mins, four per word (scale_min_k4, quant_linear.metal:12-20)
             const uint32_t scales[2] = {header.y & 0x3f3f3f3fu, (header.w & 0x0f0f0f0fu) | ((header.y >> 2) & 0x30303030u)};
             const uint32_t mins[2] = {header.z & 0x3f3f3f3fu, ((header.w >> 4) & 0x0f0f0f0fu) | ((header.z >> 2) & 0x30303030u)};
-            dScale[(buffer * kChunkSb + j) * kRows + row] = dm.x;
-            {  // min term: dmin * sum_sub m_sub * (sum of the 32 activations of the sub-block), for 8 activation rows
+            if (kDecode) {
+              dScale[(buffer * kChunkSb + j) * kRows + row] = dm.x;
+              // min term: dmin * sum_sub m_sub * (sum of the 32 activations of the sub-block), for 8 activation rows
               const float* sums = p.actSums + size_t(chunk * kChunkSb + j) * 64;  // [8 sub-blocks][8 rows]
 #pragma unroll
               for (int sub = 0; sub < 8; ++sub) {
@@ -245,24 +259,41 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
             const uint32_t aAddress = tmem + (uint32_t(quadrant * 32) << 16) + kColA + (it & 1) * 128;
             if (!(p.debug & 2))
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
-              // 32 quant bytes: low nibbles belong to sub-block 2t, high nibbles to sub-block 2t+1
-              const uint32_t pair = (scales[t >> 1] >> (16 * (t & 1))) & 0xffffu;
-              const uint32_t sL = hsub2_u32(__byte_perm(pair, 0x64u, 0x4040), k1024), sH = hsub2_u32(__byte_perm(pair, 0x64u, 0x4141), k1024);
-              const uint32_t nL = hmul2_u32(sL, kNeg1024), mH = hmul2_u32(sH, kSixteenth), nH = hmul2_u32(sH, kNeg64);
-              const uint4 q0 = *reinterpret_cast<const uint4*>(block + 16 + 32 * t), q1 = *reinterpret_cast<const uint4*>(block + 32 + 32 * t);
-              const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-              uint32_t v[32];
+              for (int t = 0; t < 4; ++t) {
+                // 32 quant bytes: low nibbles belong to sub-block 2t, high nibbles to sub-block 2t+1
+                const uint32_t pair = (scales[t >> 1] >> (16 * (t & 1))) & 0xffffu;
+                const uint4 q0 = *reinterpret_cast<const uint4*>(block + 16 + 32 * t), q1 = *reinterpret_cast<const uint4*>(block + 32 + 32 * t);
+                const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                uint32_t v[32];
+                if (kDecode) {
+                  const uint32_t sL = hsub2_u32(__byte_perm(pair, 0x64u, 0x4040), k1024), sH = hsub2_u32(__byte_perm(pair, 0x64u, 0x4141), k1024);
+                  const uint32_t nL = hmul2_u32(sL, kNeg1024), mH = hmul2_u32(sH, kSixteenth), nH = hmul2_u32(sH, kNeg64);
 #pragma unroll
-              for (int w = 0; w < 8; ++w) {
-                const uint32_t a = words[w], b = a >> 8;
-                v[2 * w] = hfma2_u32((a & 0x000f000fu) | k1024, sL, nL);           // (1024 + q) * sc - 1024 sc: bytes 0, 2, low nibble
-                v[2 * w + 1] = hfma2_u32((b & 0x000f000fu) | k1024, sL, nL);       // bytes 1, 3, low nibble
-                v[16 + 2 * w] = hfma2_u32((a & 0x00f000f0u) | k1024, mH, nH);      // (1024 + 16 q) * sc/16 - 64 sc: bytes 0, 2, high nibble
-                v[16 + 2 * w + 1] = hfma2_u32((b & 0x00f000f0u) | k1024, mH, nH);  // bytes 1, 3, high nibble
+                  for (int w = 0; w < 8; ++w) {
+                    const uint32_t a = words[w], b = a >> 8;
+                    v[2 * w] = hfma2_u32((a & 0x000f000fu) | k1024, sL, nL);           // (1024 + q) * sc - 1024 sc: bytes 0, 2, low nibble
+                    v[2 * w + 1] = hfma2_u32((b & 0x000f000fu) | k1024, sL, nL);       // bytes 1, 3, low nibble
+                    v[16 + 2 * w] = hfma2_u32((a & 0x00f000f0u) | k1024, mH, nH);      // (1024 + 16 q) * sc/16 - 64 sc: bytes 0, 2, high nibble
+                    v[16 + 2 * w + 1] = hfma2_u32((b & 0x00f000f0u) | k1024, mH, nH);  // bytes 1, 3, high nibble
+                  }
+                } else {
+                  // dequantised weight d*sc*q - dmin*m, in fp16: q is made exact first, then one fused multiply-add
+                  const uint32_t minPair = (mins[t >> 1] >> (16 * (t & 1))) & 0xffffu;
+                  const uint32_t sL = pack_half2(dm.x * float(pair & 0xffu), dm.x * float(pair & 0xffu));
+                  const uint32_t sH = pack_half2(dm.x * float(pair >> 8), dm.x * float(pair >> 8));
+                  const uint32_t nL = pack_half2(-dm.y * float(minPair & 0xffu), -dm.y * float(minPair & 0xffu));
+                  const uint32_t nH = pack_half2(-dm.y * float(minPair >> 8), -dm.y * float(minPair >> 8));
+#pragma unroll
+                  for (int w = 0; w < 8; ++w) {
+                    const uint32_t a = words[w];
+                    v[2 * w] = hfma2_u32(hsub2_u32((a & 0x000f000fu) | k1024, k1024), sL, nL);
+                    v[2 * w + 1] = hfma2_u32(hsub2_u32(((a >> 8) & 0x000f000fu) | k1024, k1024), sL, nL);
+                    v[16 + 2 * w] = hfma2_u32(hsub2_u32(((a >> 4) & 0x000f000fu) | k1024, k1024), sH, nH);
+                    v[16 + 2 * w + 1] = hfma2_u32(hsub2_u32(((a >> 12) & 0x000f000fu) | k1024, k1024), sH, nH);
+                  }
+                }
+                tmem_store32(aAddress + 32 * t, v);
               }
-              tmem_store32(aAddress + 32 * t, v);
-            }
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             fence_before_sync();
             __syncwarp();
@@ -276,9 +307,11 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
       *abortFlag = 1;
       atomicExch(p.status, kStatusBarrierTimeout);
     }
-  } else if (warp >= 12) {
+  }
+  else if (warp >= 12) {
     // ---------------- epilogue: thread = weight row ----------------
     const int quadrant = warp & 3, row = quadrant * 32 + lane;
+    const uint32_t laneBase = tmem + (uint32_t(quadrant * 32) << 16) + kColD;
     uint32_t unit = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x) {
@@ -287,33 +320,76 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
         ++segment;
       const GemvSeg& seg = p.seg[segment];
       const size_t column = size_t(tile - seg.tile0) * kRows + row;
-      float total[NMAT][8];
+      if (kDecode) {
+        float total[NMAT][8];
 #pragma unroll
-      for (int mat = 0; mat < NMAT; ++mat) {
+        for (int mat = 0; mat < NMAT; ++mat) {
+#pragma unroll
+          for (int m = 0; m < 8; ++m)
+            total[mat][m] = 0.f;
+          for (int chunk = 0; chunk < unitsPerMat && ok; ++chunk, ++unit) {
+            const uint32_t buffer = unit & 1;
+            ok = mbar_wait_bounded(&ctl.dReady[buffer], (unit >> 1) & 1, abortFlag);
+            if (!ok)
+              break;
+            fence_after_sync();
+#pragma unroll
+            for (int j = 0; j < kChunkSb; ++j) {
+              float hi[8], lo[8];
+              tmem_load8(laneBase + buffer * 128 + j * 16, hi);
+              tmem_load8(laneBase + buffer * 128 + j * 16 + 8, lo);
+              const float d = dScale[(buffer * kChunkSb + j) * kRows + row];
+#pragma unroll
+              for (int m = 0; m < 8; ++m)
+                total[mat][m] = fmaf(d, hi[m] + lo[m], total[mat][m]);
+            }
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+              const float4* part = reinterpret_cast<const float4*>(minPart + ((buffer * 2 + g) * kRows + row) * 8);
+              const float4 a = part[0], b = part[1];
+              total[mat][0] -= a.x, total[mat][1] -= a.y, total[mat][2] -= a.z, total[mat][3] -= a.w;
+              total[mat][4] -= b.x, total[mat][5] -= b.y, total[mat][6] -= b.z, total[mat][7] -= b.w;
+            }
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+              mbar_arrive(&ctl.dFree[buffer]);
+          }
+        }
+        if (!ok)
+          break;
 #pragma unroll
         for (int m = 0; m < 8; ++m)
-          total[mat][m] = 0.f;
-        for (int chunk = 0; chunk < chunks && ok; ++chunk, ++unit) {
+          if (m < p.m) {
+            const size_t at = size_t(m) * seg.ldy + column;
+            float value = NMAT == 2 ? silu_f(total[0][m]) * total[NMAT - 1][m] : total[0][m];
+            if (NMAT == 1 && seg.res)
+              value += seg.res[at];
+            seg.y[at] = value;
+          }
+      } else {
+        for (int mat = 0; mat < NMAT && ok; ++mat, ++unit) {
           const uint32_t buffer = unit & 1;
           ok = mbar_wait_bounded(&ctl.dReady[buffer], (unit >> 1) & 1, abortFlag);
           if (!ok)
             break;
           fence_after_sync();
-#pragma unroll
-          for (int j = 0; j < kChunkSb; ++j) {
+          for (int c = 0; c < NACT / 8; ++c) {
             float v[8];
-            tmem_load8(tmem + (uint32_t(quadrant * 32) << 16) + kColD + buffer * (kChunkSb * kActs) + j * kActs, v);
-            const float d = dScale[(buffer * kChunkSb + j) * kRows + row];
+            tmem_load8(laneBase + buffer * 128 + c * 8, v);
 #pragma unroll
-            for (int m = 0; m < 8; ++m)
-              total[mat][m] = fmaf(d, v[m], total[mat][m]);
-          }
-#pragma unroll
-          for (int g = 0; g < 2; ++g) {
-            const float4* part = reinterpret_cast<const float4*>(minPart + ((buffer * 2 + g) * kRows + row) * 8);
-            const float4 lo = part[0], hi = part[1];
-            total[mat][0] -= lo.x, total[mat][1] -= lo.y, total[mat][2] -= lo.z, total[mat][3] -= lo.w;
-            total[mat][4] -= hi.x, total[mat][5] -= hi.y, total[mat][6] -= hi.z, total[mat][7] -= hi.w;
+            for (int i = 0; i < 8; ++i) {
+              const int m = c * 8 + i;
+              if (m < p.m) {
+                const size_t at = size_t(m) * seg.ldy + column;
+                float value = v[i];
+                if (NMAT == 2)  // the gate half parks in y until the up half arrives (post == 2 epilogue, quant_linear.metal:224-232)
+                  value = mat == 0 ? value : silu_f(seg.y[at]) * value;
+                else if (seg.res)
+                  value += seg.res[at];
+                seg.y[at] = value;
+              }
+            }
           }
           fence_before_sync();
           __syncwarp();
@@ -321,17 +397,6 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
             mbar_arrive(&ctl.dFree[buffer]);
         }
       }
-      if (!ok)
-        break;
-#pragma unroll
-      for (int m = 0; m < 8; ++m)
-        if (m < p.m) {
-          const size_t at = size_t(m) * seg.ldy + column;
-          float value = NMAT == 2 ? silu_f(total[0][m]) * total[NMAT - 1][m] : total[0][m];
-          if (NMAT == 1 && seg.res)
-            value += seg.res[at];
-          seg.y[at] = value;
-        }
     }
     if (!ok && lane == 0) {
       *abortFlag = 1;
@@ -344,58 +409,69 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
     tmem_dealloc(tmem, kTmemCols);
 }
 
-// Splits up to 8 activation rows into hi + lo fp16 and writes them, per 256-wide super-block, as the B operand of
-// the kernel above: [16 k-steps][hi, lo][2 row groups][2 K halves][8 rows][8 values]. K inside a step follows the
-// order in which the dequantiser emits weights: step s covers quant bytes of 64-group t = s / 4, nibble side
-// (s / 2) % 2, words 4 * (s % 2) .. +3; TMEM column c of a step holds the nibbles of bytes (c % 2, c % 2 + 2) of word c / 2.
-// Also writes the per-sub-block activation sums [super-block][8 sub-blocks][8 rows] used by the min term.
+// Lays the activations out as the B operand, per 256-wide super-block: [16 k-steps][NACT/8 row groups][2 K halves][8 rows]
+// [8 values] fp16. K inside a step follows the order in which the dequantiser emits weights: step s covers quant bytes of
+// 64-group t = s / 4, nibble side (s / 2) % 2, words 4 * (s % 2) .. +3; TMEM column c of a step holds the nibbles of bytes
+// (c % 2, c % 2 + 2) of word c / 2. Decode mode (NACT = 16): rows 0..7 are the fp16 hi halves of up to 8 activation rows,
+// rows 8..15 their lo halves (x - hi), and the per-sub-block sums [super-block][8 sub-blocks][8 rows] for the min term
+// are written too. Prefill mode (NACT = 128): rows are up to 128 activation rows rounded to fp16.
 // grid = k / 256 super-blocks, 256 threads.
-__global__ void __launch_bounds__(256) umma_prepare_kernel(const float* x, int ldx, int m, __half* acts, float* sums) {
+template <int NACT> __global__ void __launch_bounds__(256) umma_prepare_kernel(const float* x, int ldx, int m, __half* acts, float* sums) {
   const int sb = blockIdx.x, tid = threadIdx.x;
   const int step = tid >> 4, kk = tid & 15;  // this thread's (k-step, position inside the step)
   const int t = step >> 2, side = (step >> 1) & 1, half = step & 1, c = kk >> 1, upper = kk & 1;
   const int word = 4 * half + (c >> 1), byte = (c & 1) + 2 * upper;
   const int element = 64 * t + 32 * side + 4 * word + byte;
-  __half* out = acts + size_t(sb) * (kActBytesPerSb / 2) + size_t(step) * 2 * 256;
+  __half* out = acts + size_t(sb) * (Mode<NACT>::kActBytesPerSb / 2) + size_t(step) * (NACT * 16);
   const int inner = (kk >> 3) * 64 + (kk & 7);  // K half, then position inside the 16-byte core-matrix row
+  if (NACT == 16) {
 #pragma unroll
-  for (int n = 0; n < kActs; ++n) {
-    const float v = n < m ? x[size_t(n) * ldx + size_t(sb) * 256 + element] : 0.f;
-    const __half hi = __float2half_rn(v), lo = __float2half_rn(v - __half2float(hi));
-    const int at = (n >> 3) * 128 + inner + (n & 7) * 8;
-    out[at] = hi;
-    out[256 + at] = lo;
-  }
-  if (tid < 64) {
-    const int sub = tid >> 3, n = tid & 7;
-    float s = 0.f;
-    if (n < m)
-      for (int e = 0; e < 32; ++e)
-        s += x[size_t(n) * ldx + size_t(sb) * 256 + sub * 32 + e];
-    sums[size_t(sb) * 64 + tid] = s;
+    for (int n = 0; n < 8; ++n) {
+      const float v = n < m ? x[size_t(n) * ldx + size_t(sb) * 256 + element] : 0.f;
+      const __half hi = __float2half_rn(v), lo = __float2half_rn(v - __half2float(hi));
+      out[inner + n * 8] = hi;         // row group 0
+      out[128 + inner + n * 8] = lo;   // row group 1
+    }
+    if (tid < 64) {
+      const int sub = tid >> 3, n = tid & 7;
+      float s = 0.f;
+      if (n < m)
+        for (int e = 0; e < 32; ++e)
+          s += x[size_t(n) * ldx + size_t(sb) * 256 + sub * 32 + e];
+      sums[size_t(sb) * 64 + tid] = s;
+    }
+  } else {
+    for (int n = 0; n < NACT; ++n) {
+      const float v = n < m ? x[size_t(n) * ldx + size_t(sb) * 256 + element] : 0.f;
+      out[(n >> 3) * 128 + inner + (n & 7) * 8] = __float2half_rn(v);
+    }
   }
 }
 
-}  // namespace
-
-cudaError_t umma_launch(bool pair, const UmmaParams& p, const float* x, int ldx, int sms, cudaStream_t stream) {
+template <int NMAT, int NACT> cudaError_t launch_mode(const UmmaParams& p, const float* x, int ldx, int sms, cudaStream_t stream) {
   static bool configured = false;
+  constexpr size_t bytes = smem_bytes<NACT>();
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(umma_linear_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes));
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(umma_linear_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes));
+    const cudaError_t e = cudaFuncSetAttribute(umma_linear_kernel<NMAT, NACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes));
     if (e != cudaSuccess)
       return e;
     configured = true;
   }
   if (!(p.debug & 4))
-    umma_prepare_kernel<<<p.k / 256, 256, 0, stream>>>(x, ldx, p.m, reinterpret_cast<__half*>(const_cast<uint8_t*>(p.acts)), const_cast<float*>(p.actSums));
+    umma_prepare_kernel<NACT><<<p.k / 256, 256, 0, stream>>>(x, ldx, p.m, reinterpret_cast<__half*>(const_cast<uint8_t*>(p.acts)),
+                                                              const_cast<float*>(p.actSums));
   const int grid = p.tiles < sms ? p.tiles : sms;
-  if (pair)
-    umma_linear_kernel<2><<<grid, kThreads, kSmemBytes, stream>>>(p);
-  else
-    umma_linear_kernel<1><<<grid, kThreads, kSmemBytes, stream>>>(p);
+  umma_linear_kernel<NMAT, NACT><<<grid, kThreads, bytes, stream>>>(p);
   return cudaGetLastError();
+}
+
+}  // namespace
+
+// p.m <= 8 runs the exact decode mode, p.m <= 128 the fp16-weight prefill mode.
+cudaError_t umma_launch(bool pair, const UmmaParams& p, const float* x, int ldx, int sms, cudaStream_t stream) {
+  if (p.m <= 8)
+    return pair ? launch_mode<2, 16>(p, x, ldx, sms, stream) : launch_mode<1, 16>(p, x, ldx, sms, stream);
+  return pair ? launch_mode<2, 128>(p, x, ldx, sms, stream) : launch_mode<1, 128>(p, x, ldx, sms, stream);
 }
 
 }  // namespace infdev
