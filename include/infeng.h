@@ -23,7 +23,7 @@ typedef struct infeng_sequence infeng_sequence;
  * receive the message when the call returns NULL. Environment: INFENG_DEVICE (GPU index, default LOCAL_RANK or
  * 0), INFENG_KV_BLOCKS (physical 128-token K/V blocks, default ceil(context/128) as engine.cpp:86),
  * INFENG_DRAFT_WIDTH (MTP proposals per step, default 2 as forward.cpp:139), INFENG_SEED (base of the per-slot
- * sampling seeds, default the clock), INFENG_BLOCK_TOKENS, INFENG_COMMIT_TIMEOUT_MS. */
+ * sampling seeds, default the clock), INFENG_BLOCK_TOKENS, INFENG_COMMIT_TIMEOUT_MS, INFENG_GRAPHS (0 disables CUDA-graph replay of decode passes). */
 infeng_engine* infeng_engine_create(const char* weights, const char* draftWeights, const char* kernels, uint32_t context, char* error);
 /* engine.cpp:251-254: drops one reference; the engine dies with its last sequence. */
 void infeng_engine_release(infeng_engine* engine);

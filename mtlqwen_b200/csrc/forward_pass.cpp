@@ -225,7 +225,7 @@ void Engine::loadModel(const std::filesystem::path& path, const std::filesystem:
   device.check(infdev_rope_table(device.ctx, maxContext, rope.as<float>()));
 }
 
-PassShape forward(Engine& engine, Batch& batch, bool drafting) {
+PassShape forward(Engine& engine, Batch& batch, bool drafting, bool launch) {
   Ops ops(engine);
   PassShape shape;
   // Finish the records on the host exactly as infdev_pack_queries does on the device (forward.cpp:171-191): the
@@ -253,7 +253,7 @@ PassShape forward(Engine& engine, Batch& batch, bool drafting) {
     shape.logits += query.samples;
     shape.rows += query.count;
   }
-  if (!shape.rows)
+  if (!shape.rows || !launch)  // launch == false: a captured graph of this pass shape will be replayed instead
     return shape;
   infdev_ctx* ctx = engine.device.ctx;
   infdev_query* deviceQueries = engine.queryData.as<infdev_query>() + (drafting ? maxBatchSequences : 0);

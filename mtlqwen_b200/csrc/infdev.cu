@@ -29,6 +29,8 @@ struct infdev_ctx {
   std::mutex mutex;
   std::unordered_map<void*, int> allocations;  // pointer -> hostVisible
   std::unordered_map<std::string, CUtensorMap> tensorMaps;  // weight matrix -> tiled-TMA descriptor
+  std::unordered_map<void*, uint64_t> graphLaunches;         // captured graph -> kernels it launches per replay
+  uint64_t captureStart = 0;
   std::string error;
 };
 
@@ -310,6 +312,7 @@ int infdev_set_xsplit(infdev_ctx* ctx, int xsplit) {
 
 int infdev_graph_begin(infdev_ctx* ctx) {
   Bind bind(ctx);
+  ctx->captureStart = ctx->launches.load();
   return check(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal), "infdev_graph_begin");
 }
 
@@ -321,11 +324,16 @@ void* infdev_graph_end(infdev_ctx* ctx) {
     return nullptr;
   const int r = check(ctx, cudaGraphInstantiate(&exec, graph, 0), "cudaGraphInstantiate");
   cudaGraphDestroy(graph);
-  return r == INFDEV_OK ? exec : nullptr;
+  if (r != INFDEV_OK)
+    return nullptr;
+  ctx->graphLaunches[exec] = ctx->launches.load() - ctx->captureStart;  // counted while capturing, not executed yet
+  ctx->launches = ctx->captureStart;
+  return exec;
 }
 
 int infdev_graph_launch(infdev_ctx* ctx, void* graph) {
   Bind bind(ctx);
+  ctx->launches += ctx->graphLaunches[graph];
   return check(ctx, cudaGraphLaunch(static_cast<cudaGraphExec_t>(graph), ctx->stream), "infdev_graph_launch");
 }
 

@@ -89,6 +89,11 @@ struct Engine {
   // step counters for roofline reporting
   std::atomic_uint64_t passes{0}, passRows{0}, passMicros{0}, passDeviceNanos{0};
   void* passEvents[2] = {nullptr, nullptr};  // CUDA events bracketing each pass on the stream
+  // Pure-decode passes (every query one row, nothing speculative) have a fixed launch sequence for a given number of
+  // live sequences; from its second occurrence such a pass is captured once into a CUDA graph and then replayed.
+  void* decodeGraphs[maxBatchSequences + 1] = {};
+  uint32_t decodeSeen[maxBatchSequences + 1] = {};
+  bool useGraphs = true;
 
   Engine(const std::filesystem::path& weights, uint32_t maxContext, const std::filesystem::path& draftWeights);
   ~Engine();
@@ -125,6 +130,6 @@ struct PassShape {
   bool sequential = false, prefill = false;
 };
 
-PassShape forward(Engine& engine, Batch& batch, bool drafting = false);
+PassShape forward(Engine& engine, Batch& batch, bool drafting = false, bool launch = true);
 
 }  // namespace infeng::qwen35

@@ -126,6 +126,7 @@ Engine::Engine(const std::filesystem::path& path, uint32_t context, const std::f
   if (!blockTokens || blockTokens % 16 || checkpointTokens % blockTokens)
     throw std::runtime_error("INFENG_BLOCK_TOKENS must be a multiple of 16 that divides 512");
   device.commitTimeoutMs = environment("INFENG_COMMIT_TIMEOUT_MS", 120000);
+  useGraphs = environment("INFENG_GRAPHS", 1) != 0;
   // The reference sizes the physical pool for one sequence of maximum context (engine.cpp:86); INFENG_KV_BLOCKS overrides.
   const uint32_t perSlot = (context + blockTokens - 1) / blockTokens;
   blocks.resize(environment("INFENG_KV_BLOCKS", perSlot));
@@ -159,6 +160,8 @@ Engine::~Engine() {
   condition.notify_all();
   if (worker.joinable())
     worker.join();
+  for (void* graph : decodeGraphs)
+    infdev_graph_destroy(device.ctx, graph);
   infdev_event_destroy(device.ctx, passEvents[0]);
   infdev_event_destroy(device.ctx, passEvents[1]);
 }
@@ -249,9 +252,24 @@ void Engine::schedule() {
           candidateStates = device.empty(stateBytes * batch.candidateRows);
         const auto started = std::chrono::steady_clock::now();
         infdev_event_record(device.ctx, passEvents[0]);
-        if (batch.candidateRows)
-          forward(*this, batch, true);
-        shape = forward(*this, batch);
+        bool pureDecode = useGraphs && !batch.candidateRows;
+        for (uint32_t i = 0; i < batch.size && pureDecode; ++i)
+          pureDecode = batch.queries[i].count == 1;
+        if (pureDecode && decodeGraphs[batch.size]) {
+          shape = forward(*this, batch, false, false);  // host bookkeeping only
+          device.check(infdev_graph_launch(device.ctx, decodeGraphs[batch.size]));
+        } else if (pureDecode && decodeSeen[batch.size]++ >= 1) {
+          device.check(infdev_graph_begin(device.ctx));
+          shape = forward(*this, batch);
+          decodeGraphs[batch.size] = infdev_graph_end(device.ctx);
+          if (!decodeGraphs[batch.size])
+            throw std::runtime_error(infdev_error(device.ctx));
+          device.check(infdev_graph_launch(device.ctx, decodeGraphs[batch.size]));
+        } else {
+          if (batch.candidateRows)
+            forward(*this, batch, true);
+          shape = forward(*this, batch);
+        }
         infdev_event_record(device.ctx, passEvents[1]);
         device.check(device.commit());
         passDeviceNanos += uint64_t(double(infdev_event_elapsed_ms(device.ctx, passEvents[0], passEvents[1])) * 1.0e6);
