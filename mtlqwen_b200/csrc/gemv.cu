@@ -81,13 +81,24 @@ __device__ __forceinline__ uint32_t lds_u32_unaligned(const uint8_t* p) {
 // t+4 of the super-block (chunk c = bytes [16c,16c+16) of qs: low nibbles are elements 64*(c/2) +
 // 16*(c%2) + [0,16) , high nibbles the same + 32; GGUF layout as read by dequant_tile,
 // quant_linear.metal:39-46). MMA i = (chunk select, word j, nibble h) consumes bytes 0..3 of word j.
+__device__ __forceinline__ uint4 lds128(uint32_t address) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(address));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t address) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(address));
+  return v;
+}
+
+// All operands are 32-bit shared-memory addresses: pA / pB the super-block of rows g and g+8, xhi / xlo the B
+// fragments of this super-block already offset by the lane's rotated slot for j = 0 (slots for j = 1..3 follow from
+// `rot`, the byte offsets of the other three rotations), xsum the lane's min-term fragment.
 template <int XSPLIT>
-__device__ __forceinline__ void q4k_unit(const uint8_t* pA, const uint8_t* pB, int lane, int cs, const uint2* xhi, const uint2* xlo,
-                                         const uint2* xsum, float (&total)[4]) {
-  const int t = lane & 3;
-  const uint4 hA = *reinterpret_cast<const uint4*>(pA), hB = *reinterpret_cast<const uint4*>(pB);
-  // This warp's half of the unit: quant chunk t + 4*cs of both rows.
-  const uint4 qA = *reinterpret_cast<const uint4*>(pA + 16 + 64 * cs + 16 * t), qB = *reinterpret_cast<const uint4*>(pB + 16 + 64 * cs + 16 * t);
+__device__ __forceinline__ void q4k_unit(uint32_t pA, uint32_t pB, int t, uint32_t xhi, uint32_t xlo, const int (&rot)[4], uint32_t xsum,
+                                         float (&total)[4]) {
+  const uint4 hA = lds128(pA), hB = lds128(pB);
   // 6-bit scales / mins of the 8 sub-blocks, four per word (scale_min_k4, quant_linear.metal:12-20).
   const uint32_t scA[2] = {hA.y & 0x3f3f3f3fu, (hA.w & 0x0f0f0f0fu) | ((hA.y >> 2) & 0x30303030u)};
   const uint32_t mnA[2] = {hA.z & 0x3f3f3f3fu, ((hA.w >> 4) & 0x0f0f0f0fu) | ((hA.z >> 2) & 0x30303030u)};
@@ -95,74 +106,70 @@ __device__ __forceinline__ void q4k_unit(const uint8_t* pA, const uint8_t* pB, i
   const uint32_t mnB[2] = {hB.z & 0x3f3f3f3fu, ((hB.w >> 4) & 0x0f0f0f0fu) | ((hB.z >> 2) & 0x30303030u)};
   const int shift = (t >> 1) * 16;
   constexpr uint32_t k1024 = 0x64006400u, kNeg1024 = 0xE400E400u, kSixteenth = 0x2C002C00u, kNeg64 = 0xD400D400u;
-  // Independent accumulator chains: consecutive MMAs never wait on each other's results.
-  float acc[8][4];
+  // Four independent accumulator chains: consecutive MMAs never wait on each other's results.
+  float acc[4][4];
 #pragma unroll
-  for (int c = 0; c < 8; ++c)
+  for (int c = 0; c < 4; ++c)
     acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f;
-  {
-    // Sub-blocks of chunk t+4cs: low nibbles -> 2*(c/2), high -> 2*(c/2)+1; their scales are bytes
-    // 2*(t/2), 2*(t/2)+1 of the cs-th scale word.
-    const uint32_t pairA = ((cs ? scA[1] : scA[0]) >> shift) & 0xffffu, pairB = ((cs ? scB[1] : scB[0]) >> shift) & 0xffffu;
+#pragma unroll
+  for (int cs = 0; cs < 2; ++cs) {
+    // This lane's quant chunk t + 4*cs of both rows. Its low nibbles belong to sub-block 2*(c/2), the high ones to
+    // 2*(c/2)+1; their scales are bytes 2*(t/2), 2*(t/2)+1 of the cs-th scale word.
+    const uint4 qA = lds128(pA + 16 + 64 * cs + 16 * t), qB = lds128(pB + 16 + 64 * cs + 16 * t);
+    const uint32_t pairA = (scA[cs] >> shift) & 0xffffu, pairB = (scB[cs] >> shift) & 0xffffu;
     const uint32_t sLA = hsub2_u32(__byte_perm(pairA, 0x64u, 0x4040), k1024), sHA = hsub2_u32(__byte_perm(pairA, 0x64u, 0x4141), k1024);
     const uint32_t sLB = hsub2_u32(__byte_perm(pairB, 0x64u, 0x4040), k1024), sHB = hsub2_u32(__byte_perm(pairB, 0x64u, 0x4141), k1024);
     const uint32_t nLA = hmul2_u32(sLA, kNeg1024), nLB = hmul2_u32(sLB, kNeg1024);
     const uint32_t mHA = hmul2_u32(sHA, kSixteenth), mHB = hmul2_u32(sHB, kSixteenth);
     const uint32_t nHA = hmul2_u32(sHA, kNeg64), nHB = hmul2_u32(sHB, kNeg64);
     const uint32_t wordsA[4] = {qA.x, qA.y, qA.z, qA.w}, wordsB[4] = {qB.x, qB.y, qB.z, qB.w};
-    xhi += cs * 8 * 32;  // fragments of MMAs 8*cs .. 8*cs+7
-    xlo += cs * 8 * 32;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const uint32_t wA = wordsA[j], wB = wordsB[j], vA = wA >> 8, vB = wB >> 8;
-      const int i = j * 2;
+      const int i = (cs * 4 + j) * 2;          // MMA index of the low-nibble step; i + 1 is the high-nibble step
+      const int at = i * 256 + rot[j];         // byte offset of fragment (i, rotated slot): 32 slots x 8 bytes per MMA
       uint32_t a[4];
       // low nibbles: (1024 + q) * sc - 1024 * sc, exact in fp16
       a[0] = hfma2_u32((wA & 0x000f000fu) | k1024, sLA, nLA);
       a[1] = hfma2_u32((wB & 0x000f000fu) | k1024, sLB, nLB);
       a[2] = hfma2_u32((vA & 0x000f000fu) | k1024, sLA, nLA);
       a[3] = hfma2_u32((vB & 0x000f000fu) | k1024, sLB, nLB);
-      const int at = (lane + j) & 31;
-      uint2 b = xhi[i * 32 + at];
-      mma_16816(acc[i & 7], a, b.x, b.y);
+      uint2 b = lds64(xhi + at);
+      mma_16816(acc[j & 1], a, b.x, b.y);
       if (XSPLIT == 2) {
-        b = xlo[i * 32 + at];
-        mma_16816(acc[i & 7], a, b.x, b.y);
+        b = lds64(xlo + at);
+        mma_16816(acc[j & 1], a, b.x, b.y);
       }
       // high nibbles in place: (1024 + 16 q) * sc/16 - 64 * sc
       a[0] = hfma2_u32((wA & 0x00f000f0u) | k1024, mHA, nHA);
       a[1] = hfma2_u32((wB & 0x00f000f0u) | k1024, mHB, nHB);
       a[2] = hfma2_u32((vA & 0x00f000f0u) | k1024, mHA, nHA);
       a[3] = hfma2_u32((vB & 0x00f000f0u) | k1024, mHB, nHB);
-      b = xhi[(i + 1) * 32 + at];
-      mma_16816(acc[(i + 1) & 7], a, b.x, b.y);
+      b = lds64(xhi + at + 256);
+      mma_16816(acc[2 + (j & 1)], a, b.x, b.y);
       if (XSPLIT == 2) {
-        b = xlo[(i + 1) * 32 + at];
-        mma_16816(acc[(i + 1) & 7], a, b.x, b.y);
+        b = lds64(xlo + at + 256);
+        mma_16816(acc[2 + (j & 1)], a, b.x, b.y);
       }
     }
   }
   // min term: sum_j m_j * (sum of the activations of sub-block j); k 0..7 carry the hi half of the sums,
   // k 8..15 the lo half, against the same mins.
   float accm[4] = {0.f, 0.f, 0.f, 0.f};
-  if (cs == 0) {
+  {
     const uint32_t wordA = (t & 2) ? mnA[1] : mnA[0], wordB = (t & 2) ? mnB[1] : mnB[0];
     const uint32_t pA2 = (wordA >> ((t & 1) * 16)) & 0xffffu, pB2 = (wordB >> ((t & 1) * 16)) & 0xffffu;
     uint32_t a[4];
     a[0] = a[2] = hsub2_u32(__byte_perm(pA2, 0x64u, 0x4140), k1024);
     a[1] = a[3] = hsub2_u32(__byte_perm(pB2, 0x64u, 0x4140), k1024);
-    const uint2 b = xsum[lane];
+    const uint2 b = lds64(xsum);
     mma_16816(accm, a, b.x, b.y);
   }
   const float2 dA = __half22float2(*reinterpret_cast<const __half2*>(&hA.x)), dB = __half22float2(*reinterpret_cast<const __half2*>(&hB.x));
-  float sum[4];
-#pragma unroll
-  for (int e = 0; e < 4; ++e)
-    sum[e] = ((acc[0][e] + acc[1][e]) + (acc[2][e] + acc[3][e])) + ((acc[4][e] + acc[5][e]) + (acc[6][e] + acc[7][e]));
-  total[0] += dA.x * sum[0] - dA.y * accm[0];
-  total[1] += dA.x * sum[1] - dA.y * accm[1];
-  total[2] += dB.x * sum[2] - dB.y * accm[2];
-  total[3] += dB.x * sum[3] - dB.y * accm[3];
+  total[0] += dA.x * ((acc[0][0] + acc[1][0]) + (acc[2][0] + acc[3][0])) - dA.y * accm[0];
+  total[1] += dA.x * ((acc[0][1] + acc[1][1]) + (acc[2][1] + acc[3][1])) - dA.y * accm[1];
+  total[2] += dB.x * ((acc[0][2] + acc[1][2]) + (acc[2][2] + acc[3][2])) - dB.y * accm[2];
+  total[3] += dB.x * ((acc[0][3] + acc[1][3]) + (acc[2][3] + acc[3][3])) - dB.y * accm[3];
 }
 
 // ---- Q6_K: one 16-row x 256-k unit -------------------------------------------------------------
@@ -282,6 +289,9 @@ template <class Q, int NMAT, int XSPLIT> __global__ void __launch_bounds__(kThre
 
   // ---- consumers ----
   const int g = lane >> 2, t = lane & 3;
+  // Shared-memory byte addresses of this lane's B fragments: slot rotated by j inside each 32-entry line.
+  const int rotation[4] = {0, (((lane + 1) & 31) - lane) * 8, (((lane + 2) & 31) - lane) * 8, (((lane + 3) & 31) - lane) * 8};
+  const uint32_t fragHiAddress = smem_u32(fragHi) + lane * 8, fragLoAddress = smem_u32(fragLo) + lane * 8, fragSumAddress = smem_u32(fragSum) + lane * 8;
   uint32_t it = 0;
   int tileCounter = 0;
   for (int chunk = 0; chunk < chunks; ++chunk) {
@@ -361,12 +371,13 @@ template <class Q, int NMAT, int XSPLIT> __global__ void __launch_bounds__(kThre
           if (warp < count && !(p.debug & 2)) {
             const uint8_t* base = ring + size_t(slot) * Q::kStageBytes + warp * Q::kBlockBytes;
             const int sb = grp * kStageBlocks + warp;
+            if (Q::kMinTerm) {
+              const uint32_t rows = smem_u32(base);
+              q4k_unit<XSPLIT>(rows + g * Q::kRowStride, rows + (g + 8) * Q::kRowStride, t, fragHiAddress + sb * 4096, fragLoAddress + sb * 4096, rotation,
+                               fragSumAddress + sb * 256, total[mat]);
+            } else {
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-              if (Q::kMinTerm)
-                q4k_unit<XSPLIT>(base + g * Q::kRowStride, base + (g + 8) * Q::kRowStride, lane, half, fragHi + sb * 512, fragLo + sb * 512,
-                                 fragSum + sb * 32, total[mat]);
-              else
+              for (int half = 0; half < 2; ++half)
                 q6k_unit<XSPLIT>(base + g * Q::kRowStride, base + (g + 8) * Q::kRowStride, lane, half, fragHi + sb * 512, fragLo + sb * 512,
                                  total[mat]);
             }

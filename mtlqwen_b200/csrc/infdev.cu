@@ -17,6 +17,8 @@
 
 struct infdev_ctx {
   int device = 0, sms = 0, xsplit = 2, debug = 0, umma = 1;  // umma: 0 never, 1 for more than 8 rows, 2 always
+  int integerDecode = 1;     // Q4_K decode GEMV: 1 integer-MMA kernel over an activation image, 0 fp16-MMA kernel
+  uint8_t* image = nullptr;  // activation image for the integer decode kernel (K up to 16384)
   void* ummaActs = nullptr;  // prepared activations + sums for the tcgen05 path (K up to 16384)
   float* ummaSums = nullptr;
   std::atomic<uint64_t> launches{0};  // kernels launched through this context
@@ -70,9 +72,9 @@ EncodeTiled encoder() {
 
 // Descriptor of a packed weight matrix [n][k/256 super-blocks] viewed as 8-byte elements: inner dimension = bytes of a
 // row / 8, outer = n rows; box = boxBlocks super-blocks x boxRows rows. Cached per matrix: encoding costs about a microsecond.
-int weight_map(infdev_ctx* ctx, const void* w, int64_t n, int64_t k, int blockBytes, int boxBlocks, int boxRows, CUtensorMap* out) {
+int weight_map(infdev_ctx* ctx, const void* w, int64_t n, int64_t k, int blockBytes, int boxBlocks, int boxRows, CUtensorMap* out, int padBytes = 0) {
   const std::string key = std::to_string(reinterpret_cast<uintptr_t>(w)) + ":" + std::to_string(n) + ":" + std::to_string(k) + ":" + std::to_string(blockBytes) + ":" +
-                          std::to_string(boxBlocks) + ":" + std::to_string(boxRows);
+                          std::to_string(boxBlocks) + ":" + std::to_string(boxRows) + ":" + std::to_string(padBytes);
   std::lock_guard<std::mutex> lock(ctx->mutex);
   auto found = ctx->tensorMaps.find(key);
   if (found != ctx->tensorMaps.end()) {
@@ -84,7 +86,8 @@ int weight_map(infdev_ctx* ctx, const void* w, int64_t n, int64_t k, int blockBy
     return fail(ctx, INFDEV_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   const uint64_t rowBytes = uint64_t(k / 256) * blockBytes;
   const cuuint64_t dims[2] = {rowBytes / 8, cuuint64_t(n)}, strides[1] = {rowBytes};
-  const cuuint32_t box[2] = {cuuint32_t(boxBlocks * blockBytes / 8), cuuint32_t(boxRows)}, elementStrides[2] = {1, 1};
+  // padBytes widens the box past its super-blocks (the extra bytes are whatever follows in the row, or zero fill).
+  const cuuint32_t box[2] = {cuuint32_t((boxBlocks * blockBytes + padBytes) / 8), cuuint32_t(boxRows)}, elementStrides[2] = {1, 1};
   CUtensorMap map;
   const CUresult result = encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(w), dims, strides, box, elementStrides,
                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -128,10 +131,13 @@ infdev_ctx* infdev_create(int device, char* error) {
     ctx->debug = std::atoi(env);
   if (const char* env = std::getenv("INFENG_UMMA"))
     ctx->umma = std::atoi(env);
+  if (const char* env = std::getenv("INFENG_INTEGER_DECODE"))
+    ctx->integerDecode = std::atoi(env) != 0;
   if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess ||
       (e = cudaEventCreateWithFlags(&ctx->done, cudaEventDisableTiming)) != cudaSuccess ||
       (e = cudaMalloc(reinterpret_cast<void**>(&ctx->status), sizeof(int))) != cudaSuccess ||
       (e = cudaMemset(ctx->status, 0, sizeof(int))) != cudaSuccess ||
+      (e = cudaMalloc(reinterpret_cast<void**>(&ctx->image), size_t(64) * infdev::kActivationImageBlockBytes)) != cudaSuccess ||
       (e = cudaMalloc(&ctx->ummaActs, size_t(64) * infdev::kUmmaMaxActBytesPerBlock)) != cudaSuccess ||
       (e = cudaMalloc(reinterpret_cast<void**>(&ctx->ummaSums), size_t(64) * 64 * sizeof(float))) != cudaSuccess ||
       (e = cudaHostAlloc(reinterpret_cast<void**>(&ctx->statusHost), sizeof(int), cudaHostAllocDefault)) != cudaSuccess) {
@@ -153,6 +159,7 @@ void infdev_destroy(infdev_ctx* ctx) {
   if (ctx->flush)
     cudaFree(ctx->flush);
   cudaFree(ctx->status);
+  cudaFree(ctx->image);
   cudaFree(ctx->ummaActs);
   cudaFree(ctx->ummaSums);
   cudaFreeHost(ctx->statusHost);
@@ -303,6 +310,11 @@ int infdev_set_umma(infdev_ctx* ctx, int enabled) {
   return INFDEV_OK;
 }
 
+int infdev_set_integer_decode(infdev_ctx* ctx, int enabled) {
+  ctx->integerDecode = enabled != 0;
+  return INFDEV_OK;
+}
+
 int infdev_set_xsplit(infdev_ctx* ctx, int xsplit) {
   if (xsplit != 1 && xsplit != 2)
     return fail(ctx, INFDEV_E_ARGUMENT, "xsplit must be 1 or 2");
@@ -408,16 +420,18 @@ static int linear_common(infdev_ctx* ctx, int type, bool pair, int count, const 
   infdev::GemvParams p{};
   p.nseg = count;
   int tiles = 0;
+  const bool integer = type == INFDEV_Q4_K && ctx->integerDecode && k <= 16384;
+  const int pad = integer ? infdev::kDecodePadBytes : 0;
   for (int i = 0; i < count; ++i) {
     if (n[i] <= 0 || n[i] % 16 || !aligned16(w[i]) || (pair && !aligned16(w2[i])))
       return fail(ctx, INFDEV_E_ARGUMENT, "linear: n must be a positive multiple of 16 and weights 16-byte aligned");
     p.seg[i] = {static_cast<const uint8_t*>(w[i]), pair ? static_cast<const uint8_t*>(w2[i]) : nullptr, y[i], residual ? residual[i] : nullptr,
                 int(n[i]), int(n[i]), tiles};
     const int blockBytes = type == INFDEV_Q4_K ? 144 : 210;
-    if (int r = weight_map(ctx, w[i], n[i], k, blockBytes, infdev::kGemvStageBlocks, infdev::kGemvTileRows, &p.map[i][0]))
+    if (int r = weight_map(ctx, w[i], n[i], k, blockBytes, infdev::kGemvStageBlocks, infdev::kGemvTileRows, &p.map[i][0], pad))
       return r;
     if (pair)
-      if (int r = weight_map(ctx, w2[i], n[i], k, blockBytes, infdev::kGemvStageBlocks, infdev::kGemvTileRows, &p.map[i][1]))
+      if (int r = weight_map(ctx, w2[i], n[i], k, blockBytes, infdev::kGemvStageBlocks, infdev::kGemvTileRows, &p.map[i][1], pad))
         return r;
     tiles += int(n[i] / 16);
   }
@@ -433,6 +447,15 @@ static int linear_common(infdev_ctx* ctx, int type, bool pair, int count, const 
     for (int i = 0; i < count; ++i) {
       p.seg[i].y = y[i] + row * n[i];
       p.seg[i].res = residual && residual[i] ? residual[i] + row * n[i] : nullptr;
+    }
+    if (integer) {
+      p.image = ctx->image;
+      if (int r = check(ctx, infdev::activation_image_launch(p.x, p.ldx, p.m, p.k, ctx->image, ctx->stream), "activation image"))
+        return r;
+      if (int r = check(ctx, infdev::q4k_decode_launch(pair, p, ctx->sms, ctx->stream), "q4k decode launch"))
+        return r;
+      ctx->launches += 2;
+      continue;
     }
     if (int r = check(ctx, infdev::gemv_launch(type, pair, ctx->xsplit, p, ctx->sms, ctx->stream), "gemv launch"))
       return r;

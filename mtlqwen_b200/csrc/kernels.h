@@ -22,6 +22,7 @@ struct GemvParams {
   GemvSeg seg[4];
   int nseg, tiles;
   const float* x;  // [m][ldx] fp32, rows 16-byte aligned
+  const uint8_t* image;  // quantised activations (act_image.cuh) of all k/256 blocks, for the integer Q4_K kernel
   int ldx, m, k;
   int* status;
   int debug;  // probe switches: 1 skips activation staging, 2 skips the MMA units
@@ -29,6 +30,10 @@ struct GemvParams {
 
 // Box geometry shared by the host encoder and the kernel.
 constexpr int kGemvStageBlocks = 8, kGemvTileRows = 16;
+// The integer Q4_K kernel reads 16 bytes past the 8 super-blocks of a box row, which makes the row pitch in shared
+// memory 1168 = 16 (mod 128) bytes: the 8 rows a warp touches in one load then fall into different banks.
+constexpr int kDecodePadBytes = 16;
+constexpr int kActivationImageBlockBytes = 4384;  // act_image.cuh: image bytes per 256 activations x 8 rows
 
 // ---- tcgen05 path (umma.cu) ----
 constexpr int kUmmaTileRows = 128, kUmmaMaxActBytesPerBlock = 16 * 128 * 16 * 2;  // prefill mode: 64 KB of fp16 activations per super-block
@@ -47,5 +52,10 @@ struct UmmaParams {
 cudaError_t umma_launch(bool pair, const UmmaParams& p, const float* x, int ldx, int sms, cudaStream_t stream);
 
 cudaError_t gemv_launch(int type, bool pair, int xsplit, const GemvParams& p, int sms, cudaStream_t stream);
+
+// Integer-MMA Q4_K decode GEMV over an activation image (q4k_decode.cu).
+cudaError_t q4k_decode_launch(bool pair, const GemvParams& p, int sms, cudaStream_t stream);
+// fp32 activations [m][ldx] -> image of k/256 blocks; rows m..7 are zero-filled.
+cudaError_t activation_image_launch(const float* x, int ldx, int m, int k, uint8_t* image, cudaStream_t stream);
 
 }  // namespace infdev

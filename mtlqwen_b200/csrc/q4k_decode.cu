@@ -1,0 +1,352 @@
+// Integer tensor-core GEMV for decode (M <= 8 activation rows) over GGUF Q4_K weights.
+//
+// Replaces linear_decode_q4_k[_add] (quant_linear.metal:245-327) and mlp_gate_up_q4_k_decode
+// (fused_kernels.metal:11-78) like gemv.cu, with a cheaper inner loop: the 4-bit quants feed the tensor cores
+// as unsigned bytes (one AND per four weights) against activations quantised to 15-bit integers per
+// (row, 256-value block) and split into a signed high and an unsigned low byte (act_image.cuh). One m16n8k32
+// integer MMA covers exactly one 32-weight sub-block of 16 weight rows, so the 6-bit sub-block scale is applied
+// to the int32 result with one integer multiply-add per accumulator; the super-block scale d, the activation
+// scale and the -dmin * m term (one fp16 MMA against the sub-block sums) are applied once per super-block.
+// The only approximation is the 15-bit activation grid: relative error about 3e-5 of the block maximum.
+//
+// One persistent CTA per SM: 8 consumer warps + 1 producer warp. The producer streams 16-row x 8-super-block
+// weight slabs with one tiled TMA copy each into a shared-memory ring, and bulk-copies the activation image of the
+// current K chunk; every wait on an mbarrier is bounded and ends in an abort flag plus a device status code.
+#include "act_image.cuh"
+#include "kernels.h"
+
+namespace infdev {
+namespace {
+
+constexpr int kConsumerWarps = 16;  // two halves of 8; consecutive ring stages alternate between the halves
+constexpr int kStageWarps = 8;       // one warp per super-block of a stage
+constexpr int kThreads = (kConsumerWarps + 1) * kWarp;
+constexpr int kChunkBlocks = 16;  // super-blocks of K whose image is resident at a time
+constexpr int kStageBlocks = kGemvStageBlocks;
+constexpr int kTileRows = kGemvTileRows;
+constexpr int kMaxStages = 8;
+constexpr int kBlockBytes = 144;
+constexpr int kRowPitch = kStageBlocks * kBlockBytes + kDecodePadBytes;  // 1168
+constexpr int kStageBytes = kTileRows * kRowPitch;                       // 18,688
+constexpr int kImagePieceBlocks = 4;                                      // blocks per bulk copy of the image
+
+struct Control {
+  uint64_t full[kMaxStages], empty[kMaxStages];
+  uint64_t imageFull, imageEmpty;
+  int abort;
+};
+constexpr int kControlBytes = 256;
+static_assert(sizeof(Control) <= kControlBytes, "control block overlaps the image");
+
+template <int NMAT> constexpr size_t fixed_bytes() {
+  return kControlBytes + size_t(kChunkBlocks) * kImageBlockBytes + size_t(2) * NMAT * kConsumerWarps * 128 * 4;
+}
+template <int NMAT> constexpr int stage_count() {
+  int stages = int((size_t(227) * 1024 - fixed_bytes<NMAT>()) / kStageBytes);
+  return stages > kMaxStages ? kMaxStages : stages;
+}
+template <int NMAT> constexpr size_t smem_bytes() { return fixed_bytes<NMAT>() + size_t(stage_count<NMAT>()) * kStageBytes; }
+
+__device__ __forceinline__ uint4 lds128(uint32_t address) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(address));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t address) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(address));
+  return v;
+}
+
+// D(16x8,s32) = A(16x32,u8,row) * B(32x8,s8 or u8,col)
+__device__ __forceinline__ void imma_u8s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
+}
+__device__ __forceinline__ void imma_u8u8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
+}
+
+// One 16-row x 256-k unit. Lane (g = lane/4, t = lane%4) owns weight rows g and g+8 (shared-memory addresses pA, pB)
+// and, in each 32-byte quant chunk c, bytes 8t .. 8t+7: their low nibbles are values 8t .. 8t+7 of sub-block 2c,
+// their high nibbles the same values of sub-block 2c+1 (GGUF layout as read by dequant_tile,
+// quant_linear.metal:39-46). The four bytes of a word fill four consecutive summation slots of the MMA, which is
+// the order the image stores the activations in. `image` is the block's image offset by this lane's fragment
+// (row g, quarter t); `sums` and `scales` address the lane's entries of the other two tables.
+__device__ __forceinline__ void q4k_unit(uint32_t pA, uint32_t pB, int t, uint32_t image, uint32_t sums, uint32_t scales, float (&total)[4]) {
+  const uint4 hA = lds128(pA), hB = lds128(pB);
+  // 6-bit scales / mins of the 8 sub-blocks, four per word (scale_min_k4, quant_linear.metal:12-20).
+  const uint32_t scA[2] = {hA.y & 0x3f3f3f3fu, (hA.w & 0x0f0f0f0fu) | ((hA.y >> 2) & 0x30303030u)};
+  const uint32_t mnA[2] = {hA.z & 0x3f3f3f3fu, ((hA.w >> 4) & 0x0f0f0f0fu) | ((hA.z >> 2) & 0x30303030u)};
+  const uint32_t scB[2] = {hB.y & 0x3f3f3f3fu, (hB.w & 0x0f0f0f0fu) | ((hB.y >> 2) & 0x30303030u)};
+  const uint32_t mnB[2] = {hB.z & 0x3f3f3f3fu, ((hB.w >> 4) & 0x0f0f0f0fu) | ((hB.z >> 2) & 0x30303030u)};
+  int part[2][4];  // sum over sub-blocks 0..3 and 4..7 of scale * (integer dot product); each stays inside int32
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+    part[h][0] = part[h][1] = part[h][2] = part[h][3] = 0;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint2 qA = lds64(pA + 16 + 32 * c + 8 * t), qB = lds64(pB + 16 + 32 * c + 8 * t);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int j = 2 * c + h;
+      uint32_t a[4];
+      if (h == 0) {
+        a[0] = qA.x & 0x0f0f0f0fu, a[1] = qB.x & 0x0f0f0f0fu, a[2] = qA.y & 0x0f0f0f0fu, a[3] = qB.y & 0x0f0f0f0fu;
+      } else {
+        a[0] = (qA.x >> 4) & 0x0f0f0f0fu, a[1] = (qB.x >> 4) & 0x0f0f0f0fu, a[2] = (qA.y >> 4) & 0x0f0f0f0fu, a[3] = (qB.y >> 4) & 0x0f0f0f0fu;
+      }
+      const uint4 b = lds128(image + j * 512);
+      int high[4], low[4];
+      imma_u8s8(high, a, b.x, b.y);
+      imma_u8u8(low, a, b.z, b.w);
+      const int sA = int(__byte_perm(scA[j >> 2], 0u, 0x4440 + (j & 3))), sB = int(__byte_perm(scB[j >> 2], 0u, 0x4440 + (j & 3)));
+      int(&sum)[4] = part[j >> 2];
+      sum[0] += sA * (low[0] + (high[0] << 8));
+      sum[1] += sA * (low[1] + (high[1] << 8));
+      sum[2] += sB * (low[2] + (high[2] << 8));
+      sum[3] += sB * (low[3] + (high[3] << 8));
+    }
+  }
+  // min term: sum_j m_j * S_j / 32; summation slots 0..7 carry the fp16 high halves of the sums, 8..15 the low halves.
+  float accm[4] = {0.f, 0.f, 0.f, 0.f};
+  {
+    constexpr uint32_t k1024 = 0x64006400u;
+    const uint32_t wordA = (t & 2) ? mnA[1] : mnA[0], wordB = (t & 2) ? mnB[1] : mnB[0];
+    const uint32_t pairA = (wordA >> ((t & 1) * 16)) & 0xffffu, pairB = (wordB >> ((t & 1) * 16)) & 0xffffu;
+    uint32_t a[4];
+    a[0] = a[2] = hsub2_u32(__byte_perm(pairA, 0x64u, 0x4140), k1024);
+    a[1] = a[3] = hsub2_u32(__byte_perm(pairB, 0x64u, 0x4140), k1024);
+    const uint2 b = lds64(sums);
+    mma_16816(accm, a, b.x, b.y);
+  }
+  const uint2 xsBits = lds64(scales);
+  const float xs0 = __uint_as_float(xsBits.x), xs1 = __uint_as_float(xsBits.y);
+  const float2 dA = __half22float2(*reinterpret_cast<const __half2*>(&hA.x)), dB = __half22float2(*reinterpret_cast<const __half2*>(&hB.x));
+  const float mA = 32.f * dA.y, mB = 32.f * dB.y;
+  total[0] += xs0 * (dA.x * (float(part[0][0]) + float(part[1][0])) - mA * accm[0]);
+  total[1] += xs1 * (dA.x * (float(part[0][1]) + float(part[1][1])) - mA * accm[1]);
+  total[2] += xs0 * (dB.x * (float(part[0][2]) + float(part[1][2])) - mB * accm[2]);
+  total[3] += xs1 * (dB.x * (float(part[0][3]) + float(part[1][3])) - mB * accm[3]);
+}
+
+__device__ __forceinline__ int find_segment(const GemvParams& p, int tile) {
+  int s = 0;
+  while (s + 1 < p.nseg && tile >= p.seg[s + 1].tile0)
+    ++s;
+  return s;
+}
+
+template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_kernel(const __grid_constant__ GemvParams p) {
+  constexpr int kStages = stage_count<NMAT>();
+  extern __shared__ __align__(128) uint8_t smemRaw[];
+  Control& ctl = *reinterpret_cast<Control*>(smemRaw);
+  uint8_t* image = smemRaw + kControlBytes;
+  float* partial = reinterpret_cast<float*>(image + size_t(kChunkBlocks) * kImageBlockBytes);
+  uint8_t* ring = reinterpret_cast<uint8_t*>(partial + 2 * NMAT * kConsumerWarps * 128);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int blocksPerRow = p.k / 256;
+  const int chunks = (blocksPerRow + kChunkBlocks - 1) / kChunkBlocks;
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&ctl.full[s], 1);
+      mbar_init(&ctl.empty[s], kStageWarps);
+    }
+    mbar_init(&ctl.imageFull, 1);
+    mbar_init(&ctl.imageEmpty, kConsumerWarps);
+    ctl.abort = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  volatile int* abortFlag = &ctl.abort;
+
+  if (warp == kConsumerWarps) {
+    // ---- producer: activation image of each K chunk, then its weight slabs ----
+    uint32_t it = 0;
+    for (int chunk = 0; chunk < chunks && !*abortFlag; ++chunk) {
+      const int chunkBlocks = min(kChunkBlocks, blocksPerRow - chunk * kChunkBlocks);
+      const int groups = (chunkBlocks + kStageBlocks - 1) / kStageBlocks;
+      bool ok = true;
+      if (lane == 0 && chunk > 0)  // the consumers have finished with the previous chunk's image
+        ok = mbar_wait_bounded(&ctl.imageEmpty, (chunk - 1) & 1, abortFlag);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) {
+        if (lane == 0) {
+          *abortFlag = 1;
+          atomicExch(p.status, kStatusBarrierTimeout);
+        }
+        break;
+      }
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&ctl.imageFull, uint32_t(chunkBlocks) * kImageBlockBytes);
+        for (int first = 0; first < chunkBlocks; first += kImagePieceBlocks) {
+          const int count = min(kImagePieceBlocks, chunkBlocks - first);
+          bulk_load(image + size_t(first) * kImageBlockBytes, p.image + size_t(chunk * kChunkBlocks + first) * kImageBlockBytes,
+                    uint32_t(count) * kImageBlockBytes, &ctl.imageFull);
+        }
+      }
+      __syncwarp();
+      for (int tile = blockIdx.x; tile < p.tiles && !*abortFlag; tile += gridDim.x) {
+        const int segment = find_segment(p, tile);
+        const int row0 = (tile - p.seg[segment].tile0) * kTileRows;
+        for (int mat = 0; mat < NMAT; ++mat) {
+          for (int grp = 0; grp < groups; ++grp, ++it) {
+            const uint32_t slot = it % kStages, round = it / kStages;
+            ok = true;
+            if (lane == 0 && round > 0)
+              ok = mbar_wait_bounded(&ctl.empty[slot], (round - 1) & 1, abortFlag);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) {
+              if (lane == 0) {
+                *abortFlag = 1;
+                atomicExch(p.status, kStatusBarrierTimeout);
+              }
+              break;
+            }
+            // One tiled copy moves the whole slab; bytes past the end of a row are zero-filled and still counted, so the
+            // transaction size is always the full box.
+            if (lane == 0) {
+              mbar_arrive_expect_tx(&ctl.full[slot], uint32_t(kStageBytes));
+              tma_load_2d(ring + size_t(slot) * kStageBytes, &p.map[segment][mat], (chunk * (kChunkBlocks / kStageBlocks) + grp) * (kStageBlocks * kBlockBytes / 8),
+                          row0, &ctl.full[slot]);
+            }
+            __syncwarp();
+          }
+        }
+      }
+    }
+    return;
+  }
+
+  // ---- consumers ----
+  const int g = lane >> 2, t = lane & 3, half = warp / kStageWarps, unit = warp % kStageWarps;
+  const uint32_t imageAddress = smem_u32(image);
+  const uint32_t laneImage = imageAddress + g * 64 + t * 16, laneSums = imageAddress + kImageSumOffset + lane * 8,
+                 laneScales = imageAddress + kImageScaleOffset + t * 8;
+  uint32_t it = 0;
+  int tileCounter = 0;
+  for (int chunk = 0; chunk < chunks; ++chunk) {
+    const int chunkBlocks = min(kChunkBlocks, blocksPerRow - chunk * kChunkBlocks);
+    const int groups = (chunkBlocks + kStageBlocks - 1) / kStageBlocks;
+    if (!*abortFlag && !mbar_wait_bounded(&ctl.imageFull, chunk & 1, abortFlag)) {
+      *abortFlag = 1;
+      atomicExch(p.status, kStatusBarrierTimeout);
+    }
+    for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++tileCounter) {
+      float total[NMAT][4];
+#pragma unroll
+      for (int mat = 0; mat < NMAT; ++mat)
+        total[mat][0] = total[mat][1] = total[mat][2] = total[mat][3] = 0.f;
+#pragma unroll
+      for (int mat = 0; mat < NMAT; ++mat)
+        for (int grp = 0; grp < groups; ++grp, ++it) {
+          const uint32_t slot = it % kStages, round = it / kStages;
+          if (*abortFlag || int(it & 1) != half)
+            continue;
+          if (!mbar_wait_bounded(&ctl.full[slot], round & 1, abortFlag)) {
+            *abortFlag = 1;
+            atomicExch(p.status, kStatusBarrierTimeout);
+            continue;
+          }
+          const int count = min(kStageBlocks, chunkBlocks - grp * kStageBlocks);
+          if (unit < count && !(p.debug & 2)) {
+            const uint32_t rows = smem_u32(ring + size_t(slot) * kStageBytes) + unit * kBlockBytes;
+            const int sb = grp * kStageBlocks + unit;
+            q4k_unit(rows + g * kRowPitch, rows + (g + 8) * kRowPitch, t, laneImage + sb * kImageBlockBytes, laneSums + sb * kImageBlockBytes,
+                     laneScales + sb * kImageBlockBytes, total[mat]);
+          }
+          __syncwarp();
+          if (lane == 0)
+            mbar_arrive(&ctl.empty[slot]);
+        }
+      // Cross-warp reduction of the K split, then the epilogue.
+      float* mine = partial + size_t(tileCounter & 1) * NMAT * kConsumerWarps * 128;
+#pragma unroll
+      for (int mat = 0; mat < NMAT; ++mat) {
+        float* dst = mine + (mat * kConsumerWarps + warp) * 128;
+        dst[(2 * t) * 16 + g] = total[mat][0];
+        dst[(2 * t + 1) * 16 + g] = total[mat][1];
+        dst[(2 * t) * 16 + g + 8] = total[mat][2];
+        dst[(2 * t + 1) * 16 + g + 8] = total[mat][3];
+      }
+      named_barrier(1, kConsumerWarps * kWarp);
+      if (tid < 128) {
+        const int row = tid >> 4, local = tid & 15;
+        float sum[NMAT];
+#pragma unroll
+        for (int mat = 0; mat < NMAT; ++mat) {
+          sum[mat] = 0.f;
+#pragma unroll
+          for (int w = 0; w < kConsumerWarps; ++w)
+            sum[mat] += mine[(mat * kConsumerWarps + w) * 128 + tid];
+        }
+        if (row < p.m) {
+          const GemvSeg& seg = p.seg[find_segment(p, tile)];
+          const size_t at = size_t(row) * seg.ldy + size_t(tile - seg.tile0) * kTileRows + local;
+          float value = sum[0];
+          if (NMAT == 2)
+            value = silu_f(sum[0]) * sum[1];
+          else if (chunk > 0)
+            value += seg.y[at];
+          else if (seg.res)
+            value += seg.res[at];
+          seg.y[at] = value;
+        }
+      }
+    }
+    // This chunk's image may now be overwritten.
+    __syncwarp();
+    if (lane == 0)
+      mbar_arrive(&ctl.imageEmpty);
+  }
+}
+
+// One warp per (row, 256-value block).
+__global__ void __launch_bounds__(256) activation_image_kernel(const float* x, int ldx, int m, int blocks, uint8_t* image) {
+  const int item = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (item >= blocks * kImageRows)
+    return;
+  const int block = item >> 3, row = item & 7;
+  uint8_t* out = image + size_t(block) * kImageBlockBytes;
+  if (row >= m) {
+    image_zero_block(out, row, lane);
+    return;
+  }
+  const float4* src = reinterpret_cast<const float4*>(x + size_t(row) * ldx + size_t(block) * 256 + lane * 8);
+  const float4 lo = src[0], hi = src[1];
+  const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+  image_store_block(out, row, lane, v);
+}
+
+template <int NMAT> cudaError_t launch(const GemvParams& p, int sms, cudaStream_t stream) {
+  static bool configured = false;
+  constexpr size_t bytes = smem_bytes<NMAT>();
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(q4k_decode_kernel<NMAT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes));
+    if (e != cudaSuccess)
+      return e;
+    configured = true;
+  }
+  const int grid = p.tiles < sms ? p.tiles : sms;
+  q4k_decode_kernel<NMAT><<<grid, kThreads, bytes, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t q4k_decode_launch(bool pair, const GemvParams& p, int sms, cudaStream_t stream) {
+  return pair ? launch<2>(p, sms, stream) : launch<1>(p, sms, stream);
+}
+
+cudaError_t activation_image_launch(const float* x, int ldx, int m, int k, uint8_t* image, cudaStream_t stream) {
+  const int blocks = k / 256;
+  activation_image_kernel<<<(blocks * kImageRows + 7) / 8, 256, 0, stream>>>(x, ldx, m, blocks, image);
+  return cudaGetLastError();
+}
+
+}  // namespace infdev

@@ -54,6 +54,7 @@ def library():
     "infdev_event_elapsed_ms": (ctypes.c_float, (vp, vp, vp)),
     "infdev_flush_l2": (i32, (vp, )),
     "infdev_set_xsplit": (i32, (vp, i32)),
+    "infdev_set_integer_decode": (i32, (vp, i32)),
     "infdev_set_umma": (i32, (vp, i32)),
     "infdev_profiler_range": (i32, (vp, i32)),
     "infdev_graph_begin": (i32, (vp, )),
@@ -181,6 +182,9 @@ class Device:
 
   def set_xsplit(self, xsplit):
     self.check(self.lib.infdev_set_xsplit(self.ctx, xsplit))
+
+  def set_integer_decode(self, enabled):
+    self.check(self.lib.infdev_set_integer_decode(self.ctx, int(enabled)))
 
   # ---- kernels ----
   def dequant(self, qtype, blocks, count, out):

@@ -38,22 +38,59 @@ def test_dequant_bit_exact_against_oracle_large(dev, qtype):
   assert out.download().tobytes() == oracle.dequant(blocks, qtype).tobytes()
 
 
-def run_linear(dev, qtype, n, k, m, seed, residual=False, xsplit=2):
-  w, x = synth.weight(qtype, n, k, seed), synth.activations(m, k, seed + 1)
+def run_linear(dev, qtype, n, k, m, seed, residual=False, xsplit=2, integer=True, x=None, w=None):
+  """integer: the integer-MMA Q4_K kernel (the default path) or the fp16-MMA kernel."""
+  w = synth.weight(qtype, n, k, seed) if w is None else w
+  x = synth.activations(m, k, seed + 1) if x is None else x
   res = synth.activations(m, n, seed + 2) if residual else None
   dev.set_xsplit(xsplit)
-  y = dev.empty((m, n))
-  dres = dev.array(res) if residual else None
-  dev.linear(qtype, dev.array(w), n, k, dev.array(x), m, y, dres)
-  dev.commit()
-  dev.set_xsplit(2)
+  dev.set_integer_decode(integer)
+  try:
+    y = dev.empty((m, n))
+    dres = dev.array(res) if residual else None
+    dev.linear(qtype, dev.array(w), n, k, dev.array(x), m, y, dres)
+    dev.commit()
+  finally:
+    dev.set_xsplit(2)
+    dev.set_integer_decode(True)
   return y.download(), oracle.linear(w, qtype, n, k, x, res)
 
 
+@pytest.mark.parametrize("integer", [True, False])
 @pytest.mark.parametrize("m", [1, 8])
-def test_q4k_linear_config1_shape(dev, m):
+def test_q4k_linear_config1_shape(dev, m, integer):
   """BASELINE config 1: weight 12288 x 4096 Q4_K, fp32 activations ~N(0,1), M in {1, 8}."""
-  got, want = run_linear(dev, D.Q4_K, 12288, 4096, m, 1234)
+  got, want = run_linear(dev, D.Q4_K, 12288, 4096, m, 1234, integer=integer)
+  assert rel_err(got, want) < TOL
+
+
+def test_integer_kernel_error_level(dev):
+  """15-bit activations per 256-value block: the error sits near 5e-5, far inside the contract."""
+  got, want = run_linear(dev, D.Q4_K, 4096, 4096, 8, 41)
+  assert 1e-7 < rel_err(got, want) < 2e-4
+
+
+def test_integer_kernel_cannot_overflow(dev):
+  """Every quant 15, every scale 63 and constant activations drive the int32 partial sums to their bound."""
+  n, k, m = 64, 4096, 8
+  blocks = np.zeros((n * k // 256, 144), np.uint8)
+  blocks[:, 0:2] = np.frombuffer(np.float16(0.01).tobytes(), np.uint8)
+  blocks[:, 2:4] = np.frombuffer(np.float16(0.02).tobytes(), np.uint8)
+  blocks[:, 4:16] = 0xFF  # scales and mins 63
+  blocks[:, 16:] = 0xFF   # quants 15
+  x = np.full((m, k), -3.0, np.float32)
+  x[1::2] = 5.0
+  got, want = run_linear(dev, D.Q4_K, n, k, m, 0, x=x, w=blocks)
+  assert rel_err(got, want) < 1e-5
+
+
+def test_integer_kernel_with_outliers_and_zero_blocks(dev):
+  n, k, m = 256, 4096, 6
+  x = synth.activations(m, k, 77)
+  x[:, 5::97] *= 200.0   # outlier channels
+  x[2, 512:1024] = 0.0   # all-zero blocks
+  x[4] = 0.0
+  got, want = run_linear(dev, D.Q4_K, n, k, m, 78, x=x)
   assert rel_err(got, want) < TOL
 
 
@@ -88,13 +125,13 @@ def test_linear_more_than_eight_rows(dev):
 
 
 def test_hi_only_activation_split_stays_inside_tolerance(dev):
-  got, want = run_linear(dev, D.Q4_K, 4096, 4096, 8, 41, xsplit=1)
+  got, want = run_linear(dev, D.Q4_K, 4096, 4096, 8, 41, xsplit=1, integer=False)
   err = rel_err(got, want)
   assert 1e-6 < err < TOL
 
 
 def test_hi_lo_split_is_fp32_accurate(dev):
-  got, want = run_linear(dev, D.Q4_K, 4096, 4096, 8, 41)
+  got, want = run_linear(dev, D.Q4_K, 4096, 4096, 8, 41, integer=False)
   assert rel_err(got, want) < 2e-5
 
 
