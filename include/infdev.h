@@ -83,8 +83,8 @@ int infdev_profiler_range(infdev_ctx* ctx, int on);
 int infdev_set_umma(infdev_ctx* ctx, int enabled);
 /* Activation split of the fp16 tensor-core GEMV: 2 = hi+lo fp16 (fp32-accurate, default), 1 = hi only. */
 int infdev_set_xsplit(infdev_ctx* ctx, int xsplit);
-/* Q4_K GEMV for up to 8 rows per launch: 1 (default) = integer-MMA kernel over activations quantised to 15 bits per
- * 256-value block (relative error about 3e-5 of the block maximum), 0 = the fp16-MMA kernel. Q6_K always takes the
+/* Q4_K GEMV for up to 8 rows per launch: 1 (default) = integer-MMA kernel over activations quantised to 16 bits per
+ * 256-value block (error at most 1.6e-5 of the block maximum), 0 = the fp16-MMA kernel. Q6_K always takes the
  * fp16-MMA kernel. Environment: INFENG_INTEGER_DECODE. */
 int infdev_set_integer_decode(infdev_ctx* ctx, int enabled);
 /* CUDA-graph capture of a pass on the context's stream (no reference counterpart: Metal re-encodes every

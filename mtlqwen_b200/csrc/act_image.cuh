@@ -1,10 +1,9 @@
 // Activation image: the operand format the integer decode GEMV (q4k_decode.cu) reads.
 //
-// Up to 8 activation rows x K values are quantised per (row, 256-value block) to 15-bit integers
-// x_int = rint(x / xs), xs = max|x| / 16383, and stored split as hi = x_int >> 8 (signed byte) and
+// Up to 8 activation rows x K values are quantised per (row, 256-value block) to 16-bit integers
+// x_int = rint(x / xs), xs = max|x| / 32767, and stored split as hi = x_int >> 8 (signed byte) and
 // lo = x_int & 255 (unsigned byte), so that sum q * x_int = 256 * sum q * hi + sum q * lo runs as two
-// m16n8k32 integer MMAs. 15 bits keep a whole 4-sub-block partial sum inside int32 for any input:
-// 4 * 63 * 15 * 32 * 16383 < 2^31.
+// m16n8k32 integer MMAs whose results are kept apart until the end of a super-block.
 //
 // Per 256-value block (kImageBlockBytes, contiguous, in this order):
 //   [8 sub-blocks][8 rows][4 quarters][16 B]   quarter t of sub-block j: 8 hi bytes then 8 lo bytes of the
@@ -25,7 +24,7 @@ constexpr int kImageSumOffset = kImageQuantBytes;  // 256 B of sums
 constexpr int kImageScaleOffset = kImageSumOffset + 256;
 constexpr int kImageBlockBytes = kImageScaleOffset + 32;  // 4384, a multiple of 16
 constexpr int kImageRows = 8;
-constexpr float kImageLevels = 16383.0f;
+constexpr float kImageLevels = 32767.0f;
 
 // One warp quantises one (row, block): lane L holds the 8 consecutive values 8L .. 8L+7 of the block
 // (sub-block L/4, quarter L%4). `block` points at the image of this 256-value block.
@@ -41,7 +40,7 @@ __device__ __forceinline__ void image_store_block(uint8_t* block, int row, int l
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     int q = __float2int_rn(v[i] * inv);
-    q = max(-16383, min(16383, q));
+    q = max(-32767, min(32767, q));
     sum += q;
     hi[i >> 2] |= (uint32_t(q >> 8) & 0xffu) << (8 * (i & 3));
     lo[i >> 2] |= (uint32_t(q) & 0xffu) << (8 * (i & 3));

@@ -47,6 +47,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Waits for a phase with an iteration limit. Returns false when the limit ran out; the caller then
 // raises the abort flag so every role of the kernel leaves its loops instead of spinning forever.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abortFlag) {
+  if (mbar_try_wait(bar, parity))  // the common case: the phase has already completed
+    return true;
   for (uint32_t spin = 0; spin < (1u << 20); ++spin) {
     if (mbar_try_wait(bar, parity))
       return true;
@@ -78,7 +80,7 @@ __device__ __forceinline__ void named_barrier(int id, int threads) {
 
 // D(16x8,f32) += A(16x16,f16,row) * B(16x8,f16,col)
 __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }

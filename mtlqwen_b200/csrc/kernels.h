@@ -25,14 +25,15 @@ struct GemvParams {
   const uint8_t* image;  // quantised activations (act_image.cuh) of all k/256 blocks, for the integer Q4_K kernel
   int ldx, m, k;
   int* status;
-  int debug;  // probe switches: 1 skips activation staging, 2 skips the MMA units
+  int debug;  // probe switches: 1 skips activation staging, 2 skips the MMA units, 4 skips the weight copies (integer kernel)
 };
 
 // Box geometry shared by the host encoder and the kernel.
 constexpr int kGemvStageBlocks = 8, kGemvTileRows = 16;
-// The integer Q4_K kernel reads 16 bytes past the 8 super-blocks of a box row, which makes the row pitch in shared
-// memory 1168 = 16 (mod 128) bytes: the 8 rows a warp touches in one load then fall into different banks.
-constexpr int kDecodePadBytes = 16;
+// The integer Q4_K kernel reads 32 bytes past the 8 super-blocks of a box row, which makes the row pitch in shared
+// memory 1184 = 32 (mod 128) bytes: the 32-byte pieces of consecutive rows that a warp reads in one load then fall
+// into different banks.
+constexpr int kDecodePadBytes = 32;
 constexpr int kActivationImageBlockBytes = 4384;  // act_image.cuh: image bytes per 256 activations x 8 rows
 
 // ---- tcgen05 path (umma.cu) ----

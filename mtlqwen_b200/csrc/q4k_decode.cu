@@ -2,12 +2,12 @@
 //
 // Replaces linear_decode_q4_k[_add] (quant_linear.metal:245-327) and mlp_gate_up_q4_k_decode
 // (fused_kernels.metal:11-78) like gemv.cu, with a cheaper inner loop: the 4-bit quants feed the tensor cores
-// as unsigned bytes (one AND per four weights) against activations quantised to 15-bit integers per
+// as unsigned bytes (one AND per four weights) against activations quantised to 16-bit integers per
 // (row, 256-value block) and split into a signed high and an unsigned low byte (act_image.cuh). One m16n8k32
 // integer MMA covers exactly one 32-weight sub-block of 16 weight rows, so the 6-bit sub-block scale is applied
 // to the int32 result with one integer multiply-add per accumulator; the super-block scale d, the activation
 // scale and the -dmin * m term (one fp16 MMA against the sub-block sums) are applied once per super-block.
-// The only approximation is the 15-bit activation grid: relative error about 3e-5 of the block maximum.
+// The only approximation is the 16-bit activation grid: absolute error at most 1.6e-5 of the block maximum.
 //
 // One persistent CTA per SM: 8 consumer warps + 1 producer warp. The producer streams 16-row x 8-super-block
 // weight slabs with one tiled TMA copy each into a shared-memory ring, and bulk-copies the activation image of the
@@ -26,8 +26,8 @@ constexpr int kStageBlocks = kGemvStageBlocks;
 constexpr int kTileRows = kGemvTileRows;
 constexpr int kMaxStages = 8;
 constexpr int kBlockBytes = 144;
-constexpr int kRowPitch = kStageBlocks * kBlockBytes + kDecodePadBytes;  // 1168
-constexpr int kStageBytes = kTileRows * kRowPitch;                       // 18,688
+constexpr int kRowPitch = kStageBlocks * kBlockBytes + kDecodePadBytes;  // 1184
+constexpr int kStageBytes = kTileRows * kRowPitch;                       // 18,944
 constexpr int kImagePieceBlocks = 4;                                      // blocks per bulk copy of the image
 
 struct Control {
@@ -47,25 +47,19 @@ template <int NMAT> constexpr int stage_count() {
 }
 template <int NMAT> constexpr size_t smem_bytes() { return fixed_bytes<NMAT>() + size_t(stage_count<NMAT>()) * kStageBytes; }
 
-__device__ __forceinline__ uint4 lds128(uint32_t address) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(address));
-  return v;
-}
-__device__ __forceinline__ uint2 lds64(uint32_t address) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(address));
-  return v;
-}
+// Ordinary loads (not volatile asm): the compiler may hoist and interleave them with the MMAs, but not move them
+// above the mbarrier wait, which clobbers memory.
+__device__ __forceinline__ uint4 lds128(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ uint2 lds64(const uint8_t* p) { return *reinterpret_cast<const uint2*>(p); }
 
 // D(16x8,s32) = A(16x32,u8,row) * B(32x8,s8 or u8,col)
 __device__ __forceinline__ void imma_u8s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
 }
 __device__ __forceinline__ void imma_u8u8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
 }
@@ -76,17 +70,17 @@ __device__ __forceinline__ void imma_u8u8(int (&d)[4], const uint32_t (&a)[4], u
 // quant_linear.metal:39-46). The four bytes of a word fill four consecutive summation slots of the MMA, which is
 // the order the image stores the activations in. `image` is the block's image offset by this lane's fragment
 // (row g, quarter t); `sums` and `scales` address the lane's entries of the other two tables.
-__device__ __forceinline__ void q4k_unit(uint32_t pA, uint32_t pB, int t, uint32_t image, uint32_t sums, uint32_t scales, float (&total)[4]) {
+__device__ __forceinline__ void q4k_unit(const uint8_t* pA, const uint8_t* pB, int t, const uint8_t* image, const uint8_t* sums, const uint8_t* scales,
+                                         float (&total)[4]) {
   const uint4 hA = lds128(pA), hB = lds128(pB);
   // 6-bit scales / mins of the 8 sub-blocks, four per word (scale_min_k4, quant_linear.metal:12-20).
   const uint32_t scA[2] = {hA.y & 0x3f3f3f3fu, (hA.w & 0x0f0f0f0fu) | ((hA.y >> 2) & 0x30303030u)};
   const uint32_t mnA[2] = {hA.z & 0x3f3f3f3fu, ((hA.w >> 4) & 0x0f0f0f0fu) | ((hA.z >> 2) & 0x30303030u)};
   const uint32_t scB[2] = {hB.y & 0x3f3f3f3fu, (hB.w & 0x0f0f0f0fu) | ((hB.y >> 2) & 0x30303030u)};
   const uint32_t mnB[2] = {hB.z & 0x3f3f3f3fu, ((hB.w >> 4) & 0x0f0f0f0fu) | ((hB.z >> 2) & 0x30303030u)};
-  int part[2][4];  // sum over sub-blocks 0..3 and 4..7 of scale * (integer dot product); each stays inside int32
-#pragma unroll
-  for (int h = 0; h < 2; ++h)
-    part[h][0] = part[h][1] = part[h][2] = part[h][3] = 0;
+  // sum over the 8 sub-blocks of scale * (integer dot product), separately for the low and the high activation byte:
+  // |low| <= 8 * 63 * 15 * 32 * 255 and |high| <= 8 * 63 * 15 * 32 * 128 both stay far inside int32.
+  int sumLow[4] = {0, 0, 0, 0}, sumHigh[4] = {0, 0, 0, 0};
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     const uint2 qA = lds64(pA + 16 + 32 * c + 8 * t), qB = lds64(pB + 16 + 32 * c + 8 * t);
@@ -104,11 +98,10 @@ __device__ __forceinline__ void q4k_unit(uint32_t pA, uint32_t pB, int t, uint32
       imma_u8s8(high, a, b.x, b.y);
       imma_u8u8(low, a, b.z, b.w);
       const int sA = int(__byte_perm(scA[j >> 2], 0u, 0x4440 + (j & 3))), sB = int(__byte_perm(scB[j >> 2], 0u, 0x4440 + (j & 3)));
-      int(&sum)[4] = part[j >> 2];
-      sum[0] += sA * (low[0] + (high[0] << 8));
-      sum[1] += sA * (low[1] + (high[1] << 8));
-      sum[2] += sB * (low[2] + (high[2] << 8));
-      sum[3] += sB * (low[3] + (high[3] << 8));
+      sumLow[0] += sA * low[0], sumHigh[0] += sA * high[0];
+      sumLow[1] += sA * low[1], sumHigh[1] += sA * high[1];
+      sumLow[2] += sB * low[2], sumHigh[2] += sB * high[2];
+      sumLow[3] += sB * low[3], sumHigh[3] += sB * high[3];
     }
   }
   // min term: sum_j m_j * S_j / 32; summation slots 0..7 carry the fp16 high halves of the sums, 8..15 the low halves.
@@ -127,10 +120,10 @@ __device__ __forceinline__ void q4k_unit(uint32_t pA, uint32_t pB, int t, uint32
   const float xs0 = __uint_as_float(xsBits.x), xs1 = __uint_as_float(xsBits.y);
   const float2 dA = __half22float2(*reinterpret_cast<const __half2*>(&hA.x)), dB = __half22float2(*reinterpret_cast<const __half2*>(&hB.x));
   const float mA = 32.f * dA.y, mB = 32.f * dB.y;
-  total[0] += xs0 * (dA.x * (float(part[0][0]) + float(part[1][0])) - mA * accm[0]);
-  total[1] += xs1 * (dA.x * (float(part[0][1]) + float(part[1][1])) - mA * accm[1]);
-  total[2] += xs0 * (dB.x * (float(part[0][2]) + float(part[1][2])) - mB * accm[2]);
-  total[3] += xs1 * (dB.x * (float(part[0][3]) + float(part[1][3])) - mB * accm[3]);
+  total[0] += xs0 * (dA.x * fmaf(float(sumHigh[0]), 256.f, float(sumLow[0])) - mA * accm[0]);
+  total[1] += xs1 * (dA.x * fmaf(float(sumHigh[1]), 256.f, float(sumLow[1])) - mA * accm[1]);
+  total[2] += xs0 * (dB.x * fmaf(float(sumHigh[2]), 256.f, float(sumLow[2])) - mB * accm[2]);
+  total[3] += xs1 * (dB.x * fmaf(float(sumHigh[3]), 256.f, float(sumLow[3])) - mB * accm[3]);
 }
 
 __device__ __forceinline__ int find_segment(const GemvParams& p, int tile) {
@@ -210,7 +203,9 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
             }
             // One tiled copy moves the whole slab; bytes past the end of a row are zero-filled and still counted, so the
             // transaction size is always the full box.
-            if (lane == 0) {
+            if (lane == 0 && (p.debug & 4)) {
+              mbar_arrive(&ctl.full[slot]);  // probe: the consumers run on whatever the ring holds
+            } else if (lane == 0) {
               mbar_arrive_expect_tx(&ctl.full[slot], uint32_t(kStageBytes));
               tma_load_2d(ring + size_t(slot) * kStageBytes, &p.map[segment][mat], (chunk * (kChunkBlocks / kStageBlocks) + grp) * (kStageBlocks * kBlockBytes / 8),
                           row0, &ctl.full[slot]);
@@ -225,9 +220,8 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
 
   // ---- consumers ----
   const int g = lane >> 2, t = lane & 3, half = warp / kStageWarps, unit = warp % kStageWarps;
-  const uint32_t imageAddress = smem_u32(image);
-  const uint32_t laneImage = imageAddress + g * 64 + t * 16, laneSums = imageAddress + kImageSumOffset + lane * 8,
-                 laneScales = imageAddress + kImageScaleOffset + t * 8;
+  const uint8_t *laneImage = image + g * 64 + t * 16, *laneSums = image + kImageSumOffset + lane * 8, *laneScales = image + kImageScaleOffset + t * 8;
+  const int laneRow = g * kRowPitch + unit * kBlockBytes;
   uint32_t it = 0;
   int tileCounter = 0;
   for (int chunk = 0; chunk < chunks; ++chunk) {
@@ -242,28 +236,32 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
 #pragma unroll
       for (int mat = 0; mat < NMAT; ++mat)
         total[mat][0] = total[mat][1] = total[mat][2] = total[mat][3] = 0.f;
-#pragma unroll
-      for (int mat = 0; mat < NMAT; ++mat)
-        for (int grp = 0; grp < groups; ++grp, ++it) {
-          const uint32_t slot = it % kStages, round = it / kStages;
-          if (*abortFlag || int(it & 1) != half)
-            continue;
-          if (!mbar_wait_bounded(&ctl.full[slot], round & 1, abortFlag)) {
-            *abortFlag = 1;
-            atomicExch(p.status, kStatusBarrierTimeout);
-            continue;
-          }
-          const int count = min(kStageBlocks, chunkBlocks - grp * kStageBlocks);
-          if (unit < count && !(p.debug & 2)) {
-            const uint32_t rows = smem_u32(ring + size_t(slot) * kStageBytes) + unit * kBlockBytes;
-            const int sb = grp * kStageBlocks + unit;
-            q4k_unit(rows + g * kRowPitch, rows + (g + 8) * kRowPitch, t, laneImage + sb * kImageBlockBytes, laneSums + sb * kImageBlockBytes,
-                     laneScales + sb * kImageBlockBytes, total[mat]);
-          }
-          __syncwarp();
-          if (lane == 0)
-            mbar_arrive(&ctl.empty[slot]);
+      // Consecutive ring stages alternate between the two halves of the consumer warps.
+      const int perTile = NMAT * groups;
+      for (int local = (half - int(it)) & 1; local < perTile; local += 2) {
+        const uint32_t stage = it + local, slot = stage % kStages, round = stage / kStages;
+        const int mat = NMAT == 2 && local >= groups, grp = local - mat * groups;
+        if (!mbar_wait_bounded(&ctl.full[slot], round & 1, abortFlag)) {  // also leaves when another role raised the abort flag
+          *abortFlag = 1;
+          atomicExch(p.status, kStatusBarrierTimeout);
+          break;
         }
+        const int count = min(kStageBlocks, chunkBlocks - grp * kStageBlocks);
+        if (unit < count && !(p.debug & 2)) {
+          const uint8_t* rows = ring + slot * kStageBytes + laneRow;
+          const int at = (grp * kStageBlocks + unit) * kImageBlockBytes;
+          if (NMAT == 2 && mat)
+            q4k_unit(rows, rows + 8 * kRowPitch, t, laneImage + at, laneSums + at, laneScales + at, total[NMAT - 1]);
+          else
+            q4k_unit(rows, rows + 8 * kRowPitch, t, laneImage + at, laneSums + at, laneScales + at, total[0]);
+        }
+        __syncwarp();
+        if (lane == 0)
+          mbar_arrive(&ctl.empty[slot]);
+      }
+      it += perTile;
+      if (p.debug & 8)  // probe: no reduction, no stores
+        continue;
       // Cross-warp reduction of the K split, then the epilogue.
       float* mine = partial + size_t(tileCounter & 1) * NMAT * kConsumerWarps * 128;
 #pragma unroll
@@ -275,15 +273,17 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
         dst[(2 * t + 1) * 16 + g + 8] = total[mat][3];
       }
       named_barrier(1, kConsumerWarps * kWarp);
-      if (tid < 128) {
-        const int row = tid >> 4, local = tid & 15;
+      // Four warps finish the tile; which four rotates so that no warp falls behind the others.
+      const int finisher = (warp - 4 * tileCounter) & (kConsumerWarps - 1);
+      if (finisher < 4) {
+        const int element = finisher * kWarp + lane, row = element >> 4, local = element & 15;
         float sum[NMAT];
 #pragma unroll
         for (int mat = 0; mat < NMAT; ++mat) {
           sum[mat] = 0.f;
 #pragma unroll
           for (int w = 0; w < kConsumerWarps; ++w)
-            sum[mat] += mine[(mat * kConsumerWarps + w) * 128 + tid];
+            sum[mat] += mine[(mat * kConsumerWarps + w) * 128 + element];
         }
         if (row < p.m) {
           const GemvSeg& seg = p.seg[find_segment(p, tile)];

@@ -65,7 +65,7 @@ def test_q4k_linear_config1_shape(dev, m, integer):
 
 
 def test_integer_kernel_error_level(dev):
-  """15-bit activations per 256-value block: the error sits near 5e-5, far inside the contract."""
+  """16-bit activations per 256-value block: the error sits near 3e-5, far inside the contract."""
   got, want = run_linear(dev, D.Q4_K, 4096, 4096, 8, 41)
   assert 1e-7 < rel_err(got, want) < 2e-4
 
