@@ -87,6 +87,25 @@ int infdev_set_xsplit(infdev_ctx* ctx, int xsplit);
  * 256-value block (error at most 1.6e-5 of the block maximum), 0 = the fp16-MMA kernel. Q6_K always takes the
  * fp16-MMA kernel. Environment: INFENG_INTEGER_DECODE. */
 int infdev_set_integer_decode(infdev_ctx* ctx, int enabled);
+
+/* ---- activation images (no reference counterpart) ----
+ * The integer Q4_K decode kernel reads its activations as an "image": per (row, 256-value block) 16-bit integers
+ * split into a high and a low byte plane in tensor-core fragment order, the block's scale and its sub-block sums;
+ * rows come in 8-row slices of k/256 blocks (4384 bytes per block and slice). A linear call builds the image from
+ * its fp32 activations with one extra small launch; a pass avoids that launch by letting the kernel that produces
+ * the activations write their image as well, and handing it to the linear call that follows. */
+size_t infdev_image_bytes(int64_t rows, int64_t k);
+/* image = quantised x[rows,k] (k a multiple of 256). */
+int infdev_quantize(infdev_ctx* ctx, const float* x, int64_t rows, int64_t k, uint8_t* image);
+/* One-shot: the next infdev_rms_norm, infdev_rms_norm_gather, infdev_delta_rule (gated, rows below 256),
+ * infdev_attention, infdev_linear or infdev_gate_up call on this context also writes the image of its result rows
+ * to `image` (infdev_image_bytes(rows, width of the result) bytes); the fp32 result is written as usual. The norm,
+ * delta-rule and attention kernels write it themselves; a linear call adds a quantisation launch on its result. */
+int infdev_image_capture(infdev_ctx* ctx, uint8_t* image);
+/* One-shot: the next infdev_linear, infdev_linear_group or infdev_gate_up call takes the image of its activations
+ * from `image` (it must be the image of exactly the x passed) instead of quantising x. Only the integer Q4_K kernel
+ * reads images; other kernels ignore the request and read x. */
+int infdev_image_supply(infdev_ctx* ctx, const uint8_t* image);
 /* CUDA-graph capture of a pass on the context's stream (no reference counterpart: Metal re-encodes every
  * pass). begin/end bracket the launches; launch replays; the handle is freed with graph_destroy. */
 int infdev_graph_begin(infdev_ctx* ctx);

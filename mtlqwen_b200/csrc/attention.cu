@@ -15,7 +15,7 @@
 // it runs alone or batched. One CTA serves the four query heads that share a kv head, so K and V are read
 // once per group.
 #include <mutex>
-#include "common.cuh"
+#include "act_image.cuh"
 #include "ops.h"
 
 namespace infdev {
@@ -185,8 +185,9 @@ __global__ void __launch_bounds__(128) attention_scan_kernel(const float* q, con
 }
 
 // grid (rows * 16), 256 threads: merge the splits, normalise, multiply by sigmoid(gate).
+// `image`, when not null, also receives the activation image of the output rows: a head is one 256-value block.
 __global__ void __launch_bounds__(256) attention_reduce_kernel(const float* partials, const float* qg, const infdev_query* queries,
-                                                               uint32_t maxSplits, float* out) {
+                                                               uint32_t maxSplits, float* out, uint8_t* image) {
   const uint32_t headRow = blockIdx.x, row = headRow / kQHeads, dim = threadIdx.x;
   const infdev_query& info = query_of_row(queries, row);
   const uint32_t attended = info.position + (row - info.start) + 1;
@@ -203,7 +204,18 @@ __global__ void __launch_bounds__(256) attention_reduce_kernel(const float* part
     numerator += src[s * kPartialStride + dim] * w;
   }
   const float gate = qg[size_t(headRow) * kDim * 2 + kDim + dim];
-  out[size_t(headRow) * kDim + dim] = (numerator / norm) / (1.0f + expf(-gate));
+  const float value = (numerator / norm) / (1.0f + expf(-gate));
+  out[size_t(headRow) * kDim + dim] = value;
+  if (image) {
+    __shared__ __align__(16) float staged[kDim];
+    staged[dim] = value;
+    __syncthreads();
+    if (dim < 32) {
+      const float4 a = *reinterpret_cast<const float4*>(&staged[dim * 8]), b = *reinterpret_cast<const float4*>(&staged[dim * 8 + 4]);
+      const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+      image_store_block(image + (size_t(row >> 3) * kQHeads + headRow % kQHeads) * kImageBlockBytes, row & 7, dim, v);
+    }
+  }
 }
 
 }  // namespace
@@ -220,13 +232,13 @@ cudaError_t attention_prepare_launch(const float* qg, const float* rawK, const f
 
 cudaError_t attention_launch(const float* q, const float* qg, const void* cacheK, const void* cacheV, const infdev_query* queries,
                              const int32_t* table, int tableStride, int blockTokens, int64_t rows, uint32_t maxSplits, float* partials, float* out,
-                             cudaStream_t stream) {
+                             uint8_t* image, cudaStream_t stream) {
   if (rows <= 0)
     return cudaSuccess;
   attention_scan_kernel<<<dim3(maxSplits, kKvHeads, unsigned(rows)), 128, 0, stream>>>(q, static_cast<const __half*>(cacheK),
                                                                                        static_cast<const __half*>(cacheV), queries, table,
                                                                                        tableStride, blockTokens, maxSplits, partials);
-  attention_reduce_kernel<<<unsigned(rows * kQHeads), 256, 0, stream>>>(partials, qg, queries, maxSplits, out);
+  attention_reduce_kernel<<<unsigned(rows * kQHeads), 256, 0, stream>>>(partials, qg, queries, maxSplits, out, image);
   return cudaGetLastError();
 }
 
@@ -267,7 +279,7 @@ cudaError_t attention_static_launch(const float* q, const float* qg, const void*
   attention_scan_kernel<<<dim3(kStaticSplits, kKvHeads, unsigned(rows)), 128, 0, stream>>>(q, static_cast<const __half*>(cacheK),
                                                                                           static_cast<const __half*>(cacheV), queries, table,
                                                                                           tableStride, blockTokens, kStaticSplits, partials);
-  attention_reduce_kernel<<<unsigned(rows * kQHeads), 256, 0, stream>>>(partials, qg, queries, kStaticSplits, out);
+  attention_reduce_kernel<<<unsigned(rows * kQHeads), 256, 0, stream>>>(partials, qg, queries, kStaticSplits, out, nullptr);
   return cudaGetLastError();
 }
 

@@ -133,11 +133,24 @@ struct Ops {
 
   // One decoder layer in place on `hidden` (Ops::decoder, forward.cpp:77-120). Layers with (layer+1) % 4 == 0
   // and the MTP layer are gated full attention, the others gated delta networks.
+  // Decode-sized passes hand the quantised form of each projection's input from the kernel that produces it to the
+  // GEMV that consumes it, which saves the GEMV its own quantisation launch.
+  void capture(const Tensor& image) {
+    if (rows <= imageRows)
+      check(infdev_image_capture(ctx, image.as<uint8_t>()));
+  }
+  void supply(const Tensor& image) {
+    if (rows <= imageRows)
+      check(infdev_image_supply(ctx, image.as<uint8_t>()));
+  }
+
   void decoder(uint32_t layer, const Tensor& hidden) {
     prefix = "blk." + std::to_string(layer) + ".";
     const bool fullAttention = layer >= engine.targetLayers || (layer + 1) % fullAttentionInterval == 0;
     const Tensor& x = scratch.norm;
+    capture(scratch.normImage);
     check(infdev_rms_norm(ctx, hidden.as<float>(), f32("attn_norm.weight"), rows, hiddenSize, x.as<float>()));
+    supply(scratch.normImage);
     if (fullAttention) {
       const uint32_t kvLayer = layer < engine.targetLayers ? layer / fullAttentionInterval : engine.kvLayers + layer - engine.targetLayers;
       linearGroup(x, {{&weight("attn_q.weight"), scratch.mixed}, {&weight("attn_k.weight"), scratch.k}, {&weight("attn_v.weight"), scratch.v}}, rows);
@@ -145,10 +158,12 @@ struct Ops {
                                      f32("attn_k_norm.weight"), engine.rope.as<float>(), queries, int(queryCount), rows, engine.kv->blockTable(),
                                      int32_t(engine.kv->tableStride()), int32_t(engine.blockTokens), scratch.attnQ.as<float>(),
                                      engine.kv->key(kvLayer).as<void>(), engine.kv->value(kvLayer).as<void>()));
+      capture(scratch.temporaryImage);
       check(infdev_attention(ctx, scratch.attnQ.as<float>(), scratch.mixed.as<float>(), engine.kv->key(kvLayer).as<void>(),
                              engine.kv->value(kvLayer).as<void>(), queries, int(queryCount), rows, engine.kv->blockTable(),
                              int32_t(engine.kv->tableStride()), int32_t(engine.blockTokens), maxAttentionSplits, scratch.attnPartials.as<float>(),
                              scratch.temporary.as<float>()));
+      supply(scratch.temporaryImage);
       linear(scratch.temporary, weight("attn_output.weight"), rows, hidden, hidden);
     } else {
       linearGroup(x, {{&weight("attn_qkv.weight"), scratch.mixed}, {&weight("attn_gate.weight"), scratch.gate}}, rows);
@@ -157,14 +172,20 @@ struct Ops {
                                f32("ssm_dt.bias"), f32("ssm_conv1d.weight"), queries, int(queryCount), rows, offset, engine.stateBytes,
                                scratch.q.as<float>(), scratch.k.as<float>(), scratch.v.as<float>(), scratch.gdnB.as<float>(),
                                scratch.gdnG.as<float>()));
+      capture(scratch.temporaryImage);
       check(infdev_delta_rule(ctx, scratch.q.as<float>(), scratch.k.as<float>(), scratch.v.as<float>(), scratch.gdnG.as<float>(),
                               scratch.gdnB.as<float>(), scratch.gate.as<float>(), f32("ssm_norm.weight"), queries, int(queryCount),
                               offset + INFDEV_CONV_STATE_BYTES, engine.stateBytes, scratch.temporary.as<float>()));
+      supply(scratch.temporaryImage);
       linear(scratch.temporary, weight("ssm_out.weight"), rows, hidden, hidden);
     }
+    capture(scratch.normImage);
     check(infdev_rms_norm(ctx, hidden.as<float>(), f32("post_attention_norm.weight"), rows, hiddenSize, x.as<float>()));
     Weight &gate = weight("ffn_gate.weight"), &up = weight("ffn_up.weight");
+    supply(scratch.normImage);
+    capture(scratch.mlpImage);
     check(infdev_gate_up(ctx, int(gate.type), gate.as<void>(), up.as<void>(), gate.n, gate.k, x.as<float>(), rows, scratch.mlpGate.as<float>()));
+    supply(scratch.mlpImage);
     linear(scratch.mlpGate, weight("ffn_down.weight"), rows, hidden, hidden);
   }
 
@@ -221,6 +242,9 @@ void Engine::loadModel(const std::filesystem::path& path, const std::filesystem:
   s.attnPartials = device.empty(infdev_attention_scratch_bytes(maxBatchTokens, maxAttentionSplits));
   s.targetLogits = device.empty(uint64_t(maxLogitRows) * vocab * sizeof(float));
   s.rowTokens = device.empty(maxBatchTokens * sizeof(int32_t));
+  s.normImage = device.empty(infdev_image_bytes(imageRows, hiddenSize));
+  s.temporaryImage = device.empty(infdev_image_bytes(imageRows, hiddenSize));
+  s.mlpImage = device.empty(infdev_image_bytes(imageRows, intermediateSize));
   rope = device.empty(uint64_t(maxContext) * 32 * 2 * sizeof(float));
   device.check(infdev_rope_table(device.ctx, maxContext, rope.as<float>()));
 }

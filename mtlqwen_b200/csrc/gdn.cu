@@ -9,7 +9,8 @@
 // CTA (256 threads x 64 values): it is read from HBM once, updated for every token of the query, and
 // written once (or once per token for speculative queries, whose every row must stay selectable). The
 // reference makes two passes over the state in device memory per token (delta_rule.metal:320-333, 351-360).
-#include "common.cuh"
+#include "act_image.cuh"
+#include "kernels.h"
 #include "ops.h"
 
 namespace infdev {
@@ -77,9 +78,12 @@ __global__ void __launch_bounds__(256) gdn_conv_kernel(const float* mixed, const
 
 // grid (32 value heads, queries), 256 threads. Thread (part = tid/32, lane) owns S[k][4*lane .. 4*lane+3]
 // for k = part + 8*i, i < 16.
+// `image`, when not null, also receives the activation image of `out`. A 256-value block holds two heads, which two
+// CTAs produce: each adds one to the block's entry in `counters` (zero between launches) after its stores, and the
+// second to arrive reads both halves back and writes the block's image, then clears the entry.
 __global__ void __launch_bounds__(256) delta_rule_kernel(const float* q, const float* k, const float* v, const float* g, const float* beta,
                                                          const float* z, const float* normWeight, const infdev_query* queries,
-                                                         uint64_t stateOffset, uint64_t stateBytes, float* out) {
+                                                         uint64_t stateOffset, uint64_t stateBytes, float* out, uint8_t* image, int* counters) {
   const infdev_query info = queries[blockIdx.y];
   const int head = blockIdx.x, keyHead = head % kKeyHeads, tid = threadIdx.x, part = tid >> 5, lane = tid & 31;
   const bool speculative = info.state != kUnbound;
@@ -174,6 +178,25 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(const float* q, const f
         dst[(part + 8 * i) * 32 + lane] = S[i];
     }
     __syncthreads();  // qs/ks/delta/red are rewritten by the next token
+    if (image && row < kImageCounters / (kValueHeads / 2)) {  // block-uniform; later rows have no counter and get no image
+      __shared__ int arrivals;
+      const int entry = int(row) * (kValueHeads / 2) + (head >> 1);
+      if (tid == 0) {
+        __threadfence();  // this CTA's stores to `out` (ordered by the barrier above) before the count
+        arrivals = atomicAdd(&counters[entry], 1);
+      }
+      __syncthreads();
+      if (arrivals == 1 && tid < 32) {
+        __threadfence();
+        const float* src = out + (row * kValueHeads + (head & ~1)) * kHeadDim + tid * 8;
+        const float4 a = __ldcg(reinterpret_cast<const float4*>(src)), b = __ldcg(reinterpret_cast<const float4*>(src + 4));
+        const float values[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        image_store_block(image + (size_t(row >> 3) * (kValueHeads / 2) + (head >> 1)) * kImageBlockBytes, int(row & 7), tid, values);
+        if (tid == 0)
+          counters[entry] = 0;
+      }
+      __syncthreads();  // `arrivals` is rewritten by the next token
+    }
   }
 }
 
@@ -191,11 +214,11 @@ cudaError_t gdn_prepare_launch(const float* x, const float* mixed, const float* 
 
 cudaError_t delta_rule_launch(const float* q, const float* k, const float* v, const float* g, const float* beta, const float* z,
                               const float* normWeight, const infdev_query* queries, int queryCount, uint64_t stateOffset, uint64_t stateBytes,
-                              float* out, cudaStream_t stream) {
+                              float* out, uint8_t* image, int* counters, cudaStream_t stream) {
   if (queryCount <= 0)
     return cudaSuccess;
   delta_rule_kernel<<<dim3(kValueHeads, unsigned(queryCount)), 256, 0, stream>>>(q, k, v, g, beta, z, normWeight, queries, stateOffset, stateBytes,
-                                                                                  out);
+                                                                                  out, image, counters);
   return cudaGetLastError();
 }
 

@@ -19,6 +19,9 @@ struct infdev_ctx {
   int device = 0, sms = 0, xsplit = 2, debug = 0, umma = 1;  // umma: 0 never, 1 for more than 8 rows, 2 always
   int integerDecode = 1;     // Q4_K decode GEMV: 1 integer-MMA kernel over an activation image, 0 fp16-MMA kernel
   uint8_t* image = nullptr;  // activation image for the integer decode kernel (K up to 16384)
+  int* imageCounters = nullptr;        // arrival counters of the kernels that write images block by block (zero between launches)
+  uint8_t* captureImage = nullptr;     // one-shot: where the next producer call writes the image of its result
+  const uint8_t* supplyImage = nullptr;  // one-shot: image the next linear call reads instead of quantising x
   void* ummaActs = nullptr;  // prepared activations + sums for the tcgen05 path (K up to 16384)
   float* ummaSums = nullptr;
   std::atomic<uint64_t> launches{0};  // kernels launched through this context
@@ -55,6 +58,18 @@ struct Bind {  // makes the context's device current for the calling thread
 };
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// The one-shot image requests are consumed by the first call that could honour them, whether or not it does.
+uint8_t* take_capture(infdev_ctx* ctx) {
+  uint8_t* image = ctx->captureImage;
+  ctx->captureImage = nullptr;
+  return image;
+}
+const uint8_t* take_supply(infdev_ctx* ctx) {
+  const uint8_t* image = ctx->supplyImage;
+  ctx->supplyImage = nullptr;
+  return image;
+}
 
 using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -99,6 +114,18 @@ int weight_map(infdev_ctx* ctx, const void* w, int64_t n, int64_t k, int blockBy
   return INFDEV_OK;
 }
 
+// fp32 rows -> activation image, one launch per 8-row slice.
+int quantize_rows(infdev_ctx* ctx, const float* x, int64_t rows, int64_t k, uint8_t* image) {
+  for (int64_t row = 0; row < rows; row += 8) {
+    if (int r = check(ctx, infdev::activation_image_launch(x + row * k, int(k), int(rows - row < 8 ? rows - row : 8), int(k),
+                                                           image + size_t(row / 8) * size_t(k / 256) * infdev::kActivationImageBlockBytes, ctx->stream),
+                      "activation image"))
+      return r;
+    ++ctx->launches;
+  }
+  return INFDEV_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -138,6 +165,8 @@ infdev_ctx* infdev_create(int device, char* error) {
       (e = cudaMalloc(reinterpret_cast<void**>(&ctx->status), sizeof(int))) != cudaSuccess ||
       (e = cudaMemset(ctx->status, 0, sizeof(int))) != cudaSuccess ||
       (e = cudaMalloc(reinterpret_cast<void**>(&ctx->image), size_t(64) * infdev::kActivationImageBlockBytes)) != cudaSuccess ||
+      (e = cudaMalloc(reinterpret_cast<void**>(&ctx->imageCounters), infdev::kImageCounters * sizeof(int))) != cudaSuccess ||
+      (e = cudaMemset(ctx->imageCounters, 0, infdev::kImageCounters * sizeof(int))) != cudaSuccess ||
       (e = cudaMalloc(&ctx->ummaActs, size_t(64) * infdev::kUmmaMaxActBytesPerBlock)) != cudaSuccess ||
       (e = cudaMalloc(reinterpret_cast<void**>(&ctx->ummaSums), size_t(64) * 64 * sizeof(float))) != cudaSuccess ||
       (e = cudaHostAlloc(reinterpret_cast<void**>(&ctx->statusHost), sizeof(int), cudaHostAllocDefault)) != cudaSuccess) {
@@ -160,6 +189,7 @@ void infdev_destroy(infdev_ctx* ctx) {
     cudaFree(ctx->flush);
   cudaFree(ctx->status);
   cudaFree(ctx->image);
+  cudaFree(ctx->imageCounters);
   cudaFree(ctx->ummaActs);
   cudaFree(ctx->ummaSums);
   cudaFreeHost(ctx->statusHost);
@@ -310,6 +340,31 @@ int infdev_set_umma(infdev_ctx* ctx, int enabled) {
   return INFDEV_OK;
 }
 
+size_t infdev_image_bytes(int64_t rows, int64_t k) {
+  return size_t((rows + 7) / 8) * size_t(k / 256) * infdev::kActivationImageBlockBytes;
+}
+
+int infdev_quantize(infdev_ctx* ctx, const float* x, int64_t rows, int64_t k, uint8_t* image) {
+  Bind bind(ctx);
+  if (rows < 0 || k <= 0 || k % 256 || !aligned16(x) || !aligned16(image))
+    return fail(ctx, INFDEV_E_ARGUMENT, "quantize: k must be a positive multiple of 256 and buffers 16-byte aligned");
+  return quantize_rows(ctx, x, rows, k, image);
+}
+
+int infdev_image_capture(infdev_ctx* ctx, uint8_t* image) {
+  if (!aligned16(image))
+    return fail(ctx, INFDEV_E_ARGUMENT, "image_capture: the image must be 16-byte aligned");
+  ctx->captureImage = image;
+  return INFDEV_OK;
+}
+
+int infdev_image_supply(infdev_ctx* ctx, const uint8_t* image) {
+  if (!aligned16(image))
+    return fail(ctx, INFDEV_E_ARGUMENT, "image_supply: the image must be 16-byte aligned");
+  ctx->supplyImage = image;
+  return INFDEV_OK;
+}
+
 int infdev_set_integer_decode(infdev_ctx* ctx, int enabled) {
   ctx->integerDecode = enabled != 0;
   return INFDEV_OK;
@@ -365,9 +420,9 @@ int infdev_dequant(infdev_ctx* ctx, int type, const void* blocks, int64_t count,
   return check(ctx, infdev::dequant_launch(type, blocks, count, out, ctx->stream), "dequant");
 }
 
-static int linear_common(infdev_ctx* ctx, int type, bool pair, int count, const void* const* w, const void* const* w2, const int64_t* n, int64_t k,
-                         const float* x, int64_t m, float* const* y, const float* const* residual) {
-  Bind bind(ctx);
+// `supplied`: image of x to read instead of quantising it (integer kernel only).
+static int linear_run(infdev_ctx* ctx, int type, bool pair, int count, const void* const* w, const void* const* w2, const int64_t* n, int64_t k,
+                      const float* x, int64_t m, float* const* y, const float* const* residual, const uint8_t* supplied) {
   if (type != INFDEV_Q4_K && type != INFDEV_Q6_K)
     return fail(ctx, INFDEV_E_ARGUMENT, "linear: weight type must be Q4_K or Q6_K");
   if (pair && type != INFDEV_Q4_K)
@@ -449,12 +504,17 @@ static int linear_common(infdev_ctx* ctx, int type, bool pair, int count, const 
       p.seg[i].res = residual && residual[i] ? residual[i] + row * n[i] : nullptr;
     }
     if (integer) {
-      p.image = ctx->image;
-      if (int r = check(ctx, infdev::activation_image_launch(p.x, p.ldx, p.m, p.k, ctx->image, ctx->stream), "activation image"))
-        return r;
+      if (supplied) {  // 8-row slices of k/256 blocks
+        p.image = supplied + size_t(row / 8) * size_t(k / 256) * infdev::kActivationImageBlockBytes;
+      } else {
+        p.image = ctx->image;
+        if (int r = check(ctx, infdev::activation_image_launch(p.x, p.ldx, p.m, p.k, ctx->image, ctx->stream), "activation image"))
+          return r;
+        ++ctx->launches;
+      }
       if (int r = check(ctx, infdev::q4k_decode_launch(pair, p, ctx->sms, ctx->stream), "q4k decode launch"))
         return r;
-      ctx->launches += 2;
+      ++ctx->launches;
       continue;
     }
     if (int r = check(ctx, infdev::gemv_launch(type, pair, ctx->xsplit, p, ctx->sms, ctx->stream), "gemv launch"))
@@ -462,6 +522,20 @@ static int linear_common(infdev_ctx* ctx, int type, bool pair, int count, const 
     ++ctx->launches;
   }
   return INFDEV_OK;
+}
+
+static int linear_common(infdev_ctx* ctx, int type, bool pair, int count, const void* const* w, const void* const* w2, const int64_t* n, int64_t k,
+                         const float* x, int64_t m, float* const* y, const float* const* residual) {
+  Bind bind(ctx);
+  const uint8_t* supplied = take_supply(ctx);
+  uint8_t* captured = take_capture(ctx);
+  if (captured && (count != 1 || n[0] % 256))
+    return fail(ctx, INFDEV_E_ARGUMENT, "linear: an image of the result needs a single matrix with n a multiple of 256");
+  if (int r = linear_run(ctx, type, pair, count, w, w2, n, k, x, m, y, residual, supplied))
+    return r;
+  // A GEMV tile is 16 outputs wide, a 256-value image block spans 16 tiles on different SMs: the image of the result
+  // takes a launch of its own.
+  return captured ? quantize_rows(ctx, y[0], m, n[0], captured) : INFDEV_OK;
 }
 
 int infdev_linear(infdev_ctx* ctx, int type, const void* w, int64_t n, int64_t k, const float* x, int64_t m, float* y, const float* residual) {
@@ -500,14 +574,17 @@ int infdev_rms_norm(infdev_ctx* ctx, const float* x, const float* w, int64_t row
   if (dim % 4 || !aligned16(x) || !aligned16(w) || !aligned16(y))
     return fail(ctx, INFDEV_E_ARGUMENT, "rms_norm: dim must be a multiple of 4 and buffers 16-byte aligned");
   ctx->launches += 1;
-  return check(ctx, infdev::rms_norm_launch(x, w, nullptr, rows, dim, y, ctx->stream), "rms_norm");
+  uint8_t* image = take_capture(ctx);
+  if (image && dim % 256)
+    return fail(ctx, INFDEV_E_ARGUMENT, "rms_norm: an image needs dim to be a multiple of 256");
+  return check(ctx, infdev::rms_norm_launch(x, w, nullptr, rows, dim, y, image, ctx->stream), "rms_norm");
 }
 
 int infdev_rms_norm_gather(infdev_ctx* ctx, const float* x, const float* w, const infdev_query* queries, int queryCount, int64_t count, float* y) {
   Bind bind(ctx);
   (void)queryCount;
   ctx->launches += 1;
-  return check(ctx, infdev::rms_norm_launch(x, w, queries, count, 4096, y, ctx->stream), "rms_norm_gather");
+  return check(ctx, infdev::rms_norm_launch(x, w, queries, count, 4096, y, take_capture(ctx), ctx->stream), "rms_norm_gather");
 }
 
 // ---- gated delta rule --------------------------------------------------------------------------
@@ -532,7 +609,9 @@ int infdev_delta_rule(infdev_ctx* ctx, const float* q, const float* k, const flo
   if (stateOffset % 16 || stateBytes % 16)
     return fail(ctx, INFDEV_E_ARGUMENT, "delta_rule: state offsets must be multiples of 16 bytes");
   ctx->launches += 1;
-  return check(ctx, infdev::delta_rule_launch(q, k, v, g, beta, z, normWeight, queries, queryCount, stateOffset, stateBytes, out, ctx->stream),
+  return check(ctx,
+               infdev::delta_rule_launch(q, k, v, g, beta, z, normWeight, queries, queryCount, stateOffset, stateBytes, out, take_capture(ctx), ctx->imageCounters,
+                                         ctx->stream),
                "delta_rule");
 }
 
@@ -576,7 +655,8 @@ int infdev_attention(infdev_ctx* ctx, const float* q, const float* qg, const voi
     return fail(ctx, INFDEV_E_ARGUMENT, "attention: blockTokens must be a multiple of 16 and maxSplits in 1..64");
   ctx->launches += 2;
   return check(ctx,
-               infdev::attention_launch(q, qg, cacheK, cacheV, queries, table, tableStride, blockTokens, rows, maxSplits, partials, out, ctx->stream),
+               infdev::attention_launch(q, qg, cacheK, cacheV, queries, table, tableStride, blockTokens, rows, maxSplits, partials, out,
+                                        take_capture(ctx), ctx->stream),
                "attention");
 }
 

@@ -34,6 +34,7 @@ constexpr int kGemvStageBlocks = 8, kGemvTileRows = 16;
 // memory 1184 = 32 (mod 128) bytes: the 32-byte pieces of consecutive rows that a warp reads in one load then fall
 // into different banks.
 constexpr int kDecodePadBytes = 32;
+constexpr int kImageCounters = 4096;  // arrival counters a context owns for block-wise image writers
 constexpr int kActivationImageBlockBytes = 4384;  // act_image.cuh: image bytes per 256 activations x 8 rows
 
 // ---- tcgen05 path (umma.cu) ----

@@ -1,6 +1,6 @@
 // Small memory-bound kernels of the forward step: block dequantisation, embedding gather, RMS norms and
 // the per-row token selection.
-#include "common.cuh"
+#include "act_image.cuh"
 #include "ops.h"
 
 namespace infdev {
@@ -87,8 +87,10 @@ __global__ void gather_tokens_kernel(const infdev_query* queries, int queryCount
   }
 }
 
+// `image`, when not null, also receives the activation image of the normalised rows (act_image.cuh; needs dim to
+// be a multiple of 256): 8-row slices of dim/256 blocks each.
 template <bool GATHER>
-__global__ void __launch_bounds__(256) rms_norm_kernel(const float* x, const float* w, const infdev_query* queries, int dim, float* y) {
+__global__ void __launch_bounds__(256) rms_norm_kernel(const float* x, const float* w, const infdev_query* queries, int dim, float* y, uint8_t* image) {
   const int row = blockIdx.x;
   const float* src = x + size_t(row) * dim;
   if (GATHER) {
@@ -113,6 +115,24 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float* x, const flo
   }
   __syncthreads();
   const float scale = sums[8];
+  if (image) {
+    // one warp per 256-value block, eight consecutive values per lane: the layout image_store_block wants
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, blocks = dim / 256;
+    uint8_t* slice = image + size_t(row >> 3) * blocks * kImageBlockBytes;
+    for (int block = warp; block < blocks; block += 8) {
+      const int d = block * 256 + lane * 8;
+      const float4 a = *reinterpret_cast<const float4*>(src + d), b = *reinterpret_cast<const float4*>(src + d + 4);
+      const float4 ga = *reinterpret_cast<const float4*>(w + d), gb = *reinterpret_cast<const float4*>(w + d + 4);
+      const float v[8] = {a.x * scale * ga.x, a.y * scale * ga.y, a.z * scale * ga.z, a.w * scale * ga.w,
+                          b.x * scale * gb.x, b.y * scale * gb.y, b.z * scale * gb.z, b.w * scale * gb.w};
+      if (y) {
+        *reinterpret_cast<float4*>(y + size_t(row) * dim + d) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(y + size_t(row) * dim + d + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      }
+      image_store_block(slice + size_t(block) * kImageBlockBytes, row & 7, lane, v);
+    }
+    return;
+  }
   for (int d = threadIdx.x * 4; d < dim; d += 1024) {
     const float4 v = *reinterpret_cast<const float4*>(src + d), g = *reinterpret_cast<const float4*>(w + d);
     *reinterpret_cast<float4*>(y + size_t(row) * dim + d) = make_float4(v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w);
@@ -207,13 +227,14 @@ cudaError_t gather_tokens_launch(const infdev_query* queries, int queryCount, co
   return cudaGetLastError();
 }
 
-cudaError_t rms_norm_launch(const float* x, const float* w, const infdev_query* queries, int64_t rows, int64_t dim, float* y, cudaStream_t stream) {
+cudaError_t rms_norm_launch(const float* x, const float* w, const infdev_query* queries, int64_t rows, int64_t dim, float* y, uint8_t* image,
+                            cudaStream_t stream) {
   if (rows <= 0)
     return cudaSuccess;
   if (queries)
-    rms_norm_kernel<true><<<unsigned(rows), 256, 0, stream>>>(x, w, queries, int(dim), y);
+    rms_norm_kernel<true><<<unsigned(rows), 256, 0, stream>>>(x, w, queries, int(dim), y, image);
   else
-    rms_norm_kernel<false><<<unsigned(rows), 256, 0, stream>>>(x, w, nullptr, int(dim), y);
+    rms_norm_kernel<false><<<unsigned(rows), 256, 0, stream>>>(x, w, nullptr, int(dim), y, image);
   return cudaGetLastError();
 }
 

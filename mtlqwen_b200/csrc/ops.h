@@ -10,7 +10,8 @@ cudaError_t dequant_launch(int type, const void* blocks, int64_t count, float* o
 cudaError_t embedding_launch(int type, const void* table, int64_t k, const int32_t* tokens, int64_t rows, float* out, cudaStream_t stream);
 cudaError_t gather_tokens_launch(const infdev_query* queries, int queryCount, const int32_t* requestData, uint32_t capacity,
                                  const int32_t* proposals, uint32_t mode, int32_t* rowTokens, cudaStream_t stream);
-cudaError_t rms_norm_launch(const float* x, const float* w, const infdev_query* queries, int64_t rows, int64_t dim, float* y, cudaStream_t stream);
+cudaError_t rms_norm_launch(const float* x, const float* w, const infdev_query* queries, int64_t rows, int64_t dim, float* y, uint8_t* image,
+                            cudaStream_t stream);
 
 cudaError_t mtp_fuse_launch(const float* embedding, const float* hidden, const infdev_query* queries, const float* enorm, const float* hnorm,
                             int64_t rows, uint32_t mode, uint64_t seedOffset, uint64_t stateBytes, float* y, cudaStream_t stream);
@@ -19,13 +20,13 @@ cudaError_t gdn_prepare_launch(const float* x, const float* mixed, const float* 
                                float* q, float* k, float* v, float* beta, float* g, cudaStream_t stream);
 cudaError_t delta_rule_launch(const float* q, const float* k, const float* v, const float* g, const float* beta, const float* z,
                               const float* normWeight, const infdev_query* queries, int queryCount, uint64_t stateOffset, uint64_t stateBytes,
-                              float* out, cudaStream_t stream);
+                              float* out, uint8_t* image, int* counters, cudaStream_t stream);
 cudaError_t attention_prepare_launch(const float* qg, const float* rawK, const float* rawV, const float* qNorm, const float* kNorm, const float* rope,
                                      const infdev_query* queries, const int32_t* table, int tableStride, int blockTokens, int64_t rows, float* q,
                                      void* cacheK, void* cacheV, cudaStream_t stream);
 cudaError_t attention_launch(const float* q, const float* qg, const void* cacheK, const void* cacheV, const infdev_query* queries,
                              const int32_t* table, int tableStride, int blockTokens, int64_t rows, uint32_t maxSplits, float* partials, float* out,
-                             cudaStream_t stream);
+                             uint8_t* image, cudaStream_t stream);
 cudaError_t attention_static_launch(const float* q, const float* qg, const void* cacheK, const void* cacheV, const infdev_query* queries,
                                     const int32_t* table, int tableStride, int blockTokens, int64_t rows, int device, float* out,
                                     cudaStream_t stream);

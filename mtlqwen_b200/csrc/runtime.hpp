@@ -38,7 +38,11 @@ struct Scratch {
   Tensor mixed, gate, q, k, v, attnQ, attnPartials;
   Tensor gdnB, gdnG;
   Tensor fused, targetLogits, rowTokens;
+  // Activation images (infdev_image_capture / infdev_image_supply) of norm, temporary and mlpGate for passes of at
+  // most imageRows rows, where the integer decode GEMV consumes them.
+  Tensor normImage, temporaryImage, mlpImage;
 };
+constexpr uint32_t imageRows = 8;
 
 struct PhysicalBlock {
   uint32_t refs = 0;

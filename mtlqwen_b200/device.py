@@ -55,6 +55,10 @@ def library():
     "infdev_flush_l2": (i32, (vp, )),
     "infdev_set_xsplit": (i32, (vp, i32)),
     "infdev_set_integer_decode": (i32, (vp, i32)),
+    "infdev_image_bytes": (ctypes.c_size_t, (i64, i64)),
+    "infdev_quantize": (i32, (vp, vp, i64, i64, vp)),
+    "infdev_image_capture": (i32, (vp, vp)),
+    "infdev_image_supply": (i32, (vp, vp)),
     "infdev_set_umma": (i32, (vp, i32)),
     "infdev_profiler_range": (i32, (vp, i32)),
     "infdev_graph_begin": (i32, (vp, )),
@@ -185,6 +189,21 @@ class Device:
 
   def set_integer_decode(self, enabled):
     self.check(self.lib.infdev_set_integer_decode(self.ctx, int(enabled)))
+
+  # ---- activation images ----
+  def image_bytes(self, rows, k):
+    return self.lib.infdev_image_bytes(rows, k)
+
+  def quantize(self, x, rows, k, image):
+    self.check(self.lib.infdev_quantize(self.ctx, x.ptr, rows, k, image.ptr))
+
+  def image_capture(self, image):
+    """The next producer call also writes the image of its result."""
+    self.check(self.lib.infdev_image_capture(self.ctx, image.ptr))
+
+  def image_supply(self, image):
+    """The next linear call reads this image instead of quantising its activations."""
+    self.check(self.lib.infdev_image_supply(self.ctx, image.ptr))
 
   # ---- kernels ----
   def dequant(self, qtype, blocks, count, out):

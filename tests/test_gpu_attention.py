@@ -4,6 +4,7 @@ import pytest
 
 import oracle
 from mtlqwen_b200 import device as D
+from mtlqwen_b200 import images
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-3  # BASELINE: attention outputs within 1e-3 relative error in fp32 accumulation
@@ -56,8 +57,14 @@ def run_attention(dev, rng, contexts, counts, block_tokens, max_splits=32):
   partials = dev.empty(dev.attention_scratch_bytes(rows, max_splits) // 4)
   dev.attention_prepare(dqg, dev.array(k), dev.array(v), dev.array(q_norm), dev.array(k_norm), rope, dq, nq, rows, dtable, stride, block_tokens,
                         q_out, dkeys, dvalues)
+  # The reduce kernel also writes the quantised image of its output when asked; it must equal the quantisation of `out`.
+  image, want_image = dev.empty(dev.image_bytes(rows, 4096), np.uint8), dev.empty(dev.image_bytes(rows, 4096), np.uint8)
+  dev.image_capture(image)
   dev.attention(q_out, dqg, dkeys, dvalues, dq, nq, rows, dtable, stride, block_tokens, max_splits, partials, out)
+  dev.quantize(out, rows, 4096, want_image)
   dev.commit()
+  for a, b in zip(images.decode(image.download(), rows, 4096), images.decode(want_image.download(), rows, 4096)):
+    assert a.tobytes() == b.tobytes()
   # oracle: same prepare, fp16 rounding at the cache, exact softmax
   rope_host = oracle.rope_table(max_context)
   assert rope.download().tobytes() == rope_host.tobytes()

@@ -4,6 +4,7 @@ import pytest
 
 import oracle
 from mtlqwen_b200 import device as D
+from mtlqwen_b200 import images
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-3  # BASELINE: GDN outputs within 1e-3 relative error in fp32 accumulation
@@ -53,8 +54,16 @@ def run_layer(dev, rng, lengths, fresh=(), speculative=()):
   beta, g, out = dev.empty((rows, 32)), dev.empty((rows, 32)), dev.empty((rows, 32, 128))
   dev.gdn_prepare(dev.array(x), dev.array(mixed), bufs["w_beta"], bufs["w_alpha"], bufs["ssm_a"], bufs["ssm_dt"], bufs["conv"], dq, nq, rows, 0,
                   LAYER, q_out, k_out, v_out, beta, g)
+  # The kernel also writes the quantised image of its output when asked; it must equal the quantisation of `out`.
+  image, want_image = dev.empty(dev.image_bytes(rows, 4096), np.uint8), dev.empty(dev.image_bytes(rows, 4096), np.uint8)
+  if rows < 256:
+    dev.image_capture(image)
   dev.delta_rule(q_out, k_out, v_out, g, beta, dev.array(z), bufs["norm"], dq, nq, D.CONV_STATE_BYTES, LAYER, out)
+  dev.quantize(out, rows, 4096, want_image)
   dev.commit()
+  if rows < 256:
+    for a, b in zip(images.decode(image.download(), rows, 4096), images.decode(want_image.download(), rows, 4096)):
+      assert a.tobytes() == b.tobytes()
   got_out, got_next, got_cand = out.download(), next_.download(), candidates.download()
   worst, start, cand = 0.0, 0, 0
   for i, count in enumerate(lengths):
