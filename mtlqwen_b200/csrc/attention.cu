@@ -44,6 +44,8 @@ __global__ void __launch_bounds__(256) attention_prepare_kernel(const float* qg,
                                                                 const float* kNorm, const float* rope, const infdev_query* queries,
                                                                 const int32_t* table, int tableStride, int blockTokens, float* q, __half* cacheK,
                                                                 __half* cacheV) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x / 20, head = blockIdx.x % 20, lane = threadIdx.x;
   const bool query = head < kQHeads;
   if (query && !qg)  // K/V store only (mtp_store_kv, attention.metal:53-100)
@@ -88,6 +90,8 @@ __global__ void __launch_bounds__(256) attention_prepare_kernel(const float* qg,
 __global__ void __launch_bounds__(128) attention_scan_kernel(const float* q, const __half* cacheK, const __half* cacheV,
                                                              const infdev_query* queries, const int32_t* table, int tableStride, int blockTokens,
                                                              uint32_t maxSplits, float* partials) {
+  pdl_launch_dependents();
+  pdl_wait();
   const uint32_t split = blockIdx.x, kvHead = blockIdx.y, row = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const infdev_query& info = query_of_row(queries, row);
@@ -188,6 +192,8 @@ __global__ void __launch_bounds__(128) attention_scan_kernel(const float* q, con
 // `image`, when not null, also receives the activation image of the output rows: a head is one 256-value block.
 __global__ void __launch_bounds__(256) attention_reduce_kernel(const float* partials, const float* qg, const infdev_query* queries,
                                                                uint32_t maxSplits, float* out, uint8_t* image) {
+  pdl_launch_dependents();
+  pdl_wait();
   const uint32_t headRow = blockIdx.x, row = headRow / kQHeads, dim = threadIdx.x;
   const infdev_query& info = query_of_row(queries, row);
   const uint32_t attended = info.position + (row - info.start) + 1;
@@ -225,7 +231,7 @@ cudaError_t attention_prepare_launch(const float* qg, const float* rawK, const f
                                      void* cacheK, void* cacheV, cudaStream_t stream) {
   if (rows <= 0)
     return cudaSuccess;
-  attention_prepare_kernel<<<unsigned(rows * 20), 256, 0, stream>>>(qg, rawK, rawV, qNorm, kNorm, rope, queries, table, tableStride, blockTokens, q,
+  launch_kernel(attention_prepare_kernel, unsigned(rows * 20), 256, 0, stream, qg, rawK, rawV, qNorm, kNorm, rope, queries, table, tableStride, blockTokens, q,
                                                                      static_cast<__half*>(cacheK), static_cast<__half*>(cacheV));
   return cudaGetLastError();
 }
@@ -235,10 +241,10 @@ cudaError_t attention_launch(const float* q, const float* qg, const void* cacheK
                              uint8_t* image, cudaStream_t stream) {
   if (rows <= 0)
     return cudaSuccess;
-  attention_scan_kernel<<<dim3(maxSplits, kKvHeads, unsigned(rows)), 128, 0, stream>>>(q, static_cast<const __half*>(cacheK),
+  launch_kernel(attention_scan_kernel, dim3(maxSplits, kKvHeads, unsigned(rows)), 128, 0, stream, q, static_cast<const __half*>(cacheK),
                                                                                        static_cast<const __half*>(cacheV), queries, table,
                                                                                        tableStride, blockTokens, maxSplits, partials);
-  attention_reduce_kernel<<<unsigned(rows * kQHeads), 256, 0, stream>>>(partials, qg, queries, maxSplits, out, image);
+  launch_kernel(attention_reduce_kernel, unsigned(rows * kQHeads), 256, 0, stream, partials, qg, queries, maxSplits, out, image);
   return cudaGetLastError();
 }
 
@@ -276,10 +282,10 @@ cudaError_t attention_static_launch(const float* q, const float* qg, const void*
   }
   // Nothing has to start at zero: the reduction reads exactly the (row, head, split) records that the scan of the
   // same call wrote; whatever an earlier call left in the array is never read.
-  attention_scan_kernel<<<dim3(kStaticSplits, kKvHeads, unsigned(rows)), 128, 0, stream>>>(q, static_cast<const __half*>(cacheK),
+  launch_kernel(attention_scan_kernel, dim3(kStaticSplits, kKvHeads, unsigned(rows)), 128, 0, stream, q, static_cast<const __half*>(cacheK),
                                                                                           static_cast<const __half*>(cacheV), queries, table,
                                                                                           tableStride, blockTokens, kStaticSplits, partials);
-  attention_reduce_kernel<<<unsigned(rows * kQHeads), 256, 0, stream>>>(partials, qg, queries, kStaticSplits, out, nullptr);
+  launch_kernel(attention_reduce_kernel, unsigned(rows * kQHeads), 256, 0, stream, partials, qg, queries, kStaticSplits, out, nullptr);
   return cudaGetLastError();
 }
 

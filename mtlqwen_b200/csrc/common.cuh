@@ -12,6 +12,35 @@ constexpr int kWarp = 32;
 // Error codes written to the per-context device status word by kernels that give up on a wait.
 enum DeviceStatus : int { kStatusOk = 0, kStatusBarrierTimeout = 1, kStatusBadArgument = 2 };
 
+// ---- programmatic dependent launch ----
+// Every kernel of a pass is launched with programmatic stream serialisation (launch_kernel below): its CTAs may become
+// resident while the kernel before it in the stream is still running. A kernel lets its successor start early with
+// pdl_launch_dependents() and must call pdl_wait() before it reads anything an earlier kernel wrote or writes
+// anything an earlier kernel may still read; the wait returns once the preceding kernel has completed and its
+// memory is visible. Because each kernel waits, completion is transitive along the stream. Both are no-ops in a
+// kernel launched without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Set once per process from INFENG_PDL: 0 no kernel is launched early, 1 every kernel, 2 only the weight-streaming
+// GEMV kernels (which use the time to fill their shared-memory ring).
+int pdl_mode();
+
+template <bool STREAMING = false, class... Params, class... Args>
+cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t sharedBytes, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = sharedBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = (pdl_mode() == 1 || (pdl_mode() == 2 && STREAMING)) ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -28,6 +28,8 @@ __device__ __forceinline__ const infdev_query& query_of_row(const infdev_query* 
 // grid (32 heads, rows), 64 threads: warp 0 -> beta, warp 1 -> g.
 __global__ void __launch_bounds__(64) gdn_ba_kernel(const float* x, const float* wBeta, const float* wAlpha, const float* A, const float* dt,
                                                     float* beta, float* g) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int head = blockIdx.x, row = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float* w = (warp ? wAlpha : wBeta) + size_t(head) * 4096;
   const float* src = x + size_t(row) * 4096;
@@ -48,6 +50,8 @@ __global__ void __launch_bounds__(64) gdn_ba_kernel(const float* x, const float*
 // One thread per (row, channel). State layout: conv taps fp32 [8192][4] at record + stateOffset.
 __global__ void __launch_bounds__(256) gdn_conv_kernel(const float* mixed, const float* w, const infdev_query* queries, int rows,
                                                        uint64_t stateOffset, uint64_t stateBytes, float* q, float* k, float* v) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t tid = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t row = tid / kChannels, c = tid % kChannels;
   if (row >= rows)
@@ -84,6 +88,8 @@ __global__ void __launch_bounds__(256) gdn_conv_kernel(const float* mixed, const
 __global__ void __launch_bounds__(256) delta_rule_kernel(const float* q, const float* k, const float* v, const float* g, const float* beta,
                                                          const float* z, const float* normWeight, const infdev_query* queries,
                                                          uint64_t stateOffset, uint64_t stateBytes, float* out, uint8_t* image, int* counters) {
+  pdl_launch_dependents();
+  pdl_wait();
   const infdev_query info = queries[blockIdx.y];
   const int head = blockIdx.x, keyHead = head % kKeyHeads, tid = threadIdx.x, part = tid >> 5, lane = tid & 31;
   const bool speculative = info.state != kUnbound;
@@ -207,8 +213,8 @@ cudaError_t gdn_prepare_launch(const float* x, const float* mixed, const float* 
                                float* q, float* k, float* v, float* beta, float* g, cudaStream_t stream) {
   if (rows <= 0)
     return cudaSuccess;
-  gdn_ba_kernel<<<dim3(kValueHeads, unsigned(rows)), 64, 0, stream>>>(x, wBeta, wAlpha, A, dt, beta, g);
-  gdn_conv_kernel<<<unsigned(rows * kChannels / 256), 256, 0, stream>>>(mixed, convWeight, queries, int(rows), stateOffset, stateBytes, q, k, v);
+  launch_kernel(gdn_ba_kernel, dim3(kValueHeads, unsigned(rows)), 64, 0, stream, x, wBeta, wAlpha, A, dt, beta, g);
+  launch_kernel(gdn_conv_kernel, unsigned(rows * kChannels / 256), 256, 0, stream, mixed, convWeight, queries, int(rows), stateOffset, stateBytes, q, k, v);
   return cudaGetLastError();
 }
 
@@ -217,7 +223,7 @@ cudaError_t delta_rule_launch(const float* q, const float* k, const float* v, co
                               float* out, uint8_t* image, int* counters, cudaStream_t stream) {
   if (queryCount <= 0)
     return cudaSuccess;
-  delta_rule_kernel<<<dim3(kValueHeads, unsigned(queryCount)), 256, 0, stream>>>(q, k, v, g, beta, z, normWeight, queries, stateOffset, stateBytes,
+  launch_kernel(delta_rule_kernel, dim3(kValueHeads, unsigned(queryCount)), 256, 0, stream, q, k, v, g, beta, z, normWeight, queries, stateOffset, stateBytes,
                                                                                   out, image, counters);
   return cudaGetLastError();
 }

@@ -247,10 +247,11 @@ template <class Q, int NMAT, int XSPLIT> __global__ void __launch_bounds__(kThre
     mbar_fence_init();
   }
   __syncthreads();
+  pdl_launch_dependents();
   volatile int* abortFlag = &ctl.abort;
 
   if (warp == kConsumerWarps) {
-    // ---- producer: stream weight slabs into the ring ----
+    // ---- producer: stream weight slabs into the ring (they do not depend on the kernels before this one) ----
     uint32_t it = 0;
     for (int chunk = 0; chunk < chunks && !*abortFlag; ++chunk) {
       const int chunkBlocks = min(kChunkBlocks, blocksPerRow - chunk * kChunkBlocks);
@@ -284,10 +285,12 @@ template <class Q, int NMAT, int XSPLIT> __global__ void __launch_bounds__(kThre
         }
       }
     }
+    pdl_wait();  // every thread of every kernel waits, so completion stays transitive along the stream
     return;
   }
 
   // ---- consumers ----
+  pdl_wait();  // the activations come from the kernels before this one
   const int g = lane >> 2, t = lane & 3;
   // Shared-memory byte addresses of this lane's B fragments: slot rotated by j inside each 32-entry line.
   const int rotation[4] = {0, (((lane + 1) & 31) - lane) * 8, (((lane + 2) & 31) - lane) * 8, (((lane + 3) & 31) - lane) * 8};
@@ -434,7 +437,7 @@ template <class Q, int NMAT, int XSPLIT> cudaError_t launch(const GemvParams& p,
     configured = true;
   }
   const int grid = p.tiles < sms ? p.tiles : sms;
-  gemv_kernel<Q, NMAT, XSPLIT><<<grid, kThreads, bytes, stream>>>(p);
+  launch_kernel<true>(gemv_kernel<Q, NMAT, XSPLIT>, grid, kThreads, bytes, stream, p);
   return cudaGetLastError();
 }
 

@@ -39,6 +39,16 @@ struct infdev_ctx {
   std::string error;
 };
 
+namespace infdev {
+int pdl_mode() {
+  static const int mode = [] {
+    const char* env = std::getenv("INFENG_PDL");
+    return env ? std::atoi(env) : 2;
+  }();
+  return mode;
+}
+}  // namespace infdev
+
 namespace {
 
 int fail(infdev_ctx* ctx, int code, const std::string& text) {

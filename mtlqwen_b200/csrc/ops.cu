@@ -39,6 +39,8 @@ __device__ __forceinline__ float dequant_q6k_element(const uint8_t* b, int r) {
 }
 
 template <int TYPE> __global__ void dequant_kernel(const uint8_t* blocks, int64_t count, float* out) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int bytes = TYPE == 12 ? 144 : 210;
   const int64_t block = blockIdx.x;
   if (block >= count)
@@ -49,6 +51,8 @@ template <int TYPE> __global__ void dequant_kernel(const uint8_t* blocks, int64_
 }
 
 template <int TYPE> __global__ void embedding_kernel(const uint8_t* table, int blocksPerRow, const int32_t* tokens, float* out) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int bytes = TYPE == 12 ? 144 : 210;
   const int64_t row = blockIdx.y, token = tokens[row];
   const int block = blockIdx.x, r = threadIdx.x;
@@ -70,6 +74,8 @@ __device__ __forceinline__ const infdev_query& query_of_logit(const infdev_query
 
 __global__ void gather_tokens_kernel(const infdev_query* queries, int queryCount, const int32_t* requestData, uint32_t capacity,
                                      const int32_t* proposals, uint32_t mode, int32_t* rowTokens) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int q = blockIdx.x;
   if (q >= queryCount)
     return;
@@ -91,6 +97,8 @@ __global__ void gather_tokens_kernel(const infdev_query* queries, int queryCount
 // be a multiple of 256): 8-row slices of dim/256 blocks each.
 template <bool GATHER>
 __global__ void __launch_bounds__(256) rms_norm_kernel(const float* x, const float* w, const infdev_query* queries, int dim, float* y, uint8_t* image) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   const float* src = x + size_t(row) * dim;
   if (GATHER) {
@@ -146,6 +154,8 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float* x, const flo
 // Mode 1 also stores the target hidden of each candidate row (speculative) or of the last row as the next seed.
 __global__ void __launch_bounds__(256) mtp_fuse_kernel(const float* embedding, const float* hidden, const infdev_query* queries, const float* enorm,
                                                        const float* hnorm, uint32_t mode, uint64_t seedOffset, uint64_t stateBytes, float* y) {
+  pdl_launch_dependents();
+  pdl_wait();
   const uint32_t row = blockIdx.x, tid = threadIdx.x;
   const infdev_query& info = query_of_row(queries, row);
   const uint32_t token = row - info.start;
@@ -194,7 +204,7 @@ cudaError_t mtp_fuse_launch(const float* embedding, const float* hidden, const i
                             int64_t rows, uint32_t mode, uint64_t seedOffset, uint64_t stateBytes, float* y, cudaStream_t stream) {
   if (rows <= 0)
     return cudaSuccess;
-  mtp_fuse_kernel<<<unsigned(rows), 256, 0, stream>>>(embedding, hidden, queries, enorm, hnorm, mode, seedOffset, stateBytes, y);
+  launch_kernel(mtp_fuse_kernel, unsigned(rows), 256, 0, stream, embedding, hidden, queries, enorm, hnorm, mode, seedOffset, stateBytes, y);
   return cudaGetLastError();
 }
 
@@ -202,9 +212,9 @@ cudaError_t dequant_launch(int type, const void* blocks, int64_t count, float* o
   if (count <= 0)
     return cudaSuccess;
   if (type == 12)
-    dequant_kernel<12><<<unsigned(count), 256, 0, stream>>>(static_cast<const uint8_t*>(blocks), count, out);
+    launch_kernel(dequant_kernel<12>, unsigned(count), 256, 0, stream, static_cast<const uint8_t*>(blocks), count, out);
   else
-    dequant_kernel<14><<<unsigned(count), 256, 0, stream>>>(static_cast<const uint8_t*>(blocks), count, out);
+    launch_kernel(dequant_kernel<14>, unsigned(count), 256, 0, stream, static_cast<const uint8_t*>(blocks), count, out);
   return cudaGetLastError();
 }
 
@@ -213,9 +223,9 @@ cudaError_t embedding_launch(int type, const void* table, int64_t k, const int32
     return cudaSuccess;
   const dim3 grid(unsigned(k / 256), unsigned(rows));
   if (type == 12)
-    embedding_kernel<12><<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(table), int(k / 256), tokens, out);
+    launch_kernel(embedding_kernel<12>, grid, 256, 0, stream, static_cast<const uint8_t*>(table), int(k / 256), tokens, out);
   else
-    embedding_kernel<14><<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(table), int(k / 256), tokens, out);
+    launch_kernel(embedding_kernel<14>, grid, 256, 0, stream, static_cast<const uint8_t*>(table), int(k / 256), tokens, out);
   return cudaGetLastError();
 }
 
@@ -223,7 +233,7 @@ cudaError_t gather_tokens_launch(const infdev_query* queries, int queryCount, co
                                  const int32_t* proposals, uint32_t mode, int32_t* rowTokens, cudaStream_t stream) {
   if (queryCount <= 0)
     return cudaSuccess;
-  gather_tokens_kernel<<<queryCount, 128, 0, stream>>>(queries, queryCount, requestData, capacity, proposals, mode, rowTokens);
+  launch_kernel(gather_tokens_kernel, queryCount, 128, 0, stream, queries, queryCount, requestData, capacity, proposals, mode, rowTokens);
   return cudaGetLastError();
 }
 
@@ -232,9 +242,9 @@ cudaError_t rms_norm_launch(const float* x, const float* w, const infdev_query* 
   if (rows <= 0)
     return cudaSuccess;
   if (queries)
-    rms_norm_kernel<true><<<unsigned(rows), 256, 0, stream>>>(x, w, queries, int(dim), y, image);
+    launch_kernel(rms_norm_kernel<true>, unsigned(rows), 256, 0, stream, x, w, queries, int(dim), y, image);
   else
-    rms_norm_kernel<false><<<unsigned(rows), 256, 0, stream>>>(x, w, nullptr, int(dim), y, image);
+    launch_kernel(rms_norm_kernel<false>, unsigned(rows), 256, 0, stream, x, w, nullptr, int(dim), y, image);
   return cudaGetLastError();
 }
 

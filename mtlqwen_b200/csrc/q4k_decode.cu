@@ -156,25 +156,15 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
     mbar_fence_init();
   }
   __syncthreads();
+  pdl_launch_dependents();
   volatile int* abortFlag = &ctl.abort;
 
   if (warp == kConsumerWarps) {
-    // ---- producer: activation image of each K chunk, then its weight slabs ----
+    // ---- producer: weight slabs into the ring, and the activation image of each K chunk ----
+    // The weights do not depend on the kernels before this one, so the ring is filled before the wait for them; the
+    // image does, so the first one is requested after that wait, once the ring is full.
     uint32_t it = 0;
-    for (int chunk = 0; chunk < chunks && !*abortFlag; ++chunk) {
-      const int chunkBlocks = min(kChunkBlocks, blocksPerRow - chunk * kChunkBlocks);
-      const int groups = (chunkBlocks + kStageBlocks - 1) / kStageBlocks;
-      bool ok = true;
-      if (lane == 0 && chunk > 0)  // the consumers have finished with the previous chunk's image
-        ok = mbar_wait_bounded(&ctl.imageEmpty, (chunk - 1) & 1, abortFlag);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) {
-        if (lane == 0) {
-          *abortFlag = 1;
-          atomicExch(p.status, kStatusBarrierTimeout);
-        }
-        break;
-      }
+    auto loadImage = [&](int chunk, int chunkBlocks) {
       if (lane == 0) {
         mbar_arrive_expect_tx(&ctl.imageFull, uint32_t(chunkBlocks) * kImageBlockBytes);
         for (int first = 0; first < chunkBlocks; first += kImagePieceBlocks) {
@@ -184,12 +174,36 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
         }
       }
       __syncwarp();
+    };
+    bool firstImage = false;
+    for (int chunk = 0; chunk < chunks && !*abortFlag; ++chunk) {
+      const int chunkBlocks = min(kChunkBlocks, blocksPerRow - chunk * kChunkBlocks);
+      const int groups = (chunkBlocks + kStageBlocks - 1) / kStageBlocks;
+      bool ok = true;
+      if (chunk > 0) {
+        if (lane == 0)  // the consumers have finished with the previous chunk's image
+          ok = mbar_wait_bounded(&ctl.imageEmpty, (chunk - 1) & 1, abortFlag);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) {
+          if (lane == 0) {
+            *abortFlag = 1;
+            atomicExch(p.status, kStatusBarrierTimeout);
+          }
+          break;
+        }
+        loadImage(chunk, chunkBlocks);
+      }
       for (int tile = blockIdx.x; tile < p.tiles && !*abortFlag; tile += gridDim.x) {
         const int segment = find_segment(p, tile);
         const int row0 = (tile - p.seg[segment].tile0) * kTileRows;
         for (int mat = 0; mat < NMAT; ++mat) {
           for (int grp = 0; grp < groups; ++grp, ++it) {
             const uint32_t slot = it % kStages, round = it / kStages;
+            if (!firstImage && it == kStages) {  // the ring is full; nothing is released before the consumers have an image
+              pdl_wait();
+              loadImage(0, chunkBlocks);
+              firstImage = true;
+            }
             ok = true;
             if (lane == 0 && round > 0)
               ok = mbar_wait_bounded(&ctl.empty[slot], (round - 1) & 1, abortFlag);
@@ -214,11 +228,18 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
           }
         }
       }
+      if (!firstImage) {  // fewer stages than the ring holds
+        pdl_wait();
+        loadImage(0, chunkBlocks);
+        firstImage = true;
+      }
     }
+    pdl_wait();  // every thread of every kernel waits, so completion stays transitive along the stream
     return;
   }
 
   // ---- consumers ----
+  pdl_wait();
   const int g = lane >> 2, t = lane & 3, half = warp / kStageWarps, unit = warp % kStageWarps;
   const uint8_t *laneImage = image + g * 64 + t * 16, *laneSums = image + kImageSumOffset + lane * 8, *laneScales = image + kImageScaleOffset + t * 8;
   const int laneRow = g * kRowPitch + unit * kBlockBytes;
@@ -308,6 +329,8 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
 
 // One warp per (row, 256-value block).
 __global__ void __launch_bounds__(256) activation_image_kernel(const float* x, int ldx, int m, int blocks, uint8_t* image) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int item = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (item >= blocks * kImageRows)
     return;
@@ -333,7 +356,7 @@ template <int NMAT> cudaError_t launch(const GemvParams& p, int sms, cudaStream_
     configured = true;
   }
   const int grid = p.tiles < sms ? p.tiles : sms;
-  q4k_decode_kernel<NMAT><<<grid, kThreads, bytes, stream>>>(p);
+  launch_kernel<true>(q4k_decode_kernel<NMAT>, grid, kThreads, bytes, stream, p);
   return cudaGetLastError();
 }
 
@@ -345,7 +368,7 @@ cudaError_t q4k_decode_launch(bool pair, const GemvParams& p, int sms, cudaStrea
 
 cudaError_t activation_image_launch(const float* x, int ldx, int m, int k, uint8_t* image, cudaStream_t stream) {
   const int blocks = k / 256;
-  activation_image_kernel<<<(blocks * kImageRows + 7) / 8, 256, 0, stream>>>(x, ldx, m, blocks, image);
+  launch_kernel(activation_image_kernel, (blocks * kImageRows + 7) / 8, 256, 0, stream, x, ldx, m, blocks, image);
   return cudaGetLastError();
 }
 

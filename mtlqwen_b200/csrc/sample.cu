@@ -44,6 +44,8 @@ __device__ __forceinline__ uint32_t sortable(float v) {
 // grid (count), 1024 threads. mode 0: target sampling; mode 1: MTP drafting (always argmax, and bumps the
 // drafter query's position, native_ops.metal:128-129).
 __global__ void __launch_bounds__(kThreads) sample_kernel(const float* logits, int vocab, infdev_query* queries, uint32_t mode, int32_t* tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
   const uint32_t i = blockIdx.x;
   const int tid = threadIdx.x;
   const infdev_query info = query_of_logit(queries, i);
@@ -283,6 +285,8 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float* logits, i
 // meta[0] = rows, meta[1] = logit rows, meta[2] = flags (1 sequential, 2 prefill).
 __global__ void pack_queries_kernel(const infdev_query* in, int count, int drafting, uint32_t draftWidth, const uint64_t* statePrevious,
                                     const uint64_t* stateNext, uint64_t candidateBase, uint64_t stateBytes, infdev_query* out, uint32_t* meta) {
+  pdl_launch_dependents();
+  pdl_wait();
   if (threadIdx.x || blockIdx.x)
     return;
   uint32_t rows = 0, logits = 0, flags = 0, packed = 0;
@@ -316,6 +320,8 @@ __global__ void pack_queries_kernel(const infdev_query* in, int count, int draft
 // sampled tokens that equal the next proposal, stopping at a stop token or at draftWidth.
 __global__ void verify_drafts_kernel(const infdev_query* queries, int count, const int32_t* sampled, const int32_t* proposed, uint32_t draftWidth,
                                      const int32_t* stops, const uint32_t* stopOffsets, uint32_t* accepted) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= count)
     return;
@@ -340,6 +346,8 @@ __global__ void verify_drafts_kernel(const infdev_query* queries, int count, con
 // (engine.cpp:217-218), driven by the device-side accepted counts. grid (chunks, queries).
 __global__ void __launch_bounds__(256) commit_states_kernel(const infdev_query* queries, const uint32_t* accepted, const uint64_t* stateNext,
                                                             uint64_t candidateBase, uint64_t stateBytes) {
+  pdl_launch_dependents();
+  pdl_wait();
   const infdev_query& query = queries[blockIdx.y];
   if (query.state == kUnbound)
     return;
@@ -356,14 +364,14 @@ cudaError_t sample_launch(const float* logits, int vocab, infdev_query* queries,
                           cudaStream_t stream) {
   if (count <= 0)
     return cudaSuccess;
-  sample_kernel<<<unsigned(count), kThreads, 0, stream>>>(logits, vocab, queries, mode, tokens);
+  launch_kernel(sample_kernel, unsigned(count), kThreads, 0, stream, logits, vocab, queries, mode, tokens);
   return cudaGetLastError();
 }
 
 cudaError_t pack_queries_launch(const infdev_query* in, int count, int drafting, uint32_t draftWidth, const uint64_t* statePrevious,
                                 const uint64_t* stateNext, uint64_t candidateBase, uint64_t stateBytes, infdev_query* out, uint32_t* meta,
                                 cudaStream_t stream) {
-  pack_queries_kernel<<<1, 32, 0, stream>>>(in, count, drafting, draftWidth, statePrevious, stateNext, candidateBase, stateBytes, out, meta);
+  launch_kernel(pack_queries_kernel, 1, 32, 0, stream, in, count, drafting, draftWidth, statePrevious, stateNext, candidateBase, stateBytes, out, meta);
   return cudaGetLastError();
 }
 
@@ -371,7 +379,7 @@ cudaError_t verify_drafts_launch(const infdev_query* queries, int count, const i
                                  const int32_t* stops, const uint32_t* stopOffsets, uint32_t* accepted, cudaStream_t stream) {
   if (count <= 0)
     return cudaSuccess;
-  verify_drafts_kernel<<<1, 32, 0, stream>>>(queries, count, sampled, proposed, draftWidth, stops, stopOffsets, accepted);
+  launch_kernel(verify_drafts_kernel, 1, 32, 0, stream, queries, count, sampled, proposed, draftWidth, stops, stopOffsets, accepted);
   return cudaGetLastError();
 }
 
@@ -379,7 +387,7 @@ cudaError_t commit_states_launch(const infdev_query* queries, int count, const u
                                  uint64_t candidateBase, uint64_t stateBytes, cudaStream_t stream) {
   if (count <= 0)
     return cudaSuccess;
-  commit_states_kernel<<<dim3(64, unsigned(count)), 256, 0, stream>>>(queries, accepted, stateNext, candidateBase, stateBytes);
+  launch_kernel(commit_states_kernel, dim3(64, unsigned(count)), 256, 0, stream, queries, accepted, stateNext, candidateBase, stateBytes);
   return cudaGetLastError();
 }
 
