@@ -30,10 +30,11 @@ __device__ __forceinline__ const infdev_query& query_of_row(const infdev_query* 
   return *queries;
 }
 
-// Splits of a row that attends to `attended` tokens: 256-token pieces, at most maxSplits, each a multiple of
-// the 16-token tile.
+// Splits of a row that attends to `attended` tokens: 64-token pieces, at most maxSplits, each a multiple of
+// the 16-token tile. A CTA walks its piece tile by tile with dependent loads, so the scan is bound by latency and
+// wants many short pieces in flight rather than few long ones.
 __device__ __forceinline__ void split_range(uint32_t attended, uint32_t maxSplits, uint32_t split, uint32_t& begin, uint32_t& end, uint32_t& count) {
-  count = min(maxSplits, (attended + 255u) / 256u);
+  count = min(maxSplits, (attended + 63u) / 64u);
   const uint32_t per = (((attended + count - 1) / count) + kTile - 1) / kTile * kTile;
   begin = min(attended, split * per);
   end = min(attended, begin + per);

@@ -1,7 +1,7 @@
 // Gated delta-rule (GDN) layer kernels.
 //
-// gdn_ba_kernel     <- gdn_ba_prepare_4096x32 (native_ops.metal:89-113)
-// gdn_conv_kernel   <- gdn_causal_conv_silu   (fused_kernels.metal:202-232)
+// gdn_prepare_kernel <- gdn_ba_prepare_4096x32 (native_ops.metal:89-113) and gdn_causal_conv_silu
+//                      (fused_kernels.metal:202-232) in one launch
 // delta_rule_kernel <- delta_rule_decode (delta_rule.metal:256-363) for every query length, fused with
 //                      gated_rms_norm_128 (fused_kernels.metal:234-254).
 //
@@ -25,37 +25,45 @@ __device__ __forceinline__ const infdev_query& query_of_row(const infdev_query* 
   return *queries;
 }
 
-// grid (32 heads, rows), 64 threads: warp 0 -> beta, warp 1 -> g.
-__global__ void __launch_bounds__(64) gdn_ba_kernel(const float* x, const float* wBeta, const float* wAlpha, const float* A, const float* dt,
-                                                    float* beta, float* g) {
+// gdn_prepare_kernel: both preparation steps of a GDN layer in one launch of 256-thread CTAs.
+//  * CTAs [0, rows * 32): causal conv + SiLU, one thread per (row, channel). State layout: conv taps fp32 [8192][4]
+//    at record + stateOffset.
+//  * CTAs [rows * 32, rows * 64): beta / g of one (row, value head): warps 0..3 share the 4096-long dot product
+//    with wBeta, warps 4..7 the one with wAlpha.
+__global__ void __launch_bounds__(256) gdn_prepare_kernel(const float* x, const float* wBeta, const float* wAlpha, const float* A, const float* dt,
+                                                          const float* mixed, const float* w, const infdev_query* queries, int rows,
+                                                          uint64_t stateOffset, uint64_t stateBytes, float* q, float* k, float* v, float* beta,
+                                                          float* g) {
   pdl_launch_dependents();
   pdl_wait();
-  const int head = blockIdx.x, row = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const float* w = (warp ? wAlpha : wBeta) + size_t(head) * 4096;
-  const float* src = x + size_t(row) * 4096;
-  float sum = 0.f;
-  for (int k = lane * 4; k < 4096; k += 128) {
-    const float4 a = *reinterpret_cast<const float4*>(src + k), b = *reinterpret_cast<const float4*>(w + k);
-    sum += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+  const int convBlocks = rows * (kChannels / 256);
+  if (int(blockIdx.x) >= convBlocks) {
+    const int item = blockIdx.x - convBlocks, brow = item / kValueHeads, head = item % kValueHeads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, which = warp >> 2, quarter = warp & 3;
+    const float* weights = (which ? wAlpha : wBeta) + size_t(head) * 4096 + quarter * 1024;
+    const float* src = x + size_t(brow) * 4096 + quarter * 1024;
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float4 a = *reinterpret_cast<const float4*>(src + i * 128 + lane * 4), b = *reinterpret_cast<const float4*>(weights + i * 128 + lane * 4);
+      sum += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+    }
+    sum = warp_sum(sum);
+    __shared__ float parts[8];
+    if (lane == 0)
+      parts[warp] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const float dot = (parts[0] + parts[1]) + (parts[2] + parts[3]);
+      beta[brow * kValueHeads + head] = 1.0f / (1.0f + expf(-dot));
+    } else if (threadIdx.x == 128) {
+      const float dot = (parts[4] + parts[5]) + (parts[6] + parts[7]);
+      g[brow * kValueHeads + head] = A[head] * logf(1.0f + expf(dot + dt[head]));
+    }
+    return;
   }
-  sum = warp_sum(sum);
-  if (lane == 0) {
-    if (warp == 0)
-      beta[row * kValueHeads + head] = 1.0f / (1.0f + expf(-sum));
-    else
-      g[row * kValueHeads + head] = A[head] * logf(1.0f + expf(sum + dt[head]));
-  }
-}
-
-// One thread per (row, channel). State layout: conv taps fp32 [8192][4] at record + stateOffset.
-__global__ void __launch_bounds__(256) gdn_conv_kernel(const float* mixed, const float* w, const infdev_query* queries, int rows,
-                                                       uint64_t stateOffset, uint64_t stateBytes, float* q, float* k, float* v) {
-  pdl_launch_dependents();
-  pdl_wait();
   const int64_t tid = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t row = tid / kChannels, c = tid % kChannels;
-  if (row >= rows)
-    return;
   const infdev_query& info = query_of_row(queries, uint32_t(row));
   const int64_t p = row - info.start;
   const bool speculative = info.state != kUnbound;
@@ -213,8 +221,8 @@ cudaError_t gdn_prepare_launch(const float* x, const float* mixed, const float* 
                                float* q, float* k, float* v, float* beta, float* g, cudaStream_t stream) {
   if (rows <= 0)
     return cudaSuccess;
-  launch_kernel(gdn_ba_kernel, dim3(kValueHeads, unsigned(rows)), 64, 0, stream, x, wBeta, wAlpha, A, dt, beta, g);
-  launch_kernel(gdn_conv_kernel, unsigned(rows * kChannels / 256), 256, 0, stream, mixed, convWeight, queries, int(rows), stateOffset, stateBytes, q, k, v);
+  launch_kernel(gdn_prepare_kernel, unsigned(rows * (kChannels / 256 + kValueHeads)), 256, 0, stream, x, wBeta, wAlpha, A, dt, mixed, convWeight, queries,
+                int(rows), stateOffset, stateBytes, q, k, v, beta, g);
   return cudaGetLastError();
 }
 

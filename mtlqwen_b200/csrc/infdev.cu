@@ -606,7 +606,7 @@ int infdev_gdn_prepare(infdev_ctx* ctx, const float* x, const float* mixed, cons
   (void)queryCount;
   if (stateOffset % 16 || stateBytes % 16)
     return fail(ctx, INFDEV_E_ARGUMENT, "gdn_prepare: state offsets must be multiples of 16 bytes");
-  ctx->launches += 2;
+  ctx->launches += 1;
   return check(ctx,
                infdev::gdn_prepare_launch(x, mixed, wBeta, wAlpha, ssmA, ssmDt, convWeight, queries, rows, stateOffset, stateBytes, q, k, v, beta, g,
                                           ctx->stream),
