@@ -243,7 +243,7 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
   const int g = lane >> 2, t = lane & 3, half = warp / kStageWarps, unit = warp % kStageWarps;
   const uint8_t *laneImage = image + g * 64 + t * 16, *laneSums = image + kImageSumOffset + lane * 8, *laneScales = image + kImageScaleOffset + t * 8;
   const int laneRow = g * kRowPitch + unit * kBlockBytes;
-  uint32_t it = 0;
+  uint32_t it = 0, mine = half, slot = half, phase = 0;
   int tileCounter = 0;
   for (int chunk = 0; chunk < chunks; ++chunk) {
     const int chunkBlocks = min(kChunkBlocks, blocksPerRow - chunk * kChunkBlocks);
@@ -257,12 +257,32 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
 #pragma unroll
       for (int mat = 0; mat < NMAT; ++mat)
         total[mat][0] = total[mat][1] = total[mat][2] = total[mat][3] = 0.f;
+      // Four warps finish the tile, 32 of its 16 x 8 results each; which four rotates so that no warp falls behind the
+      // others. They fetch what is added to their result (the residual, or the sum over the earlier K chunks) now, so
+      // that the load has long completed when the tile's partial sums are in.
+      const int finisher = (warp - 4 * tileCounter) & (kConsumerWarps - 1), element = finisher * kWarp + lane;
+      float* destination = nullptr;
+      float addend = 0.f;
+      if (finisher < 4 && (element >> 4) < p.m) {
+        const GemvSeg& seg = p.seg[find_segment(p, tile)];
+        const size_t at = size_t(element >> 4) * seg.ldy + size_t(tile - seg.tile0) * kTileRows + (element & 15);
+        destination = seg.y + at;
+        if (NMAT == 1 && chunk > 0)
+          addend = *destination;
+        else if (NMAT == 1 && seg.res)
+          addend = seg.res[at];
+      }
       // Consecutive ring stages alternate between the two halves of the consumer warps.
+      // `mine` is the next stage of this half (they are the stages congruent to `half` modulo 2), `slot` and `phase`
+      // its place in the ring.
       const int perTile = NMAT * groups;
-      for (int local = (half - int(it)) & 1; local < perTile; local += 2) {
-        const uint32_t stage = it + local, slot = stage % kStages, round = stage / kStages;
-        const int mat = NMAT == 2 && local >= groups, grp = local - mat * groups;
-        if (!mbar_wait_bounded(&ctl.full[slot], round & 1, abortFlag)) {  // also leaves when another role raised the abort flag
+      for (; mine < it + perTile; mine += 2, slot += 2) {
+        if (slot >= kStages) {
+          slot -= kStages;
+          phase ^= 1;
+        }
+        const int local = int(mine - it), mat = NMAT == 2 && local >= groups, grp = local - mat * groups;
+        if (!mbar_wait_bounded(&ctl.full[slot], phase, abortFlag)) {  // also leaves when another role raised the abort flag
           *abortFlag = 1;
           atomicExch(p.status, kStatusBarrierTimeout);
           break;
@@ -284,40 +304,27 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
       if (p.debug & 8)  // probe: no reduction, no stores
         continue;
       // Cross-warp reduction of the K split, then the epilogue.
-      float* mine = partial + size_t(tileCounter & 1) * NMAT * kConsumerWarps * 128;
+      float* sums = partial + size_t(tileCounter & 1) * NMAT * kConsumerWarps * 128;
 #pragma unroll
       for (int mat = 0; mat < NMAT; ++mat) {
-        float* dst = mine + (mat * kConsumerWarps + warp) * 128;
+        float* dst = sums + (mat * kConsumerWarps + warp) * 128;
         dst[(2 * t) * 16 + g] = total[mat][0];
         dst[(2 * t + 1) * 16 + g] = total[mat][1];
         dst[(2 * t) * 16 + g + 8] = total[mat][2];
         dst[(2 * t + 1) * 16 + g + 8] = total[mat][3];
       }
       named_barrier(1, kConsumerWarps * kWarp);
-      // Four warps finish the tile; which four rotates so that no warp falls behind the others.
-      const int finisher = (warp - 4 * tileCounter) & (kConsumerWarps - 1);
       if (finisher < 4) {
-        const int element = finisher * kWarp + lane, row = element >> 4, local = element & 15;
         float sum[NMAT];
 #pragma unroll
         for (int mat = 0; mat < NMAT; ++mat) {
           sum[mat] = 0.f;
 #pragma unroll
           for (int w = 0; w < kConsumerWarps; ++w)
-            sum[mat] += mine[(mat * kConsumerWarps + w) * 128 + element];
+            sum[mat] += sums[(mat * kConsumerWarps + w) * 128 + element];
         }
-        if (row < p.m) {
-          const GemvSeg& seg = p.seg[find_segment(p, tile)];
-          const size_t at = size_t(row) * seg.ldy + size_t(tile - seg.tile0) * kTileRows + local;
-          float value = sum[0];
-          if (NMAT == 2)
-            value = silu_f(sum[0]) * sum[1];
-          else if (chunk > 0)
-            value += seg.y[at];
-          else if (seg.res)
-            value += seg.res[at];
-          seg.y[at] = value;
-        }
+        if (destination)
+          *destination = NMAT == 2 ? silu_f(sum[0]) * sum[1] : sum[0] + addend;
       }
     }
     // This chunk's image may now be overwritten.
