@@ -73,10 +73,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return done != 0;
 }
 
+// Non-blocking test of a phase: unlike try_wait it never suspends the thread, so it answers at once when the phase
+// has already completed, which is the common case for a consumer that the producer keeps ahead of.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
 // Waits for a phase with an iteration limit. Returns false when the limit ran out; the caller then
 // raises the abort flag so every role of the kernel leaves its loops instead of spinning forever.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abortFlag) {
-  if (mbar_try_wait(bar, parity))  // the common case: the phase has already completed
+  if (mbar_test_wait(bar, parity))  // the common case: the phase has already completed
     return true;
   for (uint32_t spin = 0; spin < (1u << 20); ++spin) {
     if (mbar_try_wait(bar, parity))
