@@ -9,7 +9,7 @@
 // scale and the -dmin * m term (one fp16 MMA against the sub-block sums) are applied once per super-block.
 // The only approximation is the 16-bit activation grid: absolute error at most 1.6e-5 of the block maximum.
 //
-// One persistent CTA per SM: 8 consumer warps + 1 producer warp. The producer streams 16-row x 8-super-block
+// One persistent CTA per SM: 16 consumer warps, 4 finisher warps and 1 producer warp. The producer streams 16-row x 8-super-block
 // weight slabs with one tiled TMA copy each into a shared-memory ring, and bulk-copies the activation image of the
 // current K chunk; every wait on an mbarrier is bounded and ends in an abort flag plus a device status code.
 #include "act_image.cuh"
@@ -20,7 +20,10 @@ namespace {
 
 constexpr int kConsumerWarps = 16;  // two halves of 8; consecutive ring stages alternate between the halves
 constexpr int kStageWarps = 8;       // one warp per super-block of a stage
-constexpr int kThreads = (kConsumerWarps + 1) * kWarp;
+constexpr int kFinisherWarps = 4;    // sum the consumers' partial results of a tile and store it, off the consumers' path
+constexpr int kProducerWarp = kConsumerWarps + kFinisherWarps;
+constexpr int kThreads = (kProducerWarp + 1) * kWarp;
+constexpr int kHandoffThreads = (kConsumerWarps + kFinisherWarps) * kWarp;  // parties of the named barriers between the two roles
 constexpr int kChunkBlocks = 16;  // super-blocks of K whose image is resident at a time
 constexpr int kStageBlocks = kGemvStageBlocks;
 constexpr int kTileRows = kGemvTileRows;
@@ -159,7 +162,7 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
   pdl_launch_dependents();
   volatile int* abortFlag = &ctl.abort;
 
-  if (warp == kConsumerWarps) {
+  if (warp == kProducerWarp) {
     // ---- producer: weight slabs into the ring, and the activation image of each K chunk ----
     // The weights do not depend on the kernels before this one, so the ring is filled before the wait for them; the
     // image does, so the first one is requested after that wait, once the ring is full.
@@ -238,6 +241,46 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
     return;
   }
 
+  // Named barriers between consumers and finishers, per partial-sum buffer b = tile parity: 1 + b "partial sums of a
+  // tile are stored" (consumers arrive, finishers wait), 3 + b "the buffer has been read" (finishers arrive,
+  // consumers wait before they store into it again two tiles later).
+  if (warp >= kConsumerWarps) {
+    // ---- finishers: 128 threads, one per element of a tile's 16 x 8 result ----
+    pdl_wait();
+    const int element = (warp - kConsumerWarps) * kWarp + lane;
+    int tileCounter = 0;
+    for (int chunk = 0; chunk < chunks; ++chunk)
+      for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++tileCounter) {
+        // What is added to the result (the residual, or the sum over the earlier K chunks) is fetched before the wait.
+        float* destination = nullptr;
+        float addend = 0.f;
+        if ((element >> 4) < p.m) {
+          const GemvSeg& seg = p.nseg == 1 ? p.seg[0] : p.seg[find_segment(p, tile)];
+          const size_t at = size_t(element >> 4) * seg.ldy + size_t(tile - seg.tile0) * kTileRows + (element & 15);
+          destination = seg.y + at;
+          if (NMAT == 1 && chunk > 0)
+            addend = *destination;
+          else if (NMAT == 1 && seg.res)
+            addend = seg.res[at];
+        }
+        const int buffer = tileCounter & 1;
+        const float* sums = partial + size_t(buffer) * NMAT * kConsumerWarps * 128;
+        named_barrier(1 + buffer, kHandoffThreads);
+        float sum[NMAT];
+#pragma unroll
+        for (int mat = 0; mat < NMAT; ++mat) {
+          sum[mat] = 0.f;
+#pragma unroll
+          for (int w = 0; w < kConsumerWarps; ++w)
+            sum[mat] += sums[(mat * kConsumerWarps + w) * 128 + element];
+        }
+        named_barrier_arrive(3 + buffer, kHandoffThreads);
+        if (destination)
+          *destination = NMAT == 2 ? silu_f(sum[0]) * sum[1] : sum[0] + addend;
+      }
+    return;
+  }
+
   // ---- consumers ----
   pdl_wait();
   const int g = lane >> 2, t = lane & 3, half = warp / kStageWarps, unit = warp % kStageWarps;
@@ -257,22 +300,6 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
 #pragma unroll
       for (int mat = 0; mat < NMAT; ++mat)
         total[mat][0] = total[mat][1] = total[mat][2] = total[mat][3] = 0.f;
-      // Four warps finish the tile, 32 of its 16 x 8 results each; which four rotates so that no warp falls behind the
-      // others. They fetch what is added to their result (the residual, or the sum over the earlier K chunks) now, so
-      // that the load has long completed when the tile's partial sums are in.
-      const int finisher = (warp - 4 * tileCounter) & (kConsumerWarps - 1), element = finisher * kWarp + lane;
-      float* destination = nullptr;
-      float addend = 0.f;
-      if (finisher < 4 && (element >> 4) < p.m) {
-        const GemvSeg& seg = p.seg[find_segment(p, tile)];
-        const size_t at = size_t(element >> 4) * seg.ldy + size_t(tile - seg.tile0) * kTileRows + (element & 15);
-        destination = seg.y + at;
-        if (NMAT == 1 && chunk > 0)
-          addend = *destination;
-        else if (NMAT == 1 && seg.res)
-          addend = seg.res[at];
-      }
-      // Consecutive ring stages alternate between the two halves of the consumer warps.
       // `mine` is the next stage of this half (they are the stages congruent to `half` modulo 2), `slot` and `phase`
       // its place in the ring.
       const int perTile = NMAT * groups;
@@ -301,10 +328,11 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
           mbar_arrive(&ctl.empty[slot]);
       }
       it += perTile;
-      if (p.debug & 8)  // probe: no reduction, no stores
-        continue;
-      // Cross-warp reduction of the K split, then the epilogue.
-      float* sums = partial + size_t(tileCounter & 1) * NMAT * kConsumerWarps * 128;
+      // Hand the partial sums of the K split to the finishers and go on with the next tile.
+      const int buffer = tileCounter & 1;
+      if (tileCounter >= 2)
+        named_barrier(3 + buffer, kHandoffThreads);
+      float* sums = partial + size_t(buffer) * NMAT * kConsumerWarps * 128;
 #pragma unroll
       for (int mat = 0; mat < NMAT; ++mat) {
         float* dst = sums + (mat * kConsumerWarps + warp) * 128;
@@ -313,19 +341,7 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
         dst[(2 * t) * 16 + g + 8] = total[mat][2];
         dst[(2 * t + 1) * 16 + g + 8] = total[mat][3];
       }
-      named_barrier(1, kConsumerWarps * kWarp);
-      if (finisher < 4) {
-        float sum[NMAT];
-#pragma unroll
-        for (int mat = 0; mat < NMAT; ++mat) {
-          sum[mat] = 0.f;
-#pragma unroll
-          for (int w = 0; w < kConsumerWarps; ++w)
-            sum[mat] += sums[(mat * kConsumerWarps + w) * 128 + element];
-        }
-        if (destination)
-          *destination = NMAT == 2 ? silu_f(sum[0]) * sum[1] : sum[0] + addend;
-      }
+      named_barrier_arrive(1 + buffer, kHandoffThreads);
     }
     // This chunk's image may now be overwritten.
     __syncwarp();
