@@ -103,7 +103,7 @@ def gemv_roofline(device_index, copies=24, replays=20, xsplit=None, qtype=None, 
   # Q4_K: the integer kernel reads the quantised image of the activations, which a decode pass gets from the kernel
   # before the GEMV; it is prepared once here so that the timed launches are the GEMV kernel alone.
   image = None
-  if qtype == D.Q4_K and not xsplit:
+  if qtype == D.Q4_K and not xsplit and m <= 8:
     image = dev.empty(dev.image_bytes(m, k), np.uint8)
     dev.quantize(x, m, k, image)
 
@@ -295,19 +295,21 @@ def main():
   parser.add_argument("--steps", type=int, default=128)
   parser.add_argument("--warmup", type=int, default=16)
   parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
-  parser.add_argument("--kernel-only", default=None, choices=("q4k", "q6k"),
+  parser.add_argument("--kernel-only", default=None, choices=("q4k", "q6k", "prefill"),
                       help="run only the isolated GEMV kernel on a small ring (the case profiled with ncu) and print its rate")
   parser.add_argument("--xsplit", type=int, default=None, choices=(1, 2))
   parser.add_argument("--prompt-max", type=int, default=4096, help="upper bound of the ragged prompt lengths (profiling runs use a small one)")
   parser.add_argument("--ncu-range", action="store_true", help="bracket the timed passes with cudaProfilerStart/Stop")
   args = parser.parse_args()
   if args.kernel_only:
-    q6 = args.kernel_only == "q6k"
-    n = 65536 if q6 else 12288
+    q6, prefill = args.kernel_only == "q6k", args.kernel_only == "prefill"
+    n, m = 65536 if q6 else 12288, 128 if prefill else 8  # 128 rows take the tcgen05 prefill GEMM (two launches: prepare + GEMM)
     algorithmic, seconds, launches = gemv_roofline(int(os.environ.get("LOCAL_RANK", 0)), copies=2 if q6 else 8, replays=2, xsplit=args.xsplit,
-                                                   qtype=14 if q6 else 12, n=n)
-    print(json.dumps({"kernel": args.kernel_only, "n": n, "k": 4096, "m": 8, "us_per_launch": seconds * 1e6, "GBs": algorithmic / seconds / 1e9,
-                      "launches": launches}))
+                                                   qtype=14 if q6 else 12, n=n, m=m)
+    line = {"kernel": args.kernel_only, "n": n, "k": 4096, "m": m, "us_per_launch": seconds * 1e6, "GBs": algorithmic / seconds / 1e9, "launches": launches}
+    if prefill:
+      line["TFLOPs"] = 2.0 * m * n * 4096 / seconds / 1e12
+    print(json.dumps(line))
     return
   args.warmup = max(args.warmup, 3)
   rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
