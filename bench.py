@@ -87,6 +87,11 @@ class ClockSampler:
             "reasons": sorted(reasons), "samples": len(inside)}
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one q4k_decode_kernel launch at the config-1 shape, from the ncu capture
+# summarised in profiles/q4k_decode_12288x4096_m8.md (the same shape and launch as the roofline leg below).
+GEMV_DRAM_BYTES_PER_LAUNCH = 28_402_176
+
+
 def gemv_roofline(device_index, copies=24, replays=20, xsplit=None, qtype=None, n=12288, k=4096, m=8):
   """The dominant kernel alone: Q4_K GEMV 12288 x 4096 with 8 activation rows (BASELINE config 1), launched over a
   ring of 24 distinct weight copies (680 MB, larger than L2) and timed with CUDA events on the launching stream."""
@@ -277,7 +282,7 @@ def run_ours(args, rank, world):
             "d2h_bytes_per_step": SEQUENCES * 4 + 4,
             "note": "through infeng_sequence_append/read with host token buffers; token ids, query records and sampled tokens cross PCIe every step"},
     "roofline": {"bound": "hbm", "kernel": "q4k_decode_kernel 12288x4096 M=8 (BASELINE config 1)", "achieved": algorithmic / kernel_seconds / 1e9,
-                 "peak": peak, "unit": "GB/s", "frac": algorithmic / kernel_seconds / 1e9 / peak, "of": peak_kind, "traffic": None,
+                 "peak": peak, "unit": "GB/s", "frac": algorithmic / kernel_seconds / 1e9 / peak, "of": peak_kind, "traffic": GEMV_DRAM_BYTES_PER_LAUNCH,
                  "frac_of_nominal_8TBs": algorithmic / kernel_seconds / 8e12, "us_per_launch": kernel_seconds * 1e6, "launches_timed": kernel_launches},
     "step_hbm": {"bytes_per_step": step_bytes, "achieved_GBs": step_bytes / step_seconds / 1e9, "frac_of_measured": step_bytes / step_seconds / 1e9 / peak,
                  "frac_of_nominal_8TBs": step_bytes / step_seconds / 8e12, "mean_context": sum(contexts) / len(contexts)},
