@@ -31,8 +31,8 @@ __device__ __forceinline__ const infdev_query& query_of_row(const infdev_query* 
 }
 
 // Splits of a row that attends to `attended` tokens: 64-token pieces, at most maxSplits, each a multiple of
-// the 16-token tile. A CTA walks its piece tile by tile with dependent loads, so the scan is bound by latency and
-// wants many short pieces in flight rather than few long ones.
+// the 16-token tile. The piece length trades the fixed cost of a CTA (query load, first tile fetch, partial store)
+// against the number of CTAs in flight; it depends only on the row's own context, never on the batch.
 __device__ __forceinline__ void split_range(uint32_t attended, uint32_t maxSplits, uint32_t split, uint32_t& begin, uint32_t& end, uint32_t& count) {
   count = min(maxSplits, (attended + 63u) / 64u);
   const uint32_t per = (((attended + count - 1) / count) + kTile - 1) / kTile * kTile;
@@ -86,11 +86,18 @@ __global__ void __launch_bounds__(256) attention_prepare_kernel(const float* qg,
   }
 }
 
-// grid (maxSplits, 4 kv heads, rows), 128 threads. Warp w scores tokens 4w..4w+3 of each 16-token tile, then
-// accumulates the values for query head w of the group.
-__global__ void __launch_bounds__(128) attention_scan_kernel(const float* q, const __half* cacheK, const __half* cacheV,
-                                                             const infdev_query* queries, const int32_t* table, int tableStride, int blockTokens,
-                                                             uint32_t maxSplits, float* partials) {
+// 16-byte asynchronous copy global -> shared; `bytes` = 0 writes zeros instead (a token past the end of the piece).
+__device__ __forceinline__ void copy_async16(void* dst, const void* src, uint32_t bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+
+// grid (maxSplits, 4 kv heads, rows), 128 threads. The 16-token K and V tiles of the piece are copied into a
+// double buffer in shared memory with cp.async one tile ahead of the arithmetic, so the walk over the piece is not a
+// chain of load latencies. Warp w scores tokens 4w..4w+3 of a tile for the four query heads of the group, then
+// accumulates the values for query head w.
+__global__ void __launch_bounds__(128, 4) attention_scan_kernel(const float* q, const __half* cacheK, const __half* cacheV,
+                                                                const infdev_query* queries, const int32_t* table, int tableStride, int blockTokens,
+                                                                uint32_t maxSplits, float* partials) {
   pdl_launch_dependents();
   pdl_wait();
   const uint32_t split = blockIdx.x, kvHead = blockIdx.y, row = blockIdx.z;
@@ -102,6 +109,22 @@ __global__ void __launch_bounds__(128) attention_scan_kernel(const float* q, con
   if (split >= count)
     return;
   __shared__ float scores[kGroup][kTile];
+  __shared__ __align__(16) __half tiles[2][2][kTile][kDim];  // [buffer][K, V][token][dim]
+  const int32_t* slotTable = table + size_t(info.slot) * tableStride;
+  auto fetch = [&](uint32_t tile, int buffer) {
+    const size_t block = slotTable[tile / blockTokens];
+    const size_t base = ((block * kKvHeads + kvHead) * blockTokens + tile % blockTokens) * kDim;
+    // 16 tokens x 512 bytes per tensor = 512 chunks of 16 bytes, four per thread
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int chunk = c * 128 + threadIdx.x, token = chunk >> 5, offset = (chunk & 31) * 8;
+      const uint32_t bytes = tile + token < end ? 16u : 0u;
+      copy_async16(&tiles[buffer][0][token][offset], cacheK + base + token * kDim + offset, bytes);
+      copy_async16(&tiles[buffer][1][token][offset], cacheV + base + token * kDim + offset, bytes);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  fetch(begin, 0);
   // q of the four heads, the 8 dims of this lane: dims lane*8 .. lane*8+7
   float qv[kGroup][8];
 #pragma unroll
@@ -111,15 +134,17 @@ __global__ void __launch_bounds__(128) attention_scan_kernel(const float* q, con
     qv[h][0] = a.x, qv[h][1] = a.y, qv[h][2] = a.z, qv[h][3] = a.w, qv[h][4] = b.x, qv[h][5] = b.y, qv[h][6] = b.z, qv[h][7] = b.w;
   }
   float runningMax = -1.0e30f, runningNorm = 0.f, numerator[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  const int32_t* slotTable = table + size_t(info.slot) * tableStride;
-  for (uint32_t tile = begin; tile < end; tile += kTile) {
-    const size_t block = slotTable[tile / blockTokens];
-    const size_t base = ((block * kKvHeads + kvHead) * blockTokens + tile % blockTokens) * kDim;
-    // scores of 4 tokens x 4 heads per warp
-    float s[4][kGroup];
+  int buffer = 0;
+  for (uint32_t tile = begin; tile < end; tile += kTile, buffer ^= 1) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();  // this tile is complete for every thread, and every thread is done with the previous tile and its scores
+    if (tile + kTile < end)
+      fetch(tile + kTile, buffer ^ 1);  // lands while this tile is worked on
+    // partial scores of 4 tokens x 4 heads over this lane's 8 dims
+    float s[16];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(cacheK + base + (warp * 4 + i) * kDim + lane * 8);
+      const uint4 raw = *reinterpret_cast<const uint4*>(&tiles[buffer][0][warp * 4 + i][lane * 8]);
       const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
       float kf[8];
 #pragma unroll
@@ -133,28 +158,29 @@ __global__ void __launch_bounds__(128) attention_scan_kernel(const float* q, con
 #pragma unroll
         for (int d = 0; d < 8; ++d)
           acc = fmaf(qv[h][d], kf[d], acc);
-        s[i][h] = acc;
+        s[i * 4 + h] = acc;
       }
     }
+    // Sum the 16 values over the 32 lanes with 16 shuffles: every exchange halves the values a lane still carries;
+    // lane l ends with the total of value l / 2.
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int width = 8, step = 16; width >= 1; width >>= 1, step >>= 1) {
+      const bool upper = lane & step;
 #pragma unroll
-      for (int h = 0; h < kGroup; ++h)
-        s[i][h] = warp_sum(s[i][h]);
-    if (lane < 16) {
-      const int i = lane >> 2, h = lane & 3;
-      float value = 0.f;
-#pragma unroll
-      for (int a = 0; a < 4; ++a)
-#pragma unroll
-        for (int b = 0; b < kGroup; ++b)
-          if (a == i && b == h)
-            value = s[a][b];
+      for (int v = 0; v < width; ++v) {
+        const float keep = upper ? s[v + width] : s[v], send = upper ? s[v] : s[v + width];
+        s[v] = keep + __shfl_xor_sync(0xffffffffu, send, step);
+      }
+    }
+    s[0] += __shfl_xor_sync(0xffffffffu, s[0], 1);
+    if (!(lane & 1)) {
+      const int v = lane >> 1, i = v >> 2, h = v & 3;
       const uint32_t token = tile + warp * 4 + i;
-      scores[h][warp * 4 + i] = token < end ? value * (1.0f / 16.0f) : -INFINITY;
+      scores[h][warp * 4 + i] = token < end ? s[0] * (1.0f / 16.0f) : -INFINITY;
     }
     __syncthreads();
-    // online softmax for head `warp`; lane owns dims lane*8..+7
+    // online softmax for head `warp`; lane owns dims lane*8..+7. A token past the end has score -inf: weight 0
+    // against a zero-filled value row.
     float tileMax = -INFINITY;
 #pragma unroll
     for (int i = 0; i < kTile; ++i)
@@ -164,11 +190,11 @@ __global__ void __launch_bounds__(128) attention_scan_kernel(const float* q, con
 #pragma unroll
     for (int d = 0; d < 8; ++d)
       numerator[d] *= rescale;
-    const uint32_t live = min(uint32_t(kTile), end - tile);
-    for (uint32_t i = 0; i < live; ++i) {
+#pragma unroll
+    for (int i = 0; i < kTile; ++i) {
       const float weight = expf(scores[warp][i] - nextMax);
       runningNorm += weight;
-      const uint4 raw = *reinterpret_cast<const uint4*>(cacheV + base + i * kDim + lane * 8);
+      const uint4 raw = *reinterpret_cast<const uint4*>(&tiles[buffer][1][i][lane * 8]);
       const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
       for (int d = 0; d < 4; ++d) {
@@ -178,7 +204,6 @@ __global__ void __launch_bounds__(128) attention_scan_kernel(const float* q, con
       }
     }
     runningMax = nextMax;
-    __syncthreads();
   }
   float* dst = partials + ((size_t(row) * kQHeads + kvHead * kGroup + warp) * maxSplits + split) * kPartialStride;
   *reinterpret_cast<float4*>(dst + lane * 8) = make_float4(numerator[0], numerator[1], numerator[2], numerator[3]);
@@ -232,7 +257,7 @@ cudaError_t attention_prepare_launch(const float* qg, const float* rawK, const f
                                      void* cacheK, void* cacheV, cudaStream_t stream) {
   if (rows <= 0)
     return cudaSuccess;
-  launch_kernel(attention_prepare_kernel, unsigned(rows * 20), 256, 0, stream, qg, rawK, rawV, qNorm, kNorm, rope, queries, table, tableStride, blockTokens, q,
+  launch_kernel<2>(attention_prepare_kernel, unsigned(rows * 20), 256, 0, stream, qg, rawK, rawV, qNorm, kNorm, rope, queries, table, tableStride, blockTokens, q,
                                                                      static_cast<__half*>(cacheK), static_cast<__half*>(cacheV));
   return cudaGetLastError();
 }

@@ -23,10 +23,11 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Set once per process from INFENG_PDL: 0 no kernel is launched early, 1 every kernel, 2 only the weight-streaming
-// GEMV kernels (which use the time to fill their shared-memory ring).
+// GEMV kernels (which use the time to fill their shared-memory ring), 3 those and the small kernels that follow a
+// GEMV in a decoder layer (EARLY = 2).
 int pdl_mode();
 
-template <bool STREAMING = false, class... Params, class... Args>
+template <int EARLY = 0, class... Params, class... Args>
 cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t sharedBytes, cudaStream_t stream, Args&&... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
@@ -37,7 +38,7 @@ cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size
   attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attribute[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
-  config.numAttrs = (pdl_mode() == 1 || (pdl_mode() == 2 && STREAMING)) ? 1 : 0;
+  config.numAttrs = (pdl_mode() == 1 || (pdl_mode() == 2 && EARLY == 1) || (pdl_mode() == 3 && EARLY >= 1)) ? 1 : 0;
   return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
 

@@ -221,7 +221,7 @@ cudaError_t gdn_prepare_launch(const float* x, const float* mixed, const float* 
                                float* q, float* k, float* v, float* beta, float* g, cudaStream_t stream) {
   if (rows <= 0)
     return cudaSuccess;
-  launch_kernel(gdn_prepare_kernel, unsigned(rows * (kChannels / 256 + kValueHeads)), 256, 0, stream, x, wBeta, wAlpha, A, dt, mixed, convWeight, queries,
+  launch_kernel<2>(gdn_prepare_kernel, unsigned(rows * (kChannels / 256 + kValueHeads)), 256, 0, stream, x, wBeta, wAlpha, A, dt, mixed, convWeight, queries,
                 int(rows), stateOffset, stateBytes, q, k, v, beta, g);
   return cudaGetLastError();
 }

@@ -437,7 +437,7 @@ template <class Q, int NMAT, int XSPLIT> cudaError_t launch(const GemvParams& p,
     configured = true;
   }
   const int grid = p.tiles < sms ? p.tiles : sms;
-  launch_kernel<true>(gemv_kernel<Q, NMAT, XSPLIT>, grid, kThreads, bytes, stream, p);
+  launch_kernel<1>(gemv_kernel<Q, NMAT, XSPLIT>, grid, kThreads, bytes, stream, p);
   return cudaGetLastError();
 }
 

@@ -16,7 +16,8 @@
 #include "ops.h"
 
 struct infdev_ctx {
-  int device = 0, sms = 0, xsplit = 2, debug = 0, umma = 1;  // umma: 0 never, 1 for more than 8 rows, 2 always
+  int device = 0, sms = 0, xsplit = 2, debug = 0, umma = 1;
+  int skip = 0;  // probe (INFENG_SKIP): bit mask of kernel classes whose launches are dropped, to time a pass without them  // umma: 0 never, 1 for more than 8 rows, 2 always
   int integerDecode = 1;     // Q4_K decode GEMV: 1 integer-MMA kernel over an activation image, 0 fp16-MMA kernel
   uint8_t* image = nullptr;  // activation image for the integer decode kernel (K up to 16384)
   int* imageCounters = nullptr;        // arrival counters of the kernels that write images block by block (zero between launches)
@@ -168,6 +169,8 @@ infdev_ctx* infdev_create(int device, char* error) {
     ctx->debug = std::atoi(env);
   if (const char* env = std::getenv("INFENG_UMMA"))
     ctx->umma = std::atoi(env);
+  if (const char* env = std::getenv("INFENG_SKIP"))
+    ctx->skip = std::atoi(env);
   if (const char* env = std::getenv("INFENG_INTEGER_DECODE"))
     ctx->integerDecode = std::atoi(env) != 0;
   if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess ||
@@ -541,8 +544,11 @@ static int linear_common(infdev_ctx* ctx, int type, bool pair, int count, const 
   uint8_t* captured = take_capture(ctx);
   if (captured && (count != 1 || n[0] % 256))
     return fail(ctx, INFDEV_E_ARGUMENT, "linear: an image of the result needs a single matrix with n a multiple of 256");
-  if (int r = linear_run(ctx, type, pair, count, w, w2, n, k, x, m, y, residual, supplied))
-    return r;
+  if (!(ctx->skip & (type == INFDEV_Q6_K ? 32 : 128)))
+    if (int r = linear_run(ctx, type, pair, count, w, w2, n, k, x, m, y, residual, supplied))
+      return r;
+  if (ctx->skip & 64)
+    return INFDEV_OK;
   // A GEMV tile is 16 outputs wide, a 256-value image block spans 16 tiles on different SMs: the image of the result
   // takes a launch of its own.
   return captured ? quantize_rows(ctx, y[0], m, n[0], captured) : INFDEV_OK;
@@ -585,6 +591,8 @@ int infdev_rms_norm(infdev_ctx* ctx, const float* x, const float* w, int64_t row
     return fail(ctx, INFDEV_E_ARGUMENT, "rms_norm: dim must be a multiple of 4 and buffers 16-byte aligned");
   ctx->launches += 1;
   uint8_t* image = take_capture(ctx);
+  if (ctx->skip & 1)
+    return INFDEV_OK;
   if (image && dim % 256)
     return fail(ctx, INFDEV_E_ARGUMENT, "rms_norm: an image needs dim to be a multiple of 256");
   return check(ctx, infdev::rms_norm_launch(x, w, nullptr, rows, dim, y, image, ctx->stream), "rms_norm");
@@ -603,6 +611,10 @@ int infdev_gdn_prepare(infdev_ctx* ctx, const float* x, const float* mixed, cons
                        const float* ssmDt, const float* convWeight, const infdev_query* queries, int queryCount, int64_t rows,
                        uint64_t stateOffset, uint64_t stateBytes, float* q, float* k, float* v, float* beta, float* g) {
   Bind bind(ctx);
+  if (ctx->skip & 2) {
+    take_capture(ctx);
+    return INFDEV_OK;
+  }
   (void)queryCount;
   if (stateOffset % 16 || stateBytes % 16)
     return fail(ctx, INFDEV_E_ARGUMENT, "gdn_prepare: state offsets must be multiples of 16 bytes");
@@ -616,6 +628,10 @@ int infdev_gdn_prepare(infdev_ctx* ctx, const float* x, const float* mixed, cons
 int infdev_delta_rule(infdev_ctx* ctx, const float* q, const float* k, const float* v, const float* g, const float* beta, const float* z,
                       const float* normWeight, const infdev_query* queries, int queryCount, uint64_t stateOffset, uint64_t stateBytes, float* out) {
   Bind bind(ctx);
+  if (ctx->skip & 4) {
+    take_capture(ctx);
+    return INFDEV_OK;
+  }
   if (stateOffset % 16 || stateBytes % 16)
     return fail(ctx, INFDEV_E_ARGUMENT, "delta_rule: state offsets must be multiples of 16 bytes");
   ctx->launches += 1;
@@ -644,6 +660,10 @@ int infdev_attention_prepare(infdev_ctx* ctx, const float* qg, const float* k, c
                              const float* rope, const infdev_query* queries, int queryCount, int64_t rows, const int32_t* table,
                              int32_t tableStride, int32_t blockTokens, float* q, void* cacheK, void* cacheV) {
   Bind bind(ctx);
+  if (ctx->skip & 16) {
+    take_capture(ctx);
+    return INFDEV_OK;
+  }
   (void)queryCount;
   if (blockTokens <= 0 || blockTokens % 16)
     return fail(ctx, INFDEV_E_ARGUMENT, "attention: blockTokens must be a positive multiple of 16");
@@ -660,6 +680,10 @@ int infdev_attention(infdev_ctx* ctx, const float* q, const float* qg, const voi
                      int queryCount, int64_t rows, const int32_t* table, int32_t tableStride, int32_t blockTokens, uint32_t maxSplits,
                      float* partials, float* out) {
   Bind bind(ctx);
+  if (ctx->skip & 8) {
+    take_capture(ctx);
+    return INFDEV_OK;
+  }
   (void)queryCount;
   if (blockTokens <= 0 || blockTokens % 16 || maxSplits < 1 || maxSplits > 64)
     return fail(ctx, INFDEV_E_ARGUMENT, "attention: blockTokens must be a multiple of 16 and maxSplits in 1..64");

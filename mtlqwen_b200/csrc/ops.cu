@@ -242,9 +242,9 @@ cudaError_t rms_norm_launch(const float* x, const float* w, const infdev_query* 
   if (rows <= 0)
     return cudaSuccess;
   if (queries)
-    launch_kernel(rms_norm_kernel<true>, unsigned(rows), 256, 0, stream, x, w, queries, int(dim), y, image);
+    launch_kernel<2>(rms_norm_kernel<true>, unsigned(rows), 256, 0, stream, x, w, queries, int(dim), y, image);
   else
-    launch_kernel(rms_norm_kernel<false>, unsigned(rows), 256, 0, stream, x, w, nullptr, int(dim), y, image);
+    launch_kernel<2>(rms_norm_kernel<false>, unsigned(rows), 256, 0, stream, x, w, nullptr, int(dim), y, image);
   return cudaGetLastError();
 }
 

@@ -379,7 +379,7 @@ template <int NMAT> cudaError_t launch(const GemvParams& p, int sms, cudaStream_
     configured = true;
   }
   const int grid = p.tiles < sms ? p.tiles : sms;
-  launch_kernel<true>(q4k_decode_kernel<NMAT>, grid, kThreads, bytes, stream, p);
+  launch_kernel<1>(q4k_decode_kernel<NMAT>, grid, kThreads, bytes, stream, p);
   return cudaGetLastError();
 }
 
@@ -391,7 +391,7 @@ cudaError_t q4k_decode_launch(bool pair, const GemvParams& p, int sms, cudaStrea
 
 cudaError_t activation_image_launch(const float* x, int ldx, int m, int k, uint8_t* image, cudaStream_t stream) {
   const int blocks = k / 256;
-  launch_kernel(activation_image_kernel, (blocks * kImageRows + 7) / 8, 256, 0, stream, x, ldx, m, blocks, image);
+  launch_kernel<2>(activation_image_kernel, (blocks * kImageRows + 7) / 8, 256, 0, stream, x, ldx, m, blocks, image);
   return cudaGetLastError();
 }
 
