@@ -147,6 +147,41 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float* x, const flo
   }
 }
 
+// The same for dim = 4096 in one pass over the row: 512 threads, each keeps its eight consecutive values in registers
+// between the sum of squares and the scaling (a warp holds one 256-value block, which is also the unit of the image).
+template <bool GATHER>
+__global__ void __launch_bounds__(512) rms_norm_4096_kernel(const float* x, const float* w, const infdev_query* queries, float* y, uint8_t* image) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int kDim = 4096;
+  const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, d = threadIdx.x * 8;
+  const float* src = x + size_t(row) * kDim;
+  if (GATHER) {
+    const infdev_query& info = query_of_logit(queries, row);
+    src = x + size_t(info.start + info.count - info.samples + (row - info.logit)) * kDim;
+  }
+  const float4 a = *reinterpret_cast<const float4*>(src + d), b = *reinterpret_cast<const float4*>(src + d + 4);
+  const float4 ga = *reinterpret_cast<const float4*>(w + d), gb = *reinterpret_cast<const float4*>(w + d + 4);
+  __shared__ float sums[16];
+  const float sum = warp_sum((a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w) + (b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w));
+  if (lane == 0)
+    sums[warp] = sum;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    total += sums[i];
+  const float scale = rsqrtf(total / float(kDim) + 1.0e-6f);
+  const float v[8] = {a.x * scale * ga.x, a.y * scale * ga.y, a.z * scale * ga.z, a.w * scale * ga.w,
+                      b.x * scale * gb.x, b.y * scale * gb.y, b.z * scale * gb.z, b.w * scale * gb.w};
+  if (y) {
+    *reinterpret_cast<float4*>(y + size_t(row) * kDim + d) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(y + size_t(row) * kDim + d + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+  if (image)
+    image_store_block(image + (size_t(row >> 3) * (kDim / 256) + warp) * kImageBlockBytes, row & 7, lane, v);
+}
+
 // mtp_fuse (native_ops.metal:43-87): y[row] = [rmsnorm(embedding[row]) * enorm | rmsnorm(h) * hnorm], 8192 wide.
 // h by mode: 2 = the slot's MTP seed (the target's hidden state of the last committed position, kept at the end
 // of the state record); 1 = seed for a query's first row, else the target hidden of the previous row; 0 = the
@@ -241,6 +276,13 @@ cudaError_t rms_norm_launch(const float* x, const float* w, const infdev_query* 
                             cudaStream_t stream) {
   if (rows <= 0)
     return cudaSuccess;
+  if (dim == 4096) {
+    if (queries)
+      launch_kernel<2>(rms_norm_4096_kernel<true>, unsigned(rows), 512, 0, stream, x, w, queries, y, image);
+    else
+      launch_kernel<2>(rms_norm_4096_kernel<false>, unsigned(rows), 512, 0, stream, x, w, nullptr, y, image);
+    return cudaGetLastError();
+  }
   if (queries)
     launch_kernel<2>(rms_norm_kernel<true>, unsigned(rows), 256, 0, stream, x, w, queries, int(dim), y, image);
   else
