@@ -163,80 +163,98 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
   volatile int* abortFlag = &ctl.abort;
 
   if (warp == kProducerWarp) {
-    // ---- producer: weight slabs into the ring, and the activation image of each K chunk ----
+    // ---- producer (one thread): weight slabs into the ring, and the activation image of each K chunk ----
     // The weights do not depend on the kernels before this one, so the ring is filled before the wait for them; the
-    // image does, so the first one is requested after that wait, once the ring is full.
-    uint32_t it = 0;
-    auto loadImage = [&](int chunk, int chunkBlocks) {
-      if (lane == 0) {
+    // first image does, so it is requested after that wait, once the ring is full. The image of a later chunk
+    // replaces the one the consumers are still reading: the weights of that chunk are streamed into the ring
+    // regardless, and the image is requested at the first moment the consumers have released the old one, which the
+    // wait for a ring slot polls for (the consumers cannot free a slot of the new chunk before they have its image).
+    if (lane == 0) {
+      uint32_t it = 0;
+      int pendingChunk = -1, pendingBlocks = 0;  // image not yet requested
+      bool firstImage = false, ok = true;
+      auto load_image = [&](int chunk, int chunkBlocks) {
         mbar_arrive_expect_tx(&ctl.imageFull, uint32_t(chunkBlocks) * kImageBlockBytes);
         for (int first = 0; first < chunkBlocks; first += kImagePieceBlocks) {
           const int count = min(kImagePieceBlocks, chunkBlocks - first);
           bulk_load(image + size_t(first) * kImageBlockBytes, p.image + size_t(chunk * kChunkBlocks + first) * kImageBlockBytes,
                     uint32_t(count) * kImageBlockBytes, &ctl.imageFull);
         }
-      }
-      __syncwarp();
-    };
-    bool firstImage = false;
-    for (int chunk = 0; chunk < chunks && !*abortFlag; ++chunk) {
-      const int chunkBlocks = min(kChunkBlocks, blocksPerRow - chunk * kChunkBlocks);
-      const int groups = (chunkBlocks + kStageBlocks - 1) / kStageBlocks;
-      bool ok = true;
-      if (chunk > 0) {
-        if (lane == 0)  // the consumers have finished with the previous chunk's image
-          ok = mbar_wait_bounded(&ctl.imageEmpty, (chunk - 1) & 1, abortFlag);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) {
-          if (lane == 0) {
-            *abortFlag = 1;
-            atomicExch(p.status, kStatusBarrierTimeout);
-          }
-          break;
+      };
+      auto load_pending_if_free = [&]() {
+        if (pendingChunk >= 0 && mbar_test_wait(&ctl.imageEmpty, (pendingChunk - 1) & 1)) {
+          load_image(pendingChunk, pendingBlocks);
+          pendingChunk = -1;
         }
-        loadImage(chunk, chunkBlocks);
-      }
-      for (int tile = blockIdx.x; tile < p.tiles && !*abortFlag; tile += gridDim.x) {
-        const int segment = find_segment(p, tile);
-        const int row0 = (tile - p.seg[segment].tile0) * kTileRows;
-        for (int mat = 0; mat < NMAT; ++mat) {
-          for (int grp = 0; grp < groups; ++grp, ++it) {
-            const uint32_t slot = it % kStages, round = it / kStages;
-            if (!firstImage && it == kStages) {  // the ring is full; nothing is released before the consumers have an image
-              pdl_wait();
-              loadImage(0, chunkBlocks);
-              firstImage = true;
-            }
-            ok = true;
-            if (lane == 0 && round > 0)
-              ok = mbar_wait_bounded(&ctl.empty[slot], (round - 1) & 1, abortFlag);
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) {
-              if (lane == 0) {
-                *abortFlag = 1;
-                atomicExch(p.status, kStatusBarrierTimeout);
+      };
+      auto give_up = [&]() {
+        *abortFlag = 1;
+        atomicExch(p.status, kStatusBarrierTimeout);
+        ok = false;
+      };
+      for (int chunk = 0; chunk < chunks && ok && !*abortFlag; ++chunk) {
+        const int chunkBlocks = min(kChunkBlocks, blocksPerRow - chunk * kChunkBlocks);
+        const int groups = (chunkBlocks + kStageBlocks - 1) / kStageBlocks;
+        if (pendingChunk >= 0) {  // a chunk so short that its image was never asked for while its slabs were issued
+          if (!mbar_wait_bounded(&ctl.imageEmpty, (pendingChunk - 1) & 1, abortFlag)) {
+            give_up();
+            break;
+          }
+          load_pending_if_free();
+        }
+        if (chunk > 0)
+          pendingChunk = chunk, pendingBlocks = chunkBlocks;
+        for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x) {
+          const int segment = find_segment(p, tile);
+          const int row0 = (tile - p.seg[segment].tile0) * kTileRows;
+          for (int mat = 0; mat < NMAT && ok; ++mat) {
+            for (int grp = 0; grp < groups; ++grp, ++it) {
+              const uint32_t slot = it % kStages, round = it / kStages;
+              if (!firstImage && it == kStages) {  // the ring is full; nothing is released before the consumers have an image
+                pdl_wait();
+                load_image(0, chunkBlocks);
+                firstImage = true;
               }
-              break;
+              if (round > 0) {
+                // wait for the slot; bounded like every wait of this kernel
+                bool freed = false;
+                for (uint32_t spin = 0; spin < (1u << 22) && !freed; ++spin) {
+                  load_pending_if_free();
+                  freed = mbar_test_wait(&ctl.empty[slot], (round - 1) & 1);
+                  if (!freed && (spin & 1023u) == 1023u && *abortFlag)
+                    break;
+                }
+                if (!freed) {
+                  give_up();
+                  break;
+                }
+              }
+              // One tiled copy moves the whole slab; bytes past the end of a row are zero-filled and still counted, so
+              // the transaction size is always the full box.
+              if (p.debug & 4) {
+                mbar_arrive(&ctl.full[slot]);  // probe: the consumers run on whatever the ring holds
+              } else {
+                mbar_arrive_expect_tx(&ctl.full[slot], uint32_t(kStageBytes));
+                tma_load_2d(ring + size_t(slot) * kStageBytes, &p.map[segment][mat], (chunk * (kChunkBlocks / kStageBlocks) + grp) * (kStageBlocks * kBlockBytes / 8),
+                            row0, &ctl.full[slot]);
+              }
             }
-            // One tiled copy moves the whole slab; bytes past the end of a row are zero-filled and still counted, so the
-            // transaction size is always the full box.
-            if (lane == 0 && (p.debug & 4)) {
-              mbar_arrive(&ctl.full[slot]);  // probe: the consumers run on whatever the ring holds
-            } else if (lane == 0) {
-              mbar_arrive_expect_tx(&ctl.full[slot], uint32_t(kStageBytes));
-              tma_load_2d(ring + size_t(slot) * kStageBytes, &p.map[segment][mat], (chunk * (kChunkBlocks / kStageBlocks) + grp) * (kStageBlocks * kBlockBytes / 8),
-                          row0, &ctl.full[slot]);
-            }
-            __syncwarp();
           }
         }
+        if (ok && !firstImage) {  // fewer stages than the ring holds
+          pdl_wait();
+          load_image(0, chunkBlocks);
+          firstImage = true;
+        }
       }
-      if (!firstImage) {  // fewer stages than the ring holds
-        pdl_wait();
-        loadImage(0, chunkBlocks);
-        firstImage = true;
+      if (ok && pendingChunk >= 0) {
+        if (mbar_wait_bounded(&ctl.imageEmpty, (pendingChunk - 1) & 1, abortFlag))
+          load_pending_if_free();
+        else
+          give_up();
       }
     }
+    __syncwarp();
     pdl_wait();  // every thread of every kernel waits, so completion stays transitive along the stream
     return;
   }
