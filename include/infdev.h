@@ -155,6 +155,13 @@ int infdev_gdn_prepare(infdev_ctx* ctx, const float* x, const float* mixed, cons
  * stateOffset here addresses the layer's recurrent state S fp32 [32][128][128] inside a record. */
 int infdev_delta_rule(infdev_ctx* ctx, const float* q, const float* k, const float* v, const float* g, const float* beta, const float* z,
                       const float* normWeight, const infdev_query* queries, int queryCount, uint64_t stateOffset, uint64_t stateBytes, float* out);
+/* The same for a pass that holds prefill chunks: non-speculative queries of at least 16 tokens take the chunked form
+ * (16 tokens per step, the role of delta_rule_prefill, delta_rule.metal:19-253), every other query the sequential one.
+ * Results agree with infdev_delta_rule to fp32 rounding. Two launches; no image of the result (a pending
+ * infdev_image_capture makes the call fail). */
+int infdev_delta_rule_prefill(infdev_ctx* ctx, const float* q, const float* k, const float* v, const float* g, const float* beta, const float* z,
+                              const float* normWeight, const infdev_query* queries, int queryCount, uint64_t stateOffset, uint64_t stateBytes,
+                              float* out);
 
 /* ---- attention ---- */
 /* init_rope (native_ops.metal:115-120): cos/sin table fp32 [positions,32,2] for theta = 1e7, evaluated on

@@ -69,6 +69,7 @@ void loadWeights(Engine& engine, const std::filesystem::path& path, Weights& wei
 struct Ops {
   Engine& engine;
   uint32_t rows = 0, queryCount = 0;
+  bool prefill = false;                   // the pass holds a non-speculative query of more than one row
   const infdev_query* queries = nullptr;  // device records of this pass
   Scratch& scratch;
   std::string prefix;
@@ -173,7 +174,8 @@ struct Ops {
                                scratch.q.as<float>(), scratch.k.as<float>(), scratch.v.as<float>(), scratch.gdnB.as<float>(),
                                scratch.gdnG.as<float>()));
       capture(scratch.temporaryImage);
-      check(infdev_delta_rule(ctx, scratch.q.as<float>(), scratch.k.as<float>(), scratch.v.as<float>(), scratch.gdnG.as<float>(),
+      // a pass that carries prefill chunks lets its long queries take the chunked kernel
+      check((prefill && rows > imageRows ? infdev_delta_rule_prefill : infdev_delta_rule)(ctx, scratch.q.as<float>(), scratch.k.as<float>(), scratch.v.as<float>(), scratch.gdnG.as<float>(),
                               scratch.gdnB.as<float>(), scratch.gate.as<float>(), f32("ssm_norm.weight"), queries, int(queryCount),
                               offset + INFDEV_CONV_STATE_BYTES, engine.stateBytes, scratch.temporary.as<float>()));
       supply(scratch.temporaryImage);
@@ -286,6 +288,7 @@ PassShape forward(Engine& engine, Batch& batch, bool drafting, bool launch) {
                                 engine.candidateStates ? engine.candidateStates.address() : 0, engine.stateBytes, deviceQueries,
                                 engine.passMeta.as<uint32_t>() + (drafting ? 4 : 0)));
   ops.rows = shape.rows;
+  ops.prefill = shape.prefill && !drafting;
   ops.queryCount = shape.queries;
   ops.queries = deviceQueries;
   Scratch& scratch = engine.workspace;

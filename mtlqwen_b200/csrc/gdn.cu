@@ -95,12 +95,15 @@ __global__ void __launch_bounds__(256) gdn_prepare_kernel(const float* x, const 
 // second to arrive reads both halves back and writes the block's image, then clears the entry.
 __global__ void __launch_bounds__(256) delta_rule_kernel(const float* q, const float* k, const float* v, const float* g, const float* beta,
                                                          const float* z, const float* normWeight, const infdev_query* queries,
-                                                         uint64_t stateOffset, uint64_t stateBytes, float* out, uint8_t* image, int* counters) {
+                                                         uint64_t stateOffset, uint64_t stateBytes, float* out, uint8_t* image, int* counters,
+                                                         uint32_t chunkedFrom) {
   pdl_launch_dependents();
   pdl_wait();
   const infdev_query info = queries[blockIdx.y];
   const int head = blockIdx.x, keyHead = head % kKeyHeads, tid = threadIdx.x, part = tid >> 5, lane = tid & 31;
   const bool speculative = info.state != kUnbound;
+  if (chunkedFrom && !speculative && info.count >= chunkedFrom)  // delta_rule_chunked_kernel takes this query
+    return;
   __shared__ float qs[kHeadDim], ks[kHeadDim], red[12], partialPred[8][kHeadDim], partialQ[8][kHeadDim], delta[kHeadDim], scalars[4];
 
   float4 S[16];
@@ -214,6 +217,187 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(const float* q, const f
   }
 }
 
+// ---- chunked form for long prefill queries -----------------------------------------------------------
+// Replaces delta_rule_prefill (delta_rule.metal:19-253): 16 tokens per step instead of one. With S0 the state
+// before the chunk, d_t the decay of token t, G_t = d_0 ... d_t and R[t][i] = G_t / G_i, the recurrence of
+// delta_rule_kernel unrolls to
+//   delta_t = beta_t * (v_t - G_t * S0^T k_t - sum_{i<t} R[t][i] (k_i . k_t) delta_i)        (a unit lower-triangular system)
+//   o_t     = G_t * S0^T q_t + sum_{i<=t} R[t][i] (k_i . q_t) delta_i
+//   S       = G_15 * S0 + sum_i (G_15 / G_i) k_i delta_i^T
+// All in fp32 on the CUDA cores, like the sequential kernel (so both agree to rounding): the two S0 products cost what
+// 16 sequential steps cost, but a chunk needs 5 block-wide barriers instead of 64, which is what bounds a prefill query
+// (one CTA per head, 128 dependent steps per pass).
+// grid (32 value heads, queries), 256 threads, same state ownership as delta_rule_kernel; serves the non-speculative
+// queries of at least `chunkedFrom` tokens. A last chunk of fewer than 16 tokens is padded with tokens of beta = 0,
+// k = q = 0 and decay 1, which change nothing.
+constexpr int kChunk = 16;
+struct ChunkShared {
+  float k[kChunk][kHeadDim + 4], q[kChunk][kHeadDim + 4], v[kChunk][kHeadDim];  // rows of k, q padded: column reads over 16 rows hit 16 banks
+  float partialK[kChunk][8][kHeadDim], partialQ[kChunk][8][kHeadDim];  // per-warp partial S0^T k_t, S0^T q_t
+  float ks[kChunk][kHeadDim], qs[kChunk][kHeadDim];                    // S0^T k_t, S0^T q_t
+  float u[kChunk][kHeadDim], o[kChunk][kHeadDim];                      // (G_15 / G_t) delta_t, o_t
+  float kk[kChunk][kChunk], qk[kChunk][kChunk];                        // R[t][i] (k_i . k_t), R[t][i] (k_i . q_t)
+  float cumulative[kChunk], beta[kChunk];                              // log G_t, beta_t
+};
+
+__global__ void __launch_bounds__(256) delta_rule_chunked_kernel(const float* q, const float* k, const float* v, const float* g, const float* beta,
+                                                                 const float* z, const float* normWeight, const infdev_query* queries,
+                                                                 uint64_t stateOffset, float* out, uint32_t chunkedFrom) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const infdev_query info = queries[blockIdx.y];
+  if (info.state != kUnbound || info.count < chunkedFrom)  // delta_rule_kernel takes this query
+    return;
+  extern __shared__ __align__(16) uint8_t chunkRaw[];
+  ChunkShared& sh = *reinterpret_cast<ChunkShared*>(chunkRaw);
+  const int head = blockIdx.x, keyHead = head % kKeyHeads, tid = threadIdx.x, part = tid >> 5, lane = tid & 31;
+
+  float4 S[16];
+  if (info.previous) {
+    const float4* src = reinterpret_cast<const float4*>(info.previous + stateOffset) + size_t(head) * kHeadDim * 32;
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      S[i] = src[(part + 8 * i) * 32 + lane];
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      S[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+
+  for (uint32_t first = 0; first < info.count; first += kChunk) {
+    const uint32_t live = min(uint32_t(kChunk), info.count - first);
+    // (a) normalised q (scaled by 1/sqrt(128)) and k, raw v, gates: warp w prepares tokens 2w and 2w+1
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const uint32_t t = 2 * part + j;
+      float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), kv = qv, vv = qv;
+      if (t < live) {
+        const size_t row = info.start + first + t;
+        qv = *reinterpret_cast<const float4*>(q + (row * kKeyHeads + keyHead) * kHeadDim + 4 * lane);
+        kv = *reinterpret_cast<const float4*>(k + (row * kKeyHeads + keyHead) * kHeadDim + 4 * lane);
+        vv = *reinterpret_cast<const float4*>(v + (row * kValueHeads + head) * kHeadDim + 4 * lane);
+      }
+      const float qq = warp_sum(qv.x * qv.x + qv.y * qv.y + qv.z * qv.z + qv.w * qv.w);
+      const float kq = warp_sum(kv.x * kv.x + kv.y * kv.y + kv.z * kv.z + kv.w * kv.w);
+      const float qn = rsqrtf(qq + 1.0e-6f) * 0.08838834764831845f, kn = rsqrtf(kq + 1.0e-6f);
+      *reinterpret_cast<float4*>(&sh.q[t][4 * lane]) = make_float4(qv.x * qn, qv.y * qn, qv.z * qn, qv.w * qn);
+      *reinterpret_cast<float4*>(&sh.k[t][4 * lane]) = make_float4(kv.x * kn, kv.y * kn, kv.z * kn, kv.w * kn);
+      *reinterpret_cast<float4*>(&sh.v[t][4 * lane]) = vv;
+    }
+    if (tid == 0) {
+      float running = 0.f;
+      for (uint32_t t = 0; t < kChunk; ++t) {
+        const size_t row = info.start + first + t;
+        running += t < live ? g[row * kValueHeads + head] : 0.f;
+        sh.cumulative[t] = running;
+        sh.beta[t] = t < live ? beta[row * kValueHeads + head] : 0.f;
+      }
+    }
+    __syncthreads();
+    // (b) per-warp partial products of the chunk's keys and queries with S0, and the token-by-token dot products
+#pragma unroll 2
+    for (int t = 0; t < kChunk; ++t) {
+      float4 pk = make_float4(0.f, 0.f, 0.f, 0.f), pq = pk;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float kv = sh.k[t][part + 8 * i], qv = sh.q[t][part + 8 * i];
+        pk.x = fmaf(S[i].x, kv, pk.x), pk.y = fmaf(S[i].y, kv, pk.y), pk.z = fmaf(S[i].z, kv, pk.z), pk.w = fmaf(S[i].w, kv, pk.w);
+        pq.x = fmaf(S[i].x, qv, pq.x), pq.y = fmaf(S[i].y, qv, pq.y), pq.z = fmaf(S[i].z, qv, pq.z), pq.w = fmaf(S[i].w, qv, pq.w);
+      }
+      *reinterpret_cast<float4*>(&sh.partialK[t][part][4 * lane]) = pk;
+      *reinterpret_cast<float4*>(&sh.partialQ[t][part][4 * lane]) = pq;
+    }
+    {
+      const int t = tid >> 4, i = tid & 15;  // one (t, i) pair per thread
+      float kk = 0.f, qk = 0.f;
+      if (i <= t) {
+#pragma unroll 8
+        for (int d = 0; d < kHeadDim; d += 4) {
+          const float4 a = *reinterpret_cast<const float4*>(&sh.k[i][d]), b = *reinterpret_cast<const float4*>(&sh.k[t][d]),
+                       c = *reinterpret_cast<const float4*>(&sh.q[t][d]);
+          kk += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+          qk += a.x * c.x + a.y * c.y + a.z * c.z + a.w * c.w;
+        }
+        const float ratio = expf(sh.cumulative[t] - sh.cumulative[i]);
+        kk *= ratio, qk *= ratio;
+      }
+      sh.kk[t][i] = i < t ? kk : 0.f;
+      sh.qk[t][i] = i <= t ? qk : 0.f;
+    }
+    __syncthreads();
+    // (c) sum the eight partials: 2048 values each for ks and qs, eight per thread
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int at = tid + 256 * j, t = at >> 7, d = at & 127;
+      float a = 0.f, b = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        a += sh.partialK[t][w][d];
+        b += sh.partialQ[t][w][d];
+      }
+      sh.ks[t][d] = a;
+      sh.qs[t][d] = b;
+    }
+    __syncthreads();
+    // (d) one thread per value column: forward substitution for delta, then the outputs
+    if (tid < kHeadDim) {
+      const float last = sh.cumulative[kChunk - 1];
+      float delta[kChunk];
+#pragma unroll
+      for (int t = 0; t < kChunk; ++t) {
+        const float decay = expf(sh.cumulative[t]);
+        float r = sh.v[t][tid] - decay * sh.ks[t][tid], o = decay * sh.qs[t][tid];
+#pragma unroll
+        for (int i = 0; i < t; ++i) {
+          r = fmaf(-sh.kk[t][i], delta[i], r);
+          o = fmaf(sh.qk[t][i], delta[i], o);
+        }
+        delta[t] = r * sh.beta[t];
+        o = fmaf(sh.qk[t][t], delta[t], o);
+        sh.u[t][tid] = delta[t] * expf(last - sh.cumulative[t]);
+        sh.o[t][tid] = o;
+      }
+    }
+    __syncthreads();
+    // (e) new state, and the outputs of the chunk through the gated norm: warp w writes tokens 2w and 2w+1
+    {
+      const float decay = expf(sh.cumulative[kChunk - 1]);
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        S[i].x *= decay, S[i].y *= decay, S[i].z *= decay, S[i].w *= decay;
+#pragma unroll 4
+      for (int t = 0; t < kChunk; ++t) {
+        const float4 u = *reinterpret_cast<const float4*>(&sh.u[t][4 * lane]);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float kv = sh.k[t][part + 8 * i];
+          S[i].x = fmaf(kv, u.x, S[i].x), S[i].y = fmaf(kv, u.y, S[i].y), S[i].z = fmaf(kv, u.z, S[i].z), S[i].w = fmaf(kv, u.w, S[i].w);
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const uint32_t t = 2 * part + j;
+      if (t < live) {
+        const size_t at = ((info.start + first + t) * kValueHeads + head) * kHeadDim + 4 * lane;
+        float4 o = *reinterpret_cast<const float4*>(&sh.o[t][4 * lane]);
+        if (z) {  // gated_rms_norm_128
+          const float scale = rsqrtf(warp_sum(o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w) / float(kHeadDim) + 1.0e-6f);
+          const float4 w = *reinterpret_cast<const float4*>(normWeight + 4 * lane), gate = *reinterpret_cast<const float4*>(z + at);
+          o = make_float4(o.x * scale * w.x * silu_f(gate.x), o.y * scale * w.y * silu_f(gate.y), o.z * scale * w.z * silu_f(gate.z),
+                          o.w * scale * w.w * silu_f(gate.w));
+        }
+        *reinterpret_cast<float4*>(out + at) = o;
+      }
+    }
+    __syncthreads();  // the chunk's shared arrays are rewritten by the next chunk
+  }
+  float4* dst = reinterpret_cast<float4*>(info.next + stateOffset) + size_t(head) * kHeadDim * 32;
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    dst[(part + 8 * i) * 32 + lane] = S[i];
+}
+
 }  // namespace
 
 cudaError_t gdn_prepare_launch(const float* x, const float* mixed, const float* wBeta, const float* wAlpha, const float* A, const float* dt,
@@ -228,11 +412,22 @@ cudaError_t gdn_prepare_launch(const float* x, const float* mixed, const float* 
 
 cudaError_t delta_rule_launch(const float* q, const float* k, const float* v, const float* g, const float* beta, const float* z,
                               const float* normWeight, const infdev_query* queries, int queryCount, uint64_t stateOffset, uint64_t stateBytes,
-                              float* out, uint8_t* image, int* counters, cudaStream_t stream) {
+                              float* out, uint8_t* image, int* counters, uint32_t chunkedFrom, cudaStream_t stream) {
   if (queryCount <= 0)
     return cudaSuccess;
+  if (chunkedFrom) {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(delta_rule_chunked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(ChunkShared)));
+      if (e != cudaSuccess)
+        return e;
+      configured = true;
+    }
+    launch_kernel(delta_rule_chunked_kernel, dim3(kValueHeads, unsigned(queryCount)), 256, sizeof(ChunkShared), stream, q, k, v, g, beta, z, normWeight,
+                  queries, stateOffset, out, chunkedFrom);
+  }
   launch_kernel(delta_rule_kernel, dim3(kValueHeads, unsigned(queryCount)), 256, 0, stream, q, k, v, g, beta, z, normWeight, queries, stateOffset, stateBytes,
-                                                                                  out, image, counters);
+                out, image, counters, chunkedFrom);
   return cudaGetLastError();
 }
 

@@ -625,8 +625,9 @@ int infdev_gdn_prepare(infdev_ctx* ctx, const float* x, const float* mixed, cons
                "gdn_prepare");
 }
 
-int infdev_delta_rule(infdev_ctx* ctx, const float* q, const float* k, const float* v, const float* g, const float* beta, const float* z,
-                      const float* normWeight, const infdev_query* queries, int queryCount, uint64_t stateOffset, uint64_t stateBytes, float* out) {
+static int delta_rule_common(infdev_ctx* ctx, const float* q, const float* k, const float* v, const float* g, const float* beta, const float* z,
+                             const float* normWeight, const infdev_query* queries, int queryCount, uint64_t stateOffset, uint64_t stateBytes,
+                             float* out, uint32_t chunkedFrom) {
   Bind bind(ctx);
   if (ctx->skip & 4) {
     take_capture(ctx);
@@ -634,11 +635,26 @@ int infdev_delta_rule(infdev_ctx* ctx, const float* q, const float* k, const flo
   }
   if (stateOffset % 16 || stateBytes % 16)
     return fail(ctx, INFDEV_E_ARGUMENT, "delta_rule: state offsets must be multiples of 16 bytes");
-  ctx->launches += 1;
+  if (chunkedFrom && ctx->captureImage) {
+    take_capture(ctx);
+    return fail(ctx, INFDEV_E_ARGUMENT, "delta_rule_prefill: writes no image of its result; use infdev_delta_rule for decode-sized passes");
+  }
+  ctx->launches += chunkedFrom ? 2 : 1;
   return check(ctx,
                infdev::delta_rule_launch(q, k, v, g, beta, z, normWeight, queries, queryCount, stateOffset, stateBytes, out, take_capture(ctx), ctx->imageCounters,
-                                         ctx->stream),
+                                         chunkedFrom, ctx->stream),
                "delta_rule");
+}
+
+int infdev_delta_rule(infdev_ctx* ctx, const float* q, const float* k, const float* v, const float* g, const float* beta, const float* z,
+                      const float* normWeight, const infdev_query* queries, int queryCount, uint64_t stateOffset, uint64_t stateBytes, float* out) {
+  return delta_rule_common(ctx, q, k, v, g, beta, z, normWeight, queries, queryCount, stateOffset, stateBytes, out, 0);
+}
+
+int infdev_delta_rule_prefill(infdev_ctx* ctx, const float* q, const float* k, const float* v, const float* g, const float* beta, const float* z,
+                              const float* normWeight, const infdev_query* queries, int queryCount, uint64_t stateOffset, uint64_t stateBytes,
+                              float* out) {
+  return delta_rule_common(ctx, q, k, v, g, beta, z, normWeight, queries, queryCount, stateOffset, stateBytes, out, 16);
 }
 
 // ---- attention ---------------------------------------------------------------------------------

@@ -75,6 +75,7 @@ def library():
     "infdev_rms_norm_gather": (i32, (vp, f32p, f32p, vp, i32, i64, f32p)),
     "infdev_gdn_prepare": (i32, (vp, f32p, f32p, f32p, f32p, f32p, f32p, f32p, vp, i32, i64, u64, u64, f32p, f32p, f32p, f32p, f32p)),
     "infdev_delta_rule": (i32, (vp, f32p, f32p, f32p, f32p, f32p, f32p, f32p, vp, i32, u64, u64, f32p)),
+    "infdev_delta_rule_prefill": (i32, (vp, f32p, f32p, f32p, f32p, f32p, f32p, f32p, vp, i32, u64, u64, f32p)),
     "infdev_rope_table": (i32, (vp, i64, f32p)),
     "infdev_attention_prepare": (i32, (vp, f32p, f32p, f32p, f32p, f32p, f32p, vp, i32, i64, vp, i32, i32, f32p, vp, vp)),
     "infdev_attention": (i32, (vp, f32p, f32p, vp, vp, vp, i32, i64, vp, i32, i32, u32, f32p, f32p)),
@@ -232,8 +233,10 @@ class Device:
     self.check(self.lib.infdev_gdn_prepare(self.ctx, x.ptr, mixed.ptr, w_beta.ptr, w_alpha.ptr, ssm_a.ptr, ssm_dt.ptr, conv_w.ptr, queries.ptr, nq,
                                            rows, state_offset, state_bytes, q.ptr, k.ptr, v.ptr, beta.ptr, g.ptr))
 
-  def delta_rule(self, q, k, v, g, beta, z, norm_w, queries, nq, state_offset, state_bytes, out):
-    self.check(self.lib.infdev_delta_rule(self.ctx, q.ptr, k.ptr, v.ptr, g.ptr, beta.ptr, z.ptr if z is not None else None,
+  def delta_rule(self, q, k, v, g, beta, z, norm_w, queries, nq, state_offset, state_bytes, out, prefill=False):
+    """prefill: long non-speculative queries take the chunked kernel (infdev_delta_rule_prefill)."""
+    call = self.lib.infdev_delta_rule_prefill if prefill else self.lib.infdev_delta_rule
+    self.check(call(self.ctx, q.ptr, k.ptr, v.ptr, g.ptr, beta.ptr, z.ptr if z is not None else None,
                                           norm_w.ptr if norm_w is not None else None, queries.ptr, nq, state_offset, state_bytes, out.ptr))
 
   def rope_table(self, positions):

@@ -22,7 +22,7 @@ def layer_weights(rng):
               conv=(0.5 * rng.standard_normal((8192, 4))).astype(np.float32), norm=(1 + 0.01 * rng.standard_normal(128)).astype(np.float32))
 
 
-def run_layer(dev, rng, lengths, fresh=(), speculative=()):
+def run_layer(dev, rng, lengths, fresh=(), speculative=(), prefill=False):
   """One GDN layer over len(lengths) queries packed back to back. `fresh` queries start from no state,
   `speculative` ones write one candidate state row per token."""
   w = layer_weights(rng)
@@ -56,12 +56,13 @@ def run_layer(dev, rng, lengths, fresh=(), speculative=()):
                   LAYER, q_out, k_out, v_out, beta, g)
   # The kernel also writes the quantised image of its output when asked; it must equal the quantisation of `out`.
   image, want_image = dev.empty(dev.image_bytes(rows, 4096), np.uint8), dev.empty(dev.image_bytes(rows, 4096), np.uint8)
-  if rows < 256:
+  capture = rows < 256 and not prefill  # the prefill variant writes no image
+  if capture:
     dev.image_capture(image)
-  dev.delta_rule(q_out, k_out, v_out, g, beta, dev.array(z), bufs["norm"], dq, nq, D.CONV_STATE_BYTES, LAYER, out)
+  dev.delta_rule(q_out, k_out, v_out, g, beta, dev.array(z), bufs["norm"], dq, nq, D.CONV_STATE_BYTES, LAYER, out, prefill=prefill)
   dev.quantize(out, rows, 4096, want_image)
   dev.commit()
-  if rows < 256:
+  if capture:
     for a, b in zip(images.decode(image.download(), rows, 4096), images.decode(want_image.download(), rows, 4096)):
       assert a.tobytes() == b.tobytes()
   got_out, got_next, got_cand = out.download(), next_.download(), candidates.download()
@@ -107,3 +108,30 @@ def test_gdn_single_query_edge_lengths(dev):
   rng = np.random.default_rng(4)
   for lengths in ([1], [2], [3], [4], [512]):
     assert run_layer(dev, rng, lengths, fresh=(0, )) < TOL
+
+
+def test_gdn_chunked_prefill_config2(dev):
+  """The same ragged lengths through infdev_delta_rule_prefill: queries of 16 tokens or more take the chunked kernel."""
+  rng = np.random.default_rng(2)
+  lengths = [int(v) for v in rng.integers(1, 513, 8)]
+  assert run_layer(dev, rng, lengths, prefill=True) < TOL
+
+
+def test_gdn_chunked_mixed_pass(dev):
+  """Chunked, sequential (short or speculative) and fresh queries in one pass; lengths around the 16-token chunk."""
+  rng = np.random.default_rng(5)
+  assert run_layer(dev, rng, [16, 15, 17, 1, 128, 40, 33, 31], fresh=(0, 4), speculative=(5, ), prefill=True) < TOL
+
+
+def test_gdn_chunked_agrees_with_sequential(dev):
+  """Both forms are fp32 on the CUDA cores and must agree far inside the tolerance against the oracle."""
+  a = run_layer(dev, np.random.default_rng(6), [100, 64], prefill=False)
+  b = run_layer(dev, np.random.default_rng(6), [100, 64], prefill=True)
+  assert a < TOL and b < TOL and abs(a - b) < 2e-4
+
+
+def test_prefill_variant_refuses_an_image(dev):
+  dev.image_capture(dev.empty(dev.image_bytes(8, 4096), np.uint8))
+  with pytest.raises(RuntimeError, match="no image"):
+    dev.delta_rule(dev.empty(1), dev.empty(1), dev.empty(1), dev.empty(1), dev.empty(1), None, None, dev.queries([D.Query()]), 1, 0, LAYER, dev.empty(1),
+                   prefill=True)
