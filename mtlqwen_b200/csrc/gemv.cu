@@ -1,4 +1,5 @@
-// Dequant-fused GEMV for decode (M <= 8 activation rows) over GGUF Q4_K / Q6_K weights.
+// Dequant-fused fp16 tensor-core GEMV for decode (M <= 8 activation rows) over GGUF Q4_K / Q6_K weights. It serves
+// every Q6_K matrix (lm_head) and, when the integer kernel of q4k_decode.cu is switched off, the Q4_K ones.
 //
 // Replaces linear_decode_q4_k[_add] (quant_linear.metal:245-327), linear_decode_q6_k[_add] (:436-512) and
 // mlp_gate_up_q4_k_decode (fused_kernels.metal:11-78). The reference re-reads the weights once per
@@ -6,8 +7,8 @@
 //
 // Design (one persistent CTA per SM, 8 consumer warps + 1 producer warp):
 //  * The weight matrix is a contiguous byte stream (row n = K/256 super-blocks). The producer warp moves
-//    16-row x 8-super-block slabs into a shared-memory ring with untiled bulk copies (cp.async.bulk)
-//    that complete on mbarriers; nothing else touches HBM for the weights.
+//    16-row x 8-super-block slabs into a shared-memory ring with one tiled TMA copy each (a tensor map over
+//    the packed rows as 8-byte elements) that completes on an mbarrier; nothing else touches HBM for the weights.
 //  * At 8 rows the fp32 FMA pipe cannot keep up with HBM (8 FMAs per 4-bit weight), so the products run
 //    on the tensor cores as m16n8k16: A = 16 weight rows x 16 k, B = 16 k x 8 activation rows.
 //    The summation index of an MMA is a dummy, so k is permuted freely to suit the packed layout; the

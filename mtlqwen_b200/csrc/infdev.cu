@@ -23,6 +23,7 @@ struct infdev_ctx {
   int* imageCounters = nullptr;        // arrival counters of the kernels that write images block by block (zero between launches)
   uint8_t* captureImage = nullptr;     // one-shot: where the next producer call writes the image of its result
   const uint8_t* supplyImage = nullptr;  // one-shot: image the next linear call reads instead of quantising x
+  float* ummaPartial = nullptr;  // K-slice partial results of the tcgen05 prefill GEMM: [4][128][8192] floats, allocated on first use
   void* ummaActs = nullptr;  // prepared activations + sums for the tcgen05 path (K up to 16384)
   float* ummaSums = nullptr;
   std::atomic<uint64_t> launches{0};  // kernels launched through this context
@@ -203,6 +204,7 @@ void infdev_destroy(infdev_ctx* ctx) {
   cudaFree(ctx->status);
   cudaFree(ctx->image);
   cudaFree(ctx->imageCounters);
+  cudaFree(ctx->ummaPartial);
   cudaFree(ctx->ummaActs);
   cudaFree(ctx->ummaSums);
   cudaFreeHost(ctx->statusHost);
@@ -468,6 +470,18 @@ static int linear_run(infdev_ctx* ctx, int type, bool pair, int count, const voi
     }
     u.tiles = tiles;
     u.k = int(k);
+    // A matrix of few 128-row tiles (n = 4096: 32 of them) would leave most SMs idle during prefill: cut K into slices.
+    u.splits = 1;
+    if (!pair && count == 1 && m > 8 && n[0] <= 8192 && n[0] % 4 == 0)
+      for (int s = 4; s > 1; --s)
+        if ((k / 256) % s == 0 && tiles * s <= ctx->sms) {
+          u.splits = s;
+          break;
+        }
+    if (u.splits > 1 && !ctx->ummaPartial)
+      if (int r = check(ctx, cudaMalloc(reinterpret_cast<void**>(&ctx->ummaPartial), size_t(4) * 128 * 8192 * sizeof(float)), "prefill partial buffer"))
+        return r;
+    u.partial = ctx->ummaPartial;
     u.acts = static_cast<const uint8_t*>(ctx->ummaActs);
     u.actSums = ctx->ummaSums;
     u.status = ctx->status;
@@ -481,7 +495,7 @@ static int linear_run(infdev_ctx* ctx, int type, bool pair, int count, const voi
       }
       if (int r = check(ctx, infdev::umma_launch(pair, u, x + row * k, int(k), ctx->sms, ctx->stream), "umma launch"))
         return r;
-      ctx->launches += 2;
+      ctx->launches += u.splits > 1 ? 3 : 2;
     }
     return INFDEV_OK;
   }

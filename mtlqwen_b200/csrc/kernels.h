@@ -44,6 +44,10 @@ struct UmmaParams {
   alignas(64) CUtensorMap map[4][2];  // box = one super-block (18 x 8 bytes) x 128 rows
   GemvSeg seg[4];
   int nseg, tiles;  // tiles of 128 rows
+  // Prefill mode, one matrix: K is cut into `splits` slices that different CTAs take; their partial results go to
+  // `partial` [splits][m][n] and are summed (with the residual) by a second small kernel, in a fixed order.
+  int splits;
+  float* partial;
   int m, k;
   const uint8_t* acts;   // prepared activations: k/256 blocks of kUmmaActBytesPerBlock
   const float* actSums;  // [k/256][8 sub-blocks][8 rows]

@@ -119,7 +119,9 @@ template <int NMAT, int NACT> __global__ void __launch_bounds__(kThreads, 1) umm
   uint8_t* ring = smem + kControlBytes + kScaleBytes + kMinBytes;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int blocksPerRow = p.k / 256;
+  // With p.splits > 1 (prefill mode, one matrix) the work items are (tile, K slice) pairs, so that a matrix of few
+  // 128-row tiles still fills the GPU; `blocksPerRow` is then the super-blocks of one slice.
+  const int blocksPerRow = p.k / 256 / p.splits, items = p.tiles * p.splits;
   // A "unit" owns one accumulator buffer: 8 super-blocks in decode mode, a whole (tile, matrix) in prefill mode.
   const int unitsPerMat = kDecode ? blocksPerRow / kChunkSb : 1, blocksPerUnit = kDecode ? kChunkSb : blocksPerRow;
   volatile int* abortFlag = &ctl.abort;
@@ -149,13 +151,14 @@ template <int NMAT, int NACT> __global__ void __launch_bounds__(kThreads, 1) umm
     // ---------------- producer: one weight slab + its activation fragments per super-block ----------------
     uint32_t it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x) {
+    for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+      const int tile = item % p.tiles, firstBlock = (item / p.tiles) * blocksPerRow;
       int segment = 0;
       while (segment + 1 < p.nseg && tile >= p.seg[segment + 1].tile0)
         ++segment;
       const int row0 = (tile - p.seg[segment].tile0) * kRows;
       for (int mat = 0; mat < NMAT && ok; ++mat)
-        for (int sb = 0; sb < blocksPerRow && ok; ++sb, ++it) {
+        for (int sb = firstBlock; sb < firstBlock + blocksPerRow && ok; ++sb, ++it) {
           const uint32_t slot = it % kStages, round = it / kStages;
           if (lane == 0) {
             if (round > 0)
@@ -178,7 +181,7 @@ template <int NMAT, int NACT> __global__ void __launch_bounds__(kThreads, 1) umm
     if (lane == 0) {
       uint32_t it = 0, unit = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x)
+      for (int item = blockIdx.x; item < items && ok; item += gridDim.x)
         for (int mat = 0; mat < NMAT && ok; ++mat)
           for (int chunk = 0; chunk < unitsPerMat && ok; ++chunk, ++unit) {
             const uint32_t buffer = unit & 1;
@@ -216,7 +219,7 @@ template <int NMAT, int NACT> __global__ void __launch_bounds__(kThreads, 1) umm
     constexpr uint32_t k1024 = 0x64006400u, kNeg1024 = 0xE400E400u, kSixteenth = 0x2C002C00u, kNeg64 = 0xD400D400u;
     uint32_t it = 0, unit = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x)
+    for (int item = blockIdx.x; item < items && ok; item += gridDim.x)
       for (int mat = 0; mat < NMAT && ok; ++mat)
         for (int chunk = 0; chunk < unitsPerMat && ok; ++chunk, ++unit) {
           const uint32_t buffer = unit & 1;
@@ -314,7 +317,8 @@ template <int NMAT, int NACT> __global__ void __launch_bounds__(kThreads, 1) umm
     const uint32_t laneBase = tmem + (uint32_t(quadrant * 32) << 16) + kColD;
     uint32_t unit = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x) {
+    for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+      const int tile = item % p.tiles, slice = item / p.tiles;
       int segment = 0;
       while (segment + 1 < p.nseg && tile >= p.seg[segment + 1].tile0)
         ++segment;
@@ -383,6 +387,10 @@ template <int NMAT, int NACT> __global__ void __launch_bounds__(kThreads, 1) umm
               if (m < p.m) {
                 const size_t at = size_t(m) * seg.ldy + column;
                 float value = v[i];
+                if (NMAT == 1 && p.splits > 1) {  // a K slice: the partial sums are added up, with the residual, by umma_reduce_kernel
+                  p.partial[(size_t(slice) * p.m + m) * seg.ldy + column] = value;
+                  continue;
+                }
                 if (NMAT == 2)  // the gate half parks in y until the up half arrives (post == 2 epilogue, quant_linear.metal:224-232)
                   value = mat == 0 ? value : silu_f(seg.y[at]) * value;
                 else if (seg.res)
@@ -448,6 +456,47 @@ template <int NACT> __global__ void __launch_bounds__(256) umma_prepare_kernel(c
   }
 }
 
+// Prefill-mode form of the same layout, vectorised: eight consecutive k of a super-block are one 16-byte core-matrix
+// row of a k-step (in the order 0,2,1,3,4,6,5,7), so a thread turns two float4 loads into one 16-byte store.
+// grid (k / 256, 4), 256 threads: 128 rows x 32 groups of eight per super-block, four items per thread; a warp reads one
+// activation row's 256 values at a time.
+__global__ void __launch_bounds__(256) umma_prepare_rows_kernel(const float* x, int ldx, int m, __half* acts) {
+  constexpr int kRowsB = 128;
+  const int sb = blockIdx.x;
+  __half* out = acts + size_t(sb) * (Mode<kRowsB>::kActBytesPerSb / 2);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int item = (blockIdx.y * 4 + j) * 256 + threadIdx.x, n = item >> 5, group = item & 31;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+    if (n < m) {
+      const float4* src = reinterpret_cast<const float4*>(x + size_t(n) * ldx + size_t(sb) * 256 + group * 8);
+      a = src[0], b = src[1];
+    }
+    const __half2 h0 = __floats2half2_rn(a.x, a.z), h1 = __floats2half2_rn(a.y, a.w), h2 = __floats2half2_rn(b.x, b.z), h3 = __floats2half2_rn(b.y, b.w);
+    uint4 packed;
+    packed.x = *reinterpret_cast<const uint32_t*>(&h0), packed.y = *reinterpret_cast<const uint32_t*>(&h1);
+    packed.z = *reinterpret_cast<const uint32_t*>(&h2), packed.w = *reinterpret_cast<const uint32_t*>(&h3);
+    *reinterpret_cast<uint4*>(out + size_t(group >> 1) * (kRowsB * 16) + (n >> 3) * 128 + (group & 1) * 64 + (n & 7) * 8) = packed;
+  }
+}
+
+// y = partial[0] + partial[1] + ... (+ residual), four values per thread.
+__global__ void __launch_bounds__(256) umma_reduce_kernel(const float* partial, int splits, size_t count, const float* residual, float* y) {
+  const size_t at = (size_t(blockIdx.x) * 256 + threadIdx.x) * 4;
+  if (at >= count)
+    return;
+  float4 sum = *reinterpret_cast<const float4*>(partial + at);
+  for (int s = 1; s < splits; ++s) {
+    const float4 v = *reinterpret_cast<const float4*>(partial + s * count + at);
+    sum.x += v.x, sum.y += v.y, sum.z += v.z, sum.w += v.w;
+  }
+  if (residual) {
+    const float4 v = *reinterpret_cast<const float4*>(residual + at);
+    sum.x += v.x, sum.y += v.y, sum.z += v.z, sum.w += v.w;
+  }
+  *reinterpret_cast<float4*>(y + at) = sum;
+}
+
 template <int NMAT, int NACT> cudaError_t launch_mode(const UmmaParams& p, const float* x, int ldx, int sms, cudaStream_t stream) {
   static bool configured = false;
   constexpr size_t bytes = smem_bytes<NACT>();
@@ -457,11 +506,19 @@ template <int NMAT, int NACT> cudaError_t launch_mode(const UmmaParams& p, const
       return e;
     configured = true;
   }
-  if (!(p.debug & 4))
-    umma_prepare_kernel<NACT><<<p.k / 256, 256, 0, stream>>>(x, ldx, p.m, reinterpret_cast<__half*>(const_cast<uint8_t*>(p.acts)),
-                                                              const_cast<float*>(p.actSums));
-  const int grid = p.tiles < sms ? p.tiles : sms;
+  if (!(p.debug & 4)) {
+    if (NACT == 128 && ldx % 4 == 0)
+      umma_prepare_rows_kernel<<<dim3(p.k / 256, 4), 256, 0, stream>>>(x, ldx, p.m, reinterpret_cast<__half*>(const_cast<uint8_t*>(p.acts)));
+    else
+      umma_prepare_kernel<NACT><<<p.k / 256, 256, 0, stream>>>(x, ldx, p.m, reinterpret_cast<__half*>(const_cast<uint8_t*>(p.acts)),
+                                                                const_cast<float*>(p.actSums));
+  }
+  const int items = p.tiles * p.splits, grid = items < sms ? items : sms;
   umma_linear_kernel<NMAT, NACT><<<grid, kThreads, bytes, stream>>>(p);
+  if (p.splits > 1) {
+    const size_t count = size_t(p.m) * p.seg[0].ldy;
+    umma_reduce_kernel<<<unsigned((count / 4 + 255) / 256), 256, 0, stream>>>(p.partial, p.splits, count, p.seg[0].res, p.seg[0].y);
+  }
   return cudaGetLastError();
 }
 
