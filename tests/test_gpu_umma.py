@@ -67,3 +67,16 @@ def test_group_launch_on_tcgen05_path(umma):
   umma.linear_group(D.Q4_K, [umma.array(w) for w in ws], ns, k, umma.array(x), m, ys)
   for w, n, y in zip(ws, ns, ys):
     assert rel_err(y.download(), oracle.linear(w, D.Q4_K, n, k, x)) < 2e-5
+
+
+def test_prefill_k_slices(umma):
+  """A matrix of few 128-row tiles is cut along K (three launches: layout, GEMM over (tile, slice) items, fixed-order
+  sum of the slices plus residual); the result is reproducible bit for bit."""
+  n, k, m = 4096, 12288, 128
+  w, x, res = umma.array(synth.weight(D.Q4_K, n, k, 900)), umma.array(synth.activations(m, k, 901)), umma.array(synth.activations(m, n, 902))
+  a, b = umma.empty((m, n)), umma.empty((m, n))
+  before = umma.launch_count
+  umma.linear(D.Q4_K, w, n, k, x, m, a, res)
+  assert umma.launch_count - before == 3
+  umma.linear(D.Q4_K, w, n, k, x, m, b, res)
+  assert a.download().tobytes() == b.download().tobytes()
