@@ -34,26 +34,33 @@ constexpr int kThreads = 512;
 //             one MMA per k-step yields both products. A holds the exact integers sc*q; one accumulator per super-block.
 //  NACT = 128 prefill: up to 128 activation rows in fp16 (hi only); A holds the dequantised weight d*sc*q - dmin*m
 //             rounded to fp16, one accumulator per tile (the GEMM of linear_prefill, quant_linear.metal:151-233).
+// Shared-memory rings. Decode: 7 stages of one weight slab + its activations (26,624 bytes). Prefill: the fp16
+// activations of a super-block are 64 KB, so slab and activations travel separately and the activations in two halves
+// of eight k-steps each: 3 slab stages + 5 half stages keep two and a half super-blocks in flight (with whole
+// super-blocks as stages only two fit, and every dequantisation group then waited out a full TMA latency per block).
 template <int NACT> struct Mode {
   static constexpr int kActBytesPerSb = 16 * NACT * 16 * 2;             // 16 k-steps x [NACT x 16] fp16
-  static constexpr int kStageBytes = kSlabBytes + kActBytesPerSb;      // 26,624 / 83,968
-  static constexpr int kStages = NACT == 16 ? 7 : 2;
+  static constexpr int kStageBytes = NACT == 16 ? kSlabBytes + kActBytesPerSb : kSlabBytes;  // 26,624 / 18,432
+  static constexpr int kStages = NACT == 16 ? 7 : 3;
+  static constexpr int kActStages = 5, kActHalfBytes = kActBytesPerSb / 2;  // prefill only
   static constexpr uint32_t kInstruction = (1u << 4) | (uint32_t(NACT >> 3) << 17) | (uint32_t(kRows >> 4) << 24);
 };
 constexpr int kTmemCols = 512;
 constexpr uint32_t kColA = 0, kColD = 256;  // A: 2 x 128 columns; D: 2 x (8 super-blocks x 16 columns)
 
 struct Control {
-  uint64_t full[8], slotFree[8], aReady[2], aFree[2], dReady[2], dFree[2];
+  uint64_t full[8], slotFree[8], actFull[8], actFree[8], aReady[2], aFree[2], dReady[2], dFree[2];
   uint32_t tmemBase;
   int abort;
 };
-constexpr int kControlBytes = 256;
+constexpr int kControlBytes = 512;
 static_assert(sizeof(Control) <= kControlBytes, "control block too large");
 constexpr int kScaleBytes = 2 * kChunkSb * kRows * 4;  // d of every (buffer, super-block, row): 8,192
 constexpr int kMinBytes = 2 * 2 * kRows * 8 * 4;       // min-term partials [buffer][group][row][8]: 16,384
-template <int NACT> constexpr size_t smem_bytes() {
-  return 1024 + kControlBytes + kScaleBytes + kMinBytes + size_t(Mode<NACT>::kStages) * Mode<NACT>::kStageBytes;
+template <int NACT> constexpr size_t smem_bytes() {  // the scale / min tables belong to decode mode
+  return NACT == 16 ? 1024 + kControlBytes + kScaleBytes + kMinBytes + size_t(Mode<NACT>::kStages) * Mode<NACT>::kStageBytes
+                    : 1024 + kControlBytes + size_t(Mode<NACT>::kStages) * Mode<NACT>::kStageBytes +
+                          size_t(Mode<NACT>::kActStages) * Mode<NACT>::kActHalfBytes;
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t columns) {
@@ -114,9 +121,10 @@ template <int NMAT, int NACT> __global__ void __launch_bounds__(kThreads, 1) umm
   extern __shared__ uint8_t smemRaw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
   Control& ctl = *reinterpret_cast<Control*>(smem);
-  float* dScale = reinterpret_cast<float*>(smem + kControlBytes);                 // [2][8][128]
-  float* minPart = reinterpret_cast<float*>(smem + kControlBytes + kScaleBytes);  // [2][2][128][8]
-  uint8_t* ring = smem + kControlBytes + kScaleBytes + kMinBytes;
+  float* dScale = reinterpret_cast<float*>(smem + kControlBytes);                 // [2][8][128], decode mode
+  float* minPart = reinterpret_cast<float*>(smem + kControlBytes + kScaleBytes);  // [2][2][128][8], decode mode
+  uint8_t* ring = smem + kControlBytes + (kDecode ? kScaleBytes + kMinBytes : 0);
+  uint8_t* actRing = ring + size_t(kStages) * kStageBytes;  // prefill mode: halves of a super-block's activations
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // With p.splits > 1 (prefill mode, one matrix) the work items are (tile, K slice) pairs, so that a matrix of few
@@ -129,7 +137,11 @@ template <int NMAT, int NACT> __global__ void __launch_bounds__(kThreads, 1) umm
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&ctl.full[s], 1);
-      mbar_init(&ctl.slotFree[s], 5);  // four dequant warps + the MMA commit
+      mbar_init(&ctl.slotFree[s], kDecode ? 5 : 4);  // four dequant warps (+ the MMA commit where the stage holds activations)
+    }
+    for (int s = 0; s < M::kActStages; ++s) {
+      mbar_init(&ctl.actFull[s], 1);
+      mbar_init(&ctl.actFree[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&ctl.aReady[b], 4);
@@ -167,8 +179,20 @@ template <int NMAT, int NACT> __global__ void __launch_bounds__(kThreads, 1) umm
               uint8_t* stage = ring + size_t(slot) * kStageBytes;
               mbar_arrive_expect_tx(&ctl.full[slot], kStageBytes);
               tma_load_2d(stage, &p.map[segment][mat], sb * 18, row0, &ctl.full[slot]);
-              bulk_load(stage + kSlabBytes, p.acts + size_t(sb) * M::kActBytesPerSb, M::kActBytesPerSb, &ctl.full[slot]);
-            } else {
+              if (kDecode)
+                bulk_load(stage + kSlabBytes, p.acts + size_t(sb) * M::kActBytesPerSb, M::kActBytesPerSb, &ctl.full[slot]);
+            }
+            for (int h = 0; h < 2 && ok && !kDecode; ++h) {  // the two activation halves of this super-block
+              const uint32_t half = 2 * it + h, actSlot = half % M::kActStages, actRound = half / M::kActStages;
+              if (actRound > 0)
+                ok = mbar_wait_bounded(&ctl.actFree[actSlot], (actRound - 1) & 1, abortFlag);
+              if (ok) {
+                mbar_arrive_expect_tx(&ctl.actFull[actSlot], M::kActHalfBytes);
+                bulk_load(actRing + size_t(actSlot) * M::kActHalfBytes, p.acts + size_t(sb) * M::kActBytesPerSb + size_t(h) * M::kActHalfBytes,
+                          M::kActHalfBytes, &ctl.actFull[actSlot]);
+              }
+            }
+            if (!ok) {
               *abortFlag = 1;
               atomicExch(p.status, kStatusBarrierTimeout);
             }
@@ -193,16 +217,36 @@ template <int NMAT, int NACT> __global__ void __launch_bounds__(kThreads, 1) umm
               if (!ok)
                 break;
               fence_after_sync();
-              const uint32_t actBase = smem_u32(ring + size_t(slot) * kStageBytes + kSlabBytes);
               // decode: 16 columns per super-block; prefill: one 128-column accumulator per unit
               const uint32_t dColumn = tmem + kColD + buffer * 128 + (kDecode ? j * 16 : 0);
-              if (!(p.debug & 1))
+              if (kDecode) {
+                const uint32_t actBase = smem_u32(ring + size_t(slot) * kStageBytes + kSlabBytes);
+                if (!(p.debug & 1))
 #pragma unroll
-                for (int step = 0; step < 16; ++step)
-                  umma_ts(dColumn, tmem + kColA + aBuffer * 128 + step * 8, smem_descriptor(actBase + step * (NACT * 32), 128, 256), M::kInstruction,
-                          kDecode ? step != 0 : (j | step) != 0);
-              umma_commit(&ctl.aFree[aBuffer]);
-              umma_commit(&ctl.slotFree[slot]);
+                  for (int step = 0; step < 16; ++step)
+                    umma_ts(dColumn, tmem + kColA + aBuffer * 128 + step * 8, smem_descriptor(actBase + step * (NACT * 32), 128, 256), M::kInstruction,
+                            step != 0);
+                umma_commit(&ctl.aFree[aBuffer]);
+                umma_commit(&ctl.slotFree[slot]);
+              } else {
+                for (int h = 0; h < 2 && ok; ++h) {  // eight k-steps per activation half
+                  const uint32_t half = 2 * it + h, actSlot = half % M::kActStages;
+                  ok = mbar_wait_bounded(&ctl.actFull[actSlot], (half / M::kActStages) & 1, abortFlag);
+                  if (!ok)
+                    break;
+                  fence_after_sync();
+                  const uint32_t actBase = smem_u32(actRing + size_t(actSlot) * M::kActHalfBytes);
+                  if (!(p.debug & 1))
+#pragma unroll
+                    for (int step = 0; step < 8; ++step)
+                      umma_ts(dColumn, tmem + kColA + aBuffer * 128 + (8 * h + step) * 8, smem_descriptor(actBase + step * (NACT * 32), 128, 256),
+                              M::kInstruction, (j | h | step) != 0);
+                  umma_commit(&ctl.actFree[actSlot]);
+                }
+                if (!ok)
+                  break;
+                umma_commit(&ctl.aFree[aBuffer]);
+              }
               if (j == blocksPerUnit - 1)
                 umma_commit(&ctl.dReady[buffer]);
             }
