@@ -182,6 +182,18 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(const float* q, const f
       } else
         out[at] = o;
     }
+    // The count of the image protocol is taken before the state is written: the fence then covers only the 128 output
+    // stores, and the answer travels while the state update runs.
+    const bool imaged = image && row < kImageCounters / (kValueHeads / 2);  // block-uniform; later rows have no counter and get no image
+    __shared__ int arrivals;
+    const int entry = int(row) * (kValueHeads / 2) + (head >> 1);
+    if (imaged) {
+      __syncthreads();  // all of this CTA's stores to `out` are issued
+      if (tid == 0) {
+        __threadfence();
+        arrivals = atomicAdd(&counters[entry], 1);
+      }
+    }
     const float4 d4 = *reinterpret_cast<const float4*>(&delta[lane * 4]);
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -194,15 +206,8 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(const float* q, const f
       for (int i = 0; i < 16; ++i)
         dst[(part + 8 * i) * 32 + lane] = S[i];
     }
-    __syncthreads();  // qs/ks/delta/red are rewritten by the next token
-    if (image && row < kImageCounters / (kValueHeads / 2)) {  // block-uniform; later rows have no counter and get no image
-      __shared__ int arrivals;
-      const int entry = int(row) * (kValueHeads / 2) + (head >> 1);
-      if (tid == 0) {
-        __threadfence();  // this CTA's stores to `out` (ordered by the barrier above) before the count
-        arrivals = atomicAdd(&counters[entry], 1);
-      }
-      __syncthreads();
+    __syncthreads();  // qs/ks/delta/red are rewritten by the next token; `arrivals` is published
+    if (imaged) {
       if (arrivals == 1 && tid < 32) {
         __threadfence();
         const float* src = out + (row * kValueHeads + (head & ~1)) * kHeadDim + tid * 8;
