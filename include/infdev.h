@@ -155,6 +155,12 @@ int infdev_gdn_prepare(infdev_ctx* ctx, const float* x, const float* mixed, cons
  * stateOffset here addresses the layer's recurrent state S fp32 [32][128][128] inside a record. */
 int infdev_delta_rule(infdev_ctx* ctx, const float* q, const float* k, const float* v, const float* g, const float* beta, const float* z,
                       const float* normWeight, const infdev_query* queries, int queryCount, uint64_t stateOffset, uint64_t stateBytes, float* out);
+/* infdev_gdn_prepare followed by infdev_delta_rule (gated) in one launch, for passes whose queries are all short (decode
+ * rows, speculative rows): every (sequence, head) CTA prepares its own 384 channels and its beta / g. Same arithmetic,
+ * same results; the intermediate q, k, v, beta, g are not written. */
+int infdev_gdn_decode(infdev_ctx* ctx, const float* x, const float* mixed, const float* wBeta, const float* wAlpha, const float* ssmA,
+                      const float* ssmDt, const float* convWeight, const float* z, const float* normWeight, const infdev_query* queries,
+                      int queryCount, uint64_t convStateOffset, uint64_t stateOffset, uint64_t stateBytes, float* out);
 /* The same for a pass that holds prefill chunks: non-speculative queries of at least 16 tokens take the chunked form
  * (16 tokens per step, the role of delta_rule_prefill, delta_rule.metal:19-253), every other query the sequential one.
  * Results agree with infdev_delta_rule to fp32 rounding. Two launches; no image of the result (a pending

@@ -169,15 +169,25 @@ struct Ops {
     } else {
       linearGroup(x, {{&weight("attn_qkv.weight"), scratch.mixed}, {&weight("attn_gate.weight"), scratch.gate}}, rows);
       const uint64_t offset = uint64_t(layer - layer / fullAttentionInterval) * INFDEV_GDN_LAYER_STATE_BYTES;
-      check(infdev_gdn_prepare(ctx, x.as<float>(), scratch.mixed.as<float>(), f32("ssm_beta.weight"), f32("ssm_alpha.weight"), f32("ssm_a"),
-                               f32("ssm_dt.bias"), f32("ssm_conv1d.weight"), queries, int(queryCount), rows, offset, engine.stateBytes,
-                               scratch.q.as<float>(), scratch.k.as<float>(), scratch.v.as<float>(), scratch.gdnB.as<float>(),
-                               scratch.gdnG.as<float>()));
-      capture(scratch.temporaryImage);
-      // a pass that carries prefill chunks lets its long queries take the chunked kernel
-      check((prefill && rows > imageRows ? infdev_delta_rule_prefill : infdev_delta_rule)(ctx, scratch.q.as<float>(), scratch.k.as<float>(), scratch.v.as<float>(), scratch.gdnG.as<float>(),
-                              scratch.gdnB.as<float>(), scratch.gate.as<float>(), f32("ssm_norm.weight"), queries, int(queryCount),
-                              offset + INFDEV_CONV_STATE_BYTES, engine.stateBytes, scratch.temporary.as<float>()));
+      if (!prefill) {
+        // every query of the pass is short: preparation and recurrence in one launch
+        capture(scratch.temporaryImage);
+        check(infdev_gdn_decode(ctx, x.as<float>(), scratch.mixed.as<float>(), f32("ssm_beta.weight"), f32("ssm_alpha.weight"), f32("ssm_a"),
+                                f32("ssm_dt.bias"), f32("ssm_conv1d.weight"), scratch.gate.as<float>(), f32("ssm_norm.weight"), queries,
+                                int(queryCount), offset, offset + INFDEV_CONV_STATE_BYTES, engine.stateBytes, scratch.temporary.as<float>()));
+      } else {
+        check(infdev_gdn_prepare(ctx, x.as<float>(), scratch.mixed.as<float>(), f32("ssm_beta.weight"), f32("ssm_alpha.weight"), f32("ssm_a"),
+                                 f32("ssm_dt.bias"), f32("ssm_conv1d.weight"), queries, int(queryCount), rows, offset, engine.stateBytes,
+                                 scratch.q.as<float>(), scratch.k.as<float>(), scratch.v.as<float>(), scratch.gdnB.as<float>(),
+                                 scratch.gdnG.as<float>()));
+        capture(scratch.temporaryImage);
+        // a pass that carries prefill chunks lets its long queries take the chunked kernel
+        check((rows > imageRows ? infdev_delta_rule_prefill : infdev_delta_rule)(ctx, scratch.q.as<float>(), scratch.k.as<float>(), scratch.v.as<float>(),
+                                                                                 scratch.gdnG.as<float>(), scratch.gdnB.as<float>(),
+                                                                                 scratch.gate.as<float>(), f32("ssm_norm.weight"), queries,
+                                                                                 int(queryCount), offset + INFDEV_CONV_STATE_BYTES,
+                                                                                 engine.stateBytes, scratch.temporary.as<float>()));
+      }
       supply(scratch.temporaryImage);
       linear(scratch.temporary, weight("ssm_out.weight"), rows, hidden, hidden);
     }

@@ -93,10 +93,20 @@ __global__ void __launch_bounds__(256) gdn_prepare_kernel(const float* x, const 
 // `image`, when not null, also receives the activation image of `out`. A 256-value block holds two heads, which two
 // CTAs produce: each adds one to the block's entry in `counters` (zero between launches) after its stores, and the
 // second to arrive reads both halves back and writes the block's image, then clears the entry.
-__global__ void __launch_bounds__(256) delta_rule_kernel(const float* q, const float* k, const float* v, const float* g, const float* beta,
+// FUSED: the preparation of gdn_prepare_kernel happens here as well, for this CTA's channels only: the conv + SiLU of
+// its 128 q, k and v channels (the taps of the q / k channels are written by the first of the two value heads that
+// share a key head) and its beta / g dot products, with the same arithmetic and summation order; q, k, v, g, beta
+// are then not read. One launch less per layer for passes without prefill chunks.
+struct GdnInputs {
+  const float *x, *wBeta, *wAlpha, *A, *dt, *mixed, *convWeight;
+  uint64_t convStateOffset;
+};
+
+template <bool FUSED>
+__global__ void __launch_bounds__(256, 2) delta_rule_kernel(const float* q, const float* k, const float* v, const float* g, const float* beta,
                                                          const float* z, const float* normWeight, const infdev_query* queries,
                                                          uint64_t stateOffset, uint64_t stateBytes, float* out, uint8_t* image, int* counters,
-                                                         uint32_t chunkedFrom) {
+                                                         uint32_t chunkedFrom, GdnInputs in) {
   pdl_launch_dependents();
   pdl_wait();
   const infdev_query info = queries[blockIdx.y];
@@ -104,7 +114,7 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(const float* q, const f
   const bool speculative = info.state != kUnbound;
   if (chunkedFrom && !speculative && info.count >= chunkedFrom)  // delta_rule_chunked_kernel takes this query
     return;
-  __shared__ float qs[kHeadDim], ks[kHeadDim], red[12], partialPred[8][kHeadDim], partialQ[8][kHeadDim], delta[kHeadDim], scalars[4];
+  __shared__ float qs[kHeadDim], ks[kHeadDim], red[12], partialPred[8][kHeadDim], partialQ[8][kHeadDim], delta[kHeadDim], scalars[4], dots[8];
 
   float4 S[16];
   if (info.previous) {
@@ -121,10 +131,49 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(const float* q, const f
   for (uint32_t t = 0; t < info.count; ++t) {
     const size_t row = info.start + t;
     // L2-normalise q (scaled by 1/sqrt(128)) and k; q.k of the normalised vectors (delta_rule.metal:281-311).
-    float qv = 0.f, kv = 0.f;
+    float qv = 0.f, kv = 0.f, vv = 0.f;
+    if (FUSED) {
+      // beta / g: warps 0..3 share the dot product with wBeta, warps 4..7 the one with wAlpha (as gdn_prepare_kernel)
+      const float* weights = ((part >> 2) ? in.wAlpha : in.wBeta) + size_t(head) * 4096 + (part & 3) * 1024;
+      const float* src = in.x + row * 4096 + (part & 3) * 1024;
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 a = *reinterpret_cast<const float4*>(src + i * 128 + lane * 4), b = *reinterpret_cast<const float4*>(weights + i * 128 + lane * 4);
+        sum += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+      }
+      sum = warp_sum(sum);
+      if (lane == 0)
+        dots[part] = sum;
+    }
     if (tid < kHeadDim) {
-      qv = q[(row * kKeyHeads + keyHead) * kHeadDim + tid];
-      kv = k[(row * kKeyHeads + keyHead) * kHeadDim + tid];
+      if (FUSED) {
+        // causal conv + SiLU of this head's q, k and v channel `tid` (gdn_causal_conv_silu, fused_kernels.metal:202-232)
+        const int channels[3] = {keyHead * kHeadDim + tid, 2048 + keyHead * kHeadDim + tid, 4096 + head * kHeadDim + tid};
+        const float* previous = reinterpret_cast<const float*>(info.previous + in.convStateOffset);
+        float values[3];
+#pragma unroll
+        for (int which = 0; which < 3; ++which) {
+          const int c = channels[which];
+          float context[4], acc = 0.f;
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const int64_t position = int64_t(t) - 3 + r;
+            context[r] = position >= 0 ? in.mixed[(info.start + position) * kChannels + c] : info.previous ? previous[c * 4 + position + 4] : 0.f;
+            acc = fmaf(context[r], in.convWeight[c * 4 + r], acc);
+          }
+          values[which] = silu_f(acc);
+          if ((speculative || t + 1 == info.count) && (which == 2 || head < kKeyHeads)) {
+            float* state = reinterpret_cast<float*>(info.next + in.convStateOffset + (speculative ? uint64_t(t) * stateBytes : 0)) + c * 4;
+            *reinterpret_cast<float4*>(state) = make_float4(context[0], context[1], context[2], context[3]);
+          }
+        }
+        qv = values[0], kv = values[1], vv = values[2];
+      } else {
+        qv = q[(row * kKeyHeads + keyHead) * kHeadDim + tid];
+        kv = k[(row * kKeyHeads + keyHead) * kHeadDim + tid];
+        vv = v[(row * kValueHeads + head) * kHeadDim + tid];
+      }
       const float a = warp_sum(qv * qv), b = warp_sum(kv * kv), c = warp_sum(qv * kv);
       if (lane == 0) {
         red[part] = a;
@@ -140,8 +189,14 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(const float* q, const f
       ks[tid] = kv * kn;
       if (tid == 0) {
         scalars[0] = (red[8] + red[9] + red[10] + red[11]) * qn * kn;
-        scalars[1] = expf(g[row * kValueHeads + head]);
-        scalars[2] = beta[row * kValueHeads + head];
+        if (FUSED) {
+          const float dotBeta = (dots[0] + dots[1]) + (dots[2] + dots[3]), dotAlpha = (dots[4] + dots[5]) + (dots[6] + dots[7]);
+          scalars[1] = expf(in.A[head] * logf(1.0f + expf(dotAlpha + in.dt[head])));
+          scalars[2] = 1.0f / (1.0f + expf(-dotBeta));
+        } else {
+          scalars[1] = expf(g[row * kValueHeads + head]);
+          scalars[2] = beta[row * kValueHeads + head];
+        }
       }
     }
     __syncthreads();
@@ -166,7 +221,7 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(const float* q, const f
         p += partialPred[w][tid];
         s += partialQ[w][tid];
       }
-      const float d = (v[(row * kValueHeads + head) * kHeadDim + tid] - p) * scalars[2];
+      const float d = (vv - p) * scalars[2];
       delta[tid] = d;
       o = s + d * scalars[0];
       const float ss = warp_sum(o * o);
@@ -431,8 +486,19 @@ cudaError_t delta_rule_launch(const float* q, const float* k, const float* v, co
     launch_kernel(delta_rule_chunked_kernel, dim3(kValueHeads, unsigned(queryCount)), 256, sizeof(ChunkShared), stream, q, k, v, g, beta, z, normWeight,
                   queries, stateOffset, out, chunkedFrom);
   }
-  launch_kernel(delta_rule_kernel, dim3(kValueHeads, unsigned(queryCount)), 256, 0, stream, q, k, v, g, beta, z, normWeight, queries, stateOffset, stateBytes,
-                out, image, counters, chunkedFrom);
+  launch_kernel(delta_rule_kernel<false>, dim3(kValueHeads, unsigned(queryCount)), 256, 0, stream, q, k, v, g, beta, z, normWeight, queries, stateOffset,
+                stateBytes, out, image, counters, chunkedFrom, GdnInputs{});
+  return cudaGetLastError();
+}
+
+cudaError_t gdn_decode_launch(const float* x, const float* mixed, const float* wBeta, const float* wAlpha, const float* A, const float* dt,
+                              const float* convWeight, const float* z, const float* normWeight, const infdev_query* queries, int queryCount,
+                              uint64_t convStateOffset, uint64_t stateOffset, uint64_t stateBytes, float* out, uint8_t* image, int* counters,
+                              cudaStream_t stream) {
+  if (queryCount <= 0)
+    return cudaSuccess;
+  launch_kernel<2>(delta_rule_kernel<true>, dim3(kValueHeads, unsigned(queryCount)), 256, 0, stream, nullptr, nullptr, nullptr, nullptr, nullptr, z, normWeight,
+                   queries, stateOffset, stateBytes, out, image, counters, 0u, GdnInputs{x, wBeta, wAlpha, A, dt, mixed, convWeight, convStateOffset});
   return cudaGetLastError();
 }
 

@@ -639,6 +639,23 @@ int infdev_gdn_prepare(infdev_ctx* ctx, const float* x, const float* mixed, cons
                "gdn_prepare");
 }
 
+int infdev_gdn_decode(infdev_ctx* ctx, const float* x, const float* mixed, const float* wBeta, const float* wAlpha, const float* ssmA,
+                      const float* ssmDt, const float* convWeight, const float* z, const float* normWeight, const infdev_query* queries,
+                      int queryCount, uint64_t convStateOffset, uint64_t stateOffset, uint64_t stateBytes, float* out) {
+  Bind bind(ctx);
+  if (ctx->skip & 6) {
+    take_capture(ctx);
+    return INFDEV_OK;
+  }
+  if (convStateOffset % 16 || stateOffset % 16 || stateBytes % 16)
+    return fail(ctx, INFDEV_E_ARGUMENT, "gdn_decode: state offsets must be multiples of 16 bytes");
+  ctx->launches += 1;
+  return check(ctx,
+               infdev::gdn_decode_launch(x, mixed, wBeta, wAlpha, ssmA, ssmDt, convWeight, z, normWeight, queries, queryCount, convStateOffset, stateOffset,
+                                         stateBytes, out, take_capture(ctx), ctx->imageCounters, ctx->stream),
+               "gdn_decode");
+}
+
 static int delta_rule_common(infdev_ctx* ctx, const float* q, const float* k, const float* v, const float* g, const float* beta, const float* z,
                              const float* normWeight, const infdev_query* queries, int queryCount, uint64_t stateOffset, uint64_t stateBytes,
                              float* out, uint32_t chunkedFrom) {

@@ -21,6 +21,10 @@ cudaError_t gdn_prepare_launch(const float* x, const float* mixed, const float* 
 cudaError_t delta_rule_launch(const float* q, const float* k, const float* v, const float* g, const float* beta, const float* z,
                               const float* normWeight, const infdev_query* queries, int queryCount, uint64_t stateOffset, uint64_t stateBytes,
                               float* out, uint8_t* image, int* counters, uint32_t chunkedFrom, cudaStream_t stream);
+cudaError_t gdn_decode_launch(const float* x, const float* mixed, const float* wBeta, const float* wAlpha, const float* A, const float* dt,
+                              const float* convWeight, const float* z, const float* normWeight, const infdev_query* queries, int queryCount,
+                              uint64_t convStateOffset, uint64_t stateOffset, uint64_t stateBytes, float* out, uint8_t* image, int* counters,
+                              cudaStream_t stream);
 cudaError_t attention_prepare_launch(const float* qg, const float* rawK, const float* rawV, const float* qNorm, const float* kNorm, const float* rope,
                                      const infdev_query* queries, const int32_t* table, int tableStride, int blockTokens, int64_t rows, float* q,
                                      void* cacheK, void* cacheV, cudaStream_t stream);

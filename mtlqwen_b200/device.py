@@ -75,6 +75,7 @@ def library():
     "infdev_rms_norm_gather": (i32, (vp, f32p, f32p, vp, i32, i64, f32p)),
     "infdev_gdn_prepare": (i32, (vp, f32p, f32p, f32p, f32p, f32p, f32p, f32p, vp, i32, i64, u64, u64, f32p, f32p, f32p, f32p, f32p)),
     "infdev_delta_rule": (i32, (vp, f32p, f32p, f32p, f32p, f32p, f32p, f32p, vp, i32, u64, u64, f32p)),
+    "infdev_gdn_decode": (i32, (vp, f32p, f32p, f32p, f32p, f32p, f32p, f32p, f32p, f32p, vp, i32, u64, u64, u64, f32p)),
     "infdev_delta_rule_prefill": (i32, (vp, f32p, f32p, f32p, f32p, f32p, f32p, f32p, vp, i32, u64, u64, f32p)),
     "infdev_rope_table": (i32, (vp, i64, f32p)),
     "infdev_attention_prepare": (i32, (vp, f32p, f32p, f32p, f32p, f32p, f32p, vp, i32, i64, vp, i32, i32, f32p, vp, vp)),
@@ -238,6 +239,11 @@ class Device:
     call = self.lib.infdev_delta_rule_prefill if prefill else self.lib.infdev_delta_rule
     self.check(call(self.ctx, q.ptr, k.ptr, v.ptr, g.ptr, beta.ptr, z.ptr if z is not None else None,
                                           norm_w.ptr if norm_w is not None else None, queries.ptr, nq, state_offset, state_bytes, out.ptr))
+
+  def gdn_decode(self, x, mixed, w_beta, w_alpha, ssm_a, ssm_dt, conv_w, z, norm_w, queries, nq, conv_offset, state_offset, state_bytes, out):
+    """gdn_prepare + gated delta_rule in one launch (passes without prefill chunks)."""
+    self.check(self.lib.infdev_gdn_decode(self.ctx, x.ptr, mixed.ptr, w_beta.ptr, w_alpha.ptr, ssm_a.ptr, ssm_dt.ptr, conv_w.ptr, z.ptr, norm_w.ptr,
+                                          queries.ptr, nq, conv_offset, state_offset, state_bytes, out.ptr))
 
   def rope_table(self, positions):
     table = self.empty((positions, 32, 2))

@@ -22,7 +22,7 @@ def layer_weights(rng):
               conv=(0.5 * rng.standard_normal((8192, 4))).astype(np.float32), norm=(1 + 0.01 * rng.standard_normal(128)).astype(np.float32))
 
 
-def run_layer(dev, rng, lengths, fresh=(), speculative=(), prefill=False):
+def run_layer(dev, rng, lengths, fresh=(), speculative=(), prefill=False, fused=False, outputs=None):
   """One GDN layer over len(lengths) queries packed back to back. `fresh` queries start from no state,
   `speculative` ones write one candidate state row per token."""
   w = layer_weights(rng)
@@ -52,20 +52,27 @@ def run_layer(dev, rng, lengths, fresh=(), speculative=(), prefill=False):
   bufs = {name: dev.array(value) for name, value in w.items()}
   q_out, k_out, v_out = dev.empty((rows, 16, 128)), dev.empty((rows, 16, 128)), dev.empty((rows, 32, 128))
   beta, g, out = dev.empty((rows, 32)), dev.empty((rows, 32)), dev.empty((rows, 32, 128))
-  dev.gdn_prepare(dev.array(x), dev.array(mixed), bufs["w_beta"], bufs["w_alpha"], bufs["ssm_a"], bufs["ssm_dt"], bufs["conv"], dq, nq, rows, 0,
-                  LAYER, q_out, k_out, v_out, beta, g)
+  if not fused:
+    dev.gdn_prepare(dev.array(x), dev.array(mixed), bufs["w_beta"], bufs["w_alpha"], bufs["ssm_a"], bufs["ssm_dt"], bufs["conv"], dq, nq, rows, 0,
+                    LAYER, q_out, k_out, v_out, beta, g)
   # The kernel also writes the quantised image of its output when asked; it must equal the quantisation of `out`.
   image, want_image = dev.empty(dev.image_bytes(rows, 4096), np.uint8), dev.empty(dev.image_bytes(rows, 4096), np.uint8)
   capture = rows < 256 and not prefill  # the prefill variant writes no image
   if capture:
     dev.image_capture(image)
-  dev.delta_rule(q_out, k_out, v_out, g, beta, dev.array(z), bufs["norm"], dq, nq, D.CONV_STATE_BYTES, LAYER, out, prefill=prefill)
+  if fused:  # preparation and recurrence in one launch
+    dev.gdn_decode(dev.array(x), dev.array(mixed), bufs["w_beta"], bufs["w_alpha"], bufs["ssm_a"], bufs["ssm_dt"], bufs["conv"], dev.array(z),
+                   bufs["norm"], dq, nq, 0, D.CONV_STATE_BYTES, LAYER, out)
+  else:
+    dev.delta_rule(q_out, k_out, v_out, g, beta, dev.array(z), bufs["norm"], dq, nq, D.CONV_STATE_BYTES, LAYER, out, prefill=prefill)
   dev.quantize(out, rows, 4096, want_image)
   dev.commit()
   if capture:
     for a, b in zip(images.decode(image.download(), rows, 4096), images.decode(want_image.download(), rows, 4096)):
       assert a.tobytes() == b.tobytes()
   got_out, got_next, got_cand = out.download(), next_.download(), candidates.download()
+  if outputs is not None:
+    outputs.extend([got_out, got_next, got_cand])
   worst, start, cand = 0.0, 0, 0
   for i, count in enumerate(lengths):
     rows_i = slice(start, start + count)
@@ -135,3 +142,14 @@ def test_prefill_variant_refuses_an_image(dev):
   with pytest.raises(RuntimeError, match="no image"):
     dev.delta_rule(dev.empty(1), dev.empty(1), dev.empty(1), dev.empty(1), dev.empty(1), None, None, dev.queries([D.Query()]), 1, 0, LAYER, dev.empty(1),
                    prefill=True)
+
+
+def test_gdn_fused_decode_is_identical_to_the_two_launches(dev):
+  """infdev_gdn_decode = infdev_gdn_prepare + infdev_delta_rule with the same arithmetic: outputs, recurrent states, conv
+  taps and speculative candidate records must agree bit for bit, and with the oracle within the tolerance."""
+  lengths, fresh, speculative = [1, 1, 5, 1, 3, 1, 1, 2], (1, ), (2, 4)
+  a, b = [], []
+  assert run_layer(dev, np.random.default_rng(7), lengths, fresh=fresh, speculative=speculative, outputs=a) < TOL
+  assert run_layer(dev, np.random.default_rng(7), lengths, fresh=fresh, speculative=speculative, fused=True, outputs=b) < TOL
+  for x, y in zip(a, b):
+    assert x.tobytes() == y.tobytes()
