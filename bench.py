@@ -63,7 +63,7 @@ class ClockSampler:
 
   def start(self):
     try:
-      self.process = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+      self.process = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
                                       stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
       threading.Thread(target=lambda: self.lines.extend(self.process.stdout), daemon=True).start()
     except OSError:
@@ -74,9 +74,9 @@ class ClockSampler:
       return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
     time.sleep(0.25)
     self.process.terminate()
-    # nvidia-smi emits one line per 100 ms from `started`; keep those that fall inside the timed region
+    # nvidia-smi emits one line per 200 ms from `started`; keep those that fall inside the timed region
     rows = [[field.strip() for field in line.split(",")] for line in self.lines if line.count(",") >= 7]
-    inside = [row for i, row in enumerate(rows) if busy_from - 0.15 <= started + 0.1 * i <= busy_to + 0.15] or rows
+    inside = [row for i, row in enumerate(rows) if busy_from - 0.25 <= started + 0.2 * i <= busy_to + 0.25] or rows
     clocks = [float(row[1]) for row in inside if row[1].replace(".", "").isdigit()]
     reasons = set()
     for row in inside:
