@@ -93,8 +93,8 @@ __device__ __forceinline__ void copy_async16(void* dst, const void* src, uint32_
 
 // grid (maxSplits, 4 kv heads, rows), 128 threads. The 16-token K and V tiles of the piece are copied into a
 // double buffer in shared memory with cp.async one tile ahead of the arithmetic, so the walk over the piece is not a
-// chain of load latencies. Warp w scores tokens 4w..4w+3 of a tile for the four query heads of the group, then
-// accumulates the values for query head w.
+// chain of load latencies. Warp w scores tokens 4w..4w+3 of a tile for the four query heads of the group on the CUDA
+// cores, then accumulates the weighted values of dims 64w .. 64w+63 for all four heads on the tensor cores.
 __global__ void __launch_bounds__(128, 4) attention_scan_kernel(const float* q, const __half* cacheK, const __half* cacheV,
                                                                 const infdev_query* queries, const int32_t* table, int tableStride, int blockTokens,
                                                                 uint32_t maxSplits, float* partials) {
@@ -109,7 +109,8 @@ __global__ void __launch_bounds__(128, 4) attention_scan_kernel(const float* q, 
   if (split >= count)
     return;
   __shared__ float scores[kGroup][kTile];
-  __shared__ __align__(16) __half tiles[2][2][kTile][kDim];  // [buffer][K, V][token][dim]
+  // [buffer][K, V][token][dim]; rows padded by 16 bytes so that the eight token rows one ldmatrix phase reads hit different banks
+  __shared__ __align__(16) __half tiles[2][2][kTile][kDim + 8];
   const int32_t* slotTable = table + size_t(info.slot) * tableStride;
   auto fetch = [&](uint32_t tile, int buffer) {
     const size_t block = slotTable[tile / blockTokens];
@@ -133,7 +134,16 @@ __global__ void __launch_bounds__(128, 4) attention_scan_kernel(const float* q, 
     const float4 a = src[0], b = src[1];
     qv[h][0] = a.x, qv[h][1] = a.y, qv[h][2] = a.z, qv[h][3] = a.w, qv[h][4] = b.x, qv[h][5] = b.y, qv[h][6] = b.z, qv[h][7] = b.w;
   }
-  float runningMax = -1.0e30f, runningNorm = 0.f, numerator[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  // Value accumulation on the tensor cores (m16n8k16, fp16 operands, fp32 accumulate): warp w owns value dims 64w .. 64w+63
+  // in four 16-dim chunks; A = V^T of the tile (dims x tokens, read transposed by ldmatrix), B = the tile's softmax weights
+  // (tokens x 8 columns: columns 0..3 the fp16 high halves for the four heads, columns 4..7 the low halves, so the result is
+  // accurate to fp32 rounding of the weights). Lane (g, t) builds column g of B, i.e. head g % 4, and tracks that head's
+  // running maximum and, over its four tokens of every tile, its share of the norm.
+  const int g = lane >> 2, t = lane & 3, myHead = g & 3;
+  float runningMax = -1.0e30f, runningNorm = 0.f, acc[4][4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+    acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f;
   int buffer = 0;
   for (uint32_t tile = begin; tile < end; tile += kTile, buffer ^= 1) {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -179,38 +189,58 @@ __global__ void __launch_bounds__(128, 4) attention_scan_kernel(const float* q, 
       scores[h][warp * 4 + i] = token < end ? s[0] * (1.0f / 16.0f) : -INFINITY;
     }
     __syncthreads();
-    // online softmax for head `warp`; lane owns dims lane*8..+7. A token past the end has score -inf: weight 0
-    // against a zero-filled value row.
+    // online softmax. A token past the end has score -inf: weight 0 against a zero-filled value row.
     float tileMax = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < kTile; ++i)
-      tileMax = fmaxf(tileMax, scores[warp][i]);
-    const float nextMax = fmaxf(runningMax, tileMax), rescale = expf(runningMax - nextMax);
-    runningNorm *= rescale;
-#pragma unroll
-    for (int d = 0; d < 8; ++d)
-      numerator[d] *= rescale;
-#pragma unroll
-    for (int i = 0; i < kTile; ++i) {
-      const float weight = expf(scores[warp][i] - nextMax);
-      runningNorm += weight;
-      const uint4 raw = *reinterpret_cast<const uint4*>(&tiles[buffer][1][i][lane * 8]);
-      const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
-#pragma unroll
-      for (int d = 0; d < 4; ++d) {
-        const float2 f = __half22float2(h2[d]);
-        numerator[2 * d] = fmaf(weight, f.x, numerator[2 * d]);
-        numerator[2 * d + 1] = fmaf(weight, f.y, numerator[2 * d + 1]);
-      }
+    for (int i = 0; i < kTile; i += 4) {
+      const float4 four = *reinterpret_cast<const float4*>(&scores[myHead][i]);
+      tileMax = fmaxf(fmaxf(tileMax, fmaxf(four.x, four.y)), fmaxf(four.z, four.w));
     }
+    const float nextMax = fmaxf(runningMax, tileMax), rescale = expf(runningMax - nextMax);
     runningMax = nextMax;
+    // weights of this lane's four tokens (the summation slots 2t, 2t+1, 2t+8, 2t+9 of the B fragment)
+    const float w0 = expf(scores[myHead][2 * t] - nextMax), w1 = expf(scores[myHead][2 * t + 1] - nextMax);
+    const float w2 = expf(scores[myHead][2 * t + 8] - nextMax), w3 = expf(scores[myHead][2 * t + 9] - nextMax);
+    runningNorm = runningNorm * rescale + ((w0 + w1) + (w2 + w3));
+    __half2 b0 = __floats2half2_rn(w0, w1), b1 = __floats2half2_rn(w2, w3);
+    if (g >= 4) {  // the low halves
+      const float2 f0 = __half22float2(b0), f1 = __half22float2(b1);
+      b0 = __floats2half2_rn(w0 - f0.x, w1 - f0.y), b1 = __floats2half2_rn(w2 - f1.x, w3 - f1.y);
+    }
+    // this lane's accumulators are columns 2t and 2t+1: heads (2t) % 4 and (2t+1) % 4
+    const float r0 = __shfl_sync(0xffffffffu, rescale, ((2 * t) & 3) * 4), r1 = __shfl_sync(0xffffffffu, rescale, ((2 * t + 1) & 3) * 4);
+    const int matrix = lane >> 3, tokenRow = (lane & 7) + 8 * (matrix >> 1), dimOffset = 8 * (matrix & 1);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t a[4];
+      const uint32_t address = smem_u32(&tiles[buffer][1][tokenRow][64 * warp + 16 * c + dimOffset]);
+      asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(address));
+      acc[c][0] *= r0, acc[c][1] *= r1, acc[c][2] *= r0, acc[c][3] *= r1;
+      mma_16816(acc[c], a, *reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1));
+    }
   }
-  float* dst = partials + ((size_t(row) * kQHeads + kvHead * kGroup + warp) * maxSplits + split) * kPartialStride;
-  *reinterpret_cast<float4*>(dst + lane * 8) = make_float4(numerator[0], numerator[1], numerator[2], numerator[3]);
-  *reinterpret_cast<float4*>(dst + lane * 8 + 4) = make_float4(numerator[4], numerator[5], numerator[6], numerator[7]);
-  if (lane == 0) {
-    dst[kDim] = runningMax;
-    dst[kDim + 1] = runningNorm;
+  // columns 4..7 (lanes t = 2, 3) hold the low-half products of heads 0..3: add them to columns 0..3 (lanes t = 0, 1)
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      acc[c][i] += __shfl_xor_sync(0xffffffffu, acc[c][i], 2);
+  runningNorm += __shfl_xor_sync(0xffffffffu, runningNorm, 1);
+  runningNorm += __shfl_xor_sync(0xffffffffu, runningNorm, 2);
+  float* base = partials + ((size_t(row) * kQHeads + kvHead * kGroup) * maxSplits + split) * kPartialStride;
+  const size_t headStride = size_t(maxSplits) * kPartialStride;
+  if (t < 2) {
+    float *first = base + (2 * t) * headStride, *second = base + (2 * t + 1) * headStride;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int dim = 64 * warp + 16 * c + g;
+      first[dim] = acc[c][0], second[dim] = acc[c][1];
+      first[dim + 8] = acc[c][2], second[dim + 8] = acc[c][3];
+    }
+  }
+  if (warp == 0 && g < 4 && t == 0) {
+    base[g * headStride + kDim] = runningMax;
+    base[g * headStride + kDim + 1] = runningNorm;
   }
 }
 
