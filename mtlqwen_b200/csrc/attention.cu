@@ -93,8 +93,9 @@ __device__ __forceinline__ void copy_async16(void* dst, const void* src, uint32_
 
 // grid (maxSplits, 4 kv heads, rows), 128 threads. The 16-token K and V tiles of the piece are copied into a
 // double buffer in shared memory with cp.async one tile ahead of the arithmetic, so the walk over the piece is not a
-// chain of load latencies. Warp w scores tokens 4w..4w+3 of a tile for the four query heads of the group on the CUDA
-// cores, then accumulates the weighted values of dims 64w .. 64w+63 for all four heads on the tensor cores.
+// chain of load latencies. Both contractions run on the tensor cores as m16n8k16 with fp16 operands split hi + lo where
+// they are not fp16 already: warp 0 scores the tile's 16 tokens for the four query heads of the group, then warp w
+// accumulates the weighted values of dims 64w .. 64w+63 for all four heads.
 __global__ void __launch_bounds__(128, 4) attention_scan_kernel(const float* q, const __half* cacheK, const __half* cacheV,
                                                                 const infdev_query* queries, const int32_t* table, int tableStride, int blockTokens,
                                                                 uint32_t maxSplits, float* partials) {
@@ -126,20 +127,29 @@ __global__ void __launch_bounds__(128, 4) attention_scan_kernel(const float* q, 
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   fetch(begin, 0);
-  // q of the four heads, the 8 dims of this lane: dims lane*8 .. lane*8+7
-  float qv[kGroup][8];
+  // Scores on the tensor cores too (warp 0): A = the K tile (16 tokens x 256 dims, 16 dims per MMA), B = q of the four
+  // heads as 8 columns, columns 0..3 the fp16 high halves, columns 4..7 the low halves (q - hi). Lane (g, t) keeps column
+  // g of B for all 16 dim steps: 32 registers.
+  const int g = lane >> 2, t = lane & 3, myHead = g & 3;
+  uint32_t qFragment[16][2];
+  if (warp == 0) {
+    const float* src = q + (size_t(row) * kQHeads + kvHead * kGroup + myHead) * kDim;
 #pragma unroll
-  for (int h = 0; h < kGroup; ++h) {
-    const float4* src = reinterpret_cast<const float4*>(q + (size_t(row) * kQHeads + kvHead * kGroup + h) * kDim + lane * 8);
-    const float4 a = src[0], b = src[1];
-    qv[h][0] = a.x, qv[h][1] = a.y, qv[h][2] = a.z, qv[h][3] = a.w, qv[h][4] = b.x, qv[h][5] = b.y, qv[h][6] = b.z, qv[h][7] = b.w;
+    for (int step = 0; step < 16; ++step) {
+      const float2 a = *reinterpret_cast<const float2*>(src + 16 * step + 2 * t), b = *reinterpret_cast<const float2*>(src + 16 * step + 2 * t + 8);
+      __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(b.x, b.y);
+      if (g >= 4) {
+        const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+        h0 = __floats2half2_rn(a.x - f0.x, a.y - f0.y), h1 = __floats2half2_rn(b.x - f1.x, b.y - f1.y);
+      }
+      qFragment[step][0] = *reinterpret_cast<const uint32_t*>(&h0), qFragment[step][1] = *reinterpret_cast<const uint32_t*>(&h1);
+    }
   }
   // Value accumulation on the tensor cores (m16n8k16, fp16 operands, fp32 accumulate): warp w owns value dims 64w .. 64w+63
   // in four 16-dim chunks; A = V^T of the tile (dims x tokens, read transposed by ldmatrix), B = the tile's softmax weights
   // (tokens x 8 columns: columns 0..3 the fp16 high halves for the four heads, columns 4..7 the low halves, so the result is
   // accurate to fp32 rounding of the weights). Lane (g, t) builds column g of B, i.e. head g % 4, and tracks that head's
   // running maximum and, over its four tokens of every tile, its share of the norm.
-  const int g = lane >> 2, t = lane & 3, myHead = g & 3;
   float runningMax = -1.0e30f, runningNorm = 0.f, acc[4][4];
 #pragma unroll
   for (int c = 0; c < 4; ++c)
@@ -150,43 +160,29 @@ __global__ void __launch_bounds__(128, 4) attention_scan_kernel(const float* q, 
     __syncthreads();  // this tile is complete for every thread, and every thread is done with the previous tile and its scores
     if (tile + kTile < end)
       fetch(tile + kTile, buffer ^ 1);  // lands while this tile is worked on
-    // partial scores of 4 tokens x 4 heads over this lane's 8 dims
-    float s[16];
+    if (warp == 0) {
+      // scores of the tile's 16 tokens for the four heads: two accumulator chains over the 16 dim steps
+      float score[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      const int matrix = lane >> 3, tokenRow = (lane & 7) + 8 * (matrix & 1), dimOffset = 8 * (matrix >> 1);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(&tiles[buffer][0][warp * 4 + i][lane * 8]);
-      const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
-      float kf[8];
-#pragma unroll
-      for (int d = 0; d < 4; ++d) {
-        const float2 f = __half22float2(h2[d]);
-        kf[2 * d] = f.x, kf[2 * d + 1] = f.y;
+      for (int step = 0; step < 16; ++step) {
+        uint32_t a[4];
+        const uint32_t address = smem_u32(&tiles[buffer][0][tokenRow][16 * step + dimOffset]);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(address));
+        mma_16816(score[step & 1], a, qFragment[step][0], qFragment[step][1]);
       }
+      // columns 4..7 (lanes t = 2, 3) carry the low-half products of heads 0..3
 #pragma unroll
-      for (int h = 0; h < kGroup; ++h) {
-        float acc = 0.f;
-#pragma unroll
-        for (int d = 0; d < 8; ++d)
-          acc = fmaf(qv[h][d], kf[d], acc);
-        s[i * 4 + h] = acc;
+      for (int i = 0; i < 4; ++i) {
+        score[0][i] += score[1][i];
+        score[0][i] += __shfl_xor_sync(0xffffffffu, score[0][i], 2);
       }
-    }
-    // Sum the 16 values over the 32 lanes with 16 shuffles: every exchange halves the values a lane still carries;
-    // lane l ends with the total of value l / 2.
-#pragma unroll
-    for (int width = 8, step = 16; width >= 1; width >>= 1, step >>= 1) {
-      const bool upper = lane & step;
-#pragma unroll
-      for (int v = 0; v < width; ++v) {
-        const float keep = upper ? s[v + width] : s[v], send = upper ? s[v] : s[v + width];
-        s[v] = keep + __shfl_xor_sync(0xffffffffu, send, step);
+      if (t < 2) {
+        scores[2 * t][g] = tile + g < end ? score[0][0] * (1.0f / 16.0f) : -INFINITY;
+        scores[2 * t + 1][g] = tile + g < end ? score[0][1] * (1.0f / 16.0f) : -INFINITY;
+        scores[2 * t][g + 8] = tile + g + 8 < end ? score[0][2] * (1.0f / 16.0f) : -INFINITY;
+        scores[2 * t + 1][g + 8] = tile + g + 8 < end ? score[0][3] * (1.0f / 16.0f) : -INFINITY;
       }
-    }
-    s[0] += __shfl_xor_sync(0xffffffffu, s[0], 1);
-    if (!(lane & 1)) {
-      const int v = lane >> 1, i = v >> 2, h = v & 3;
-      const uint32_t token = tile + warp * 4 + i;
-      scores[h][warp * 4 + i] = token < end ? s[0] * (1.0f / 16.0f) : -INFINITY;
     }
     __syncthreads();
     // online softmax. A token past the end has score -inf: weight 0 against a zero-filled value row.
