@@ -24,7 +24,12 @@ namespace {
 constexpr int kQHeads = 16, kKvHeads = 4, kDim = 256, kGroup = kQHeads / kKvHeads, kTile = 16;
 constexpr int kPartialStride = kDim + 4;  // 260 floats keeps every record 16-byte aligned for the float4 stores
 
-__device__ __forceinline__ const infdev_query& query_of_row(const infdev_query* queries, uint32_t row) {
+// Row -> query. In a decode pass every query is one row, so query `row` is the answer; probing it first saves a chain
+// of dependent loads at the head of every CTA (queryCount bounds the probe).
+__device__ __forceinline__ const infdev_query& query_of_row(const infdev_query* queries, int queryCount, uint32_t row) {
+  const infdev_query& guess = queries[min(row, uint32_t(queryCount - 1))];
+  if (row >= guess.start && row < guess.start + guess.count)
+    return guess;
   while (row >= queries->start + queries->count)
     ++queries;
   return *queries;
@@ -42,7 +47,7 @@ __device__ __forceinline__ void split_range(uint32_t attended, uint32_t maxSplit
 
 // grid (rows * 20), 256 threads: heads 0..15 are queries, 16..19 keys (which also store the value head).
 __global__ void __launch_bounds__(256) attention_prepare_kernel(const float* qg, const float* rawK, const float* rawV, const float* qNorm,
-                                                                const float* kNorm, const float* rope, const infdev_query* queries,
+                                                                const float* kNorm, const float* rope, const infdev_query* queries, int queryCount,
                                                                 const int32_t* table, int tableStride, int blockTokens, float* q, __half* cacheK,
                                                                 __half* cacheV) {
   pdl_launch_dependents();
@@ -67,7 +72,7 @@ __global__ void __launch_bounds__(256) attention_prepare_kernel(const float* qg,
     scale = rsqrtf(total / float(kDim) + 1.0e-6f);
   }
   __syncthreads();
-  const infdev_query& info = query_of_row(queries, row);
+  const infdev_query& info = query_of_row(queries, queryCount, row);
   const uint32_t position = info.position + row - info.start;
   float result = value * scale * weight[lane];
   if (lane < 64) {
@@ -97,13 +102,13 @@ __device__ __forceinline__ void copy_async16(void* dst, const void* src, uint32_
 // they are not fp16 already: warp 0 scores the tile's 16 tokens for the four query heads of the group, then warp w
 // accumulates the weighted values of dims 64w .. 64w+63 for all four heads.
 __global__ void __launch_bounds__(128, 4) attention_scan_kernel(const float* q, const __half* cacheK, const __half* cacheV,
-                                                                const infdev_query* queries, const int32_t* table, int tableStride, int blockTokens,
-                                                                uint32_t maxSplits, float* partials) {
+                                                                const infdev_query* queries, int queryCount, const int32_t* table, int tableStride,
+                                                                int blockTokens, uint32_t maxSplits, float* partials) {
   pdl_launch_dependents();
   pdl_wait();
   const uint32_t split = blockIdx.x, kvHead = blockIdx.y, row = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const infdev_query& info = query_of_row(queries, row);
+  const infdev_query& info = query_of_row(queries, queryCount, row);
   const uint32_t attended = info.position + (row - info.start) + 1;
   uint32_t begin, end, count;
   split_range(attended, maxSplits, split, begin, end, count);
@@ -242,12 +247,12 @@ __global__ void __launch_bounds__(128, 4) attention_scan_kernel(const float* q, 
 
 // grid (rows * 16), 256 threads: merge the splits, normalise, multiply by sigmoid(gate).
 // `image`, when not null, also receives the activation image of the output rows: a head is one 256-value block.
-__global__ void __launch_bounds__(256) attention_reduce_kernel(const float* partials, const float* qg, const infdev_query* queries,
+__global__ void __launch_bounds__(256) attention_reduce_kernel(const float* partials, const float* qg, const infdev_query* queries, int queryCount,
                                                                uint32_t maxSplits, float* out, uint8_t* image) {
   pdl_launch_dependents();
   pdl_wait();
   const uint32_t headRow = blockIdx.x, row = headRow / kQHeads, dim = threadIdx.x;
-  const infdev_query& info = query_of_row(queries, row);
+  const infdev_query& info = query_of_row(queries, queryCount, row);
   const uint32_t attended = info.position + (row - info.start) + 1;
   uint32_t begin, end, count;
   split_range(attended, maxSplits, 0, begin, end, count);
@@ -279,24 +284,24 @@ __global__ void __launch_bounds__(256) attention_reduce_kernel(const float* part
 }  // namespace
 
 cudaError_t attention_prepare_launch(const float* qg, const float* rawK, const float* rawV, const float* qNorm, const float* kNorm, const float* rope,
-                                     const infdev_query* queries, const int32_t* table, int tableStride, int blockTokens, int64_t rows, float* q,
+                                     const infdev_query* queries, int queryCount, const int32_t* table, int tableStride, int blockTokens, int64_t rows, float* q,
                                      void* cacheK, void* cacheV, cudaStream_t stream) {
   if (rows <= 0)
     return cudaSuccess;
-  launch_kernel<2>(attention_prepare_kernel, unsigned(rows * 20), 256, 0, stream, qg, rawK, rawV, qNorm, kNorm, rope, queries, table, tableStride, blockTokens, q,
+  launch_kernel<2>(attention_prepare_kernel, unsigned(rows * 20), 256, 0, stream, qg, rawK, rawV, qNorm, kNorm, rope, queries, queryCount, table, tableStride, blockTokens, q,
                                                                      static_cast<__half*>(cacheK), static_cast<__half*>(cacheV));
   return cudaGetLastError();
 }
 
 cudaError_t attention_launch(const float* q, const float* qg, const void* cacheK, const void* cacheV, const infdev_query* queries,
-                             const int32_t* table, int tableStride, int blockTokens, int64_t rows, uint32_t maxSplits, float* partials, float* out,
+                             int queryCount, const int32_t* table, int tableStride, int blockTokens, int64_t rows, uint32_t maxSplits, float* partials, float* out,
                              uint8_t* image, cudaStream_t stream) {
   if (rows <= 0)
     return cudaSuccess;
   launch_kernel(attention_scan_kernel, dim3(maxSplits, kKvHeads, unsigned(rows)), 128, 0, stream, q, static_cast<const __half*>(cacheK),
-                                                                                       static_cast<const __half*>(cacheV), queries, table,
+                                                                                       static_cast<const __half*>(cacheV), queries, queryCount, table,
                                                                                        tableStride, blockTokens, maxSplits, partials);
-  launch_kernel(attention_reduce_kernel, unsigned(rows * kQHeads), 256, 0, stream, partials, qg, queries, maxSplits, out, image);
+  launch_kernel(attention_reduce_kernel, unsigned(rows * kQHeads), 256, 0, stream, partials, qg, queries, queryCount, maxSplits, out, image);
   return cudaGetLastError();
 }
 
@@ -310,7 +315,7 @@ constexpr int kStaticRows = 8, kStaticSplits = 16;
 static __device__ __align__(256) float staticPartials[size_t(kStaticRows) * kQHeads * kStaticSplits * kPartialStride];
 
 cudaError_t attention_static_launch(const float* q, const float* qg, const void* cacheK, const void* cacheV, const infdev_query* queries,
-                                    const int32_t* table, int tableStride, int blockTokens, int64_t rows, int device, float* out,
+                                    int queryCount, const int32_t* table, int tableStride, int blockTokens, int64_t rows, int device, float* out,
                                     cudaStream_t stream) {
   // In host code `staticPartials` is only a handle; the kernels need the device address, looked up once per
   // device (with that device current, which the caller guarantees) and remembered.
@@ -335,9 +340,9 @@ cudaError_t attention_static_launch(const float* q, const float* qg, const void*
   // Nothing has to start at zero: the reduction reads exactly the (row, head, split) records that the scan of the
   // same call wrote; whatever an earlier call left in the array is never read.
   launch_kernel(attention_scan_kernel, dim3(kStaticSplits, kKvHeads, unsigned(rows)), 128, 0, stream, q, static_cast<const __half*>(cacheK),
-                                                                                          static_cast<const __half*>(cacheV), queries, table,
+                                                                                          static_cast<const __half*>(cacheV), queries, queryCount, table,
                                                                                           tableStride, blockTokens, kStaticSplits, partials);
-  launch_kernel(attention_reduce_kernel, unsigned(rows * kQHeads), 256, 0, stream, partials, qg, queries, kStaticSplits, out, nullptr);
+  launch_kernel(attention_reduce_kernel, unsigned(rows * kQHeads), 256, 0, stream, partials, qg, queries, queryCount, kStaticSplits, out, nullptr);
   return cudaGetLastError();
 }
 

@@ -711,12 +711,13 @@ int infdev_attention_prepare(infdev_ctx* ctx, const float* qg, const float* k, c
     take_capture(ctx);
     return INFDEV_OK;
   }
-  (void)queryCount;
+  if (rows > 0 && queryCount < 1)
+    return fail(ctx, INFDEV_E_ARGUMENT, "attention: rows without queries");
   if (blockTokens <= 0 || blockTokens % 16)
     return fail(ctx, INFDEV_E_ARGUMENT, "attention: blockTokens must be a positive multiple of 16");
   ctx->launches += 1;
   return check(ctx,
-               infdev::attention_prepare_launch(qg, k, v, qNorm, kNorm, rope, queries, table, tableStride, blockTokens, rows, q, cacheK, cacheV,
+               infdev::attention_prepare_launch(qg, k, v, qNorm, kNorm, rope, queries, queryCount, table, tableStride, blockTokens, rows, q, cacheK, cacheV,
                                                 ctx->stream),
                "attention_prepare");
 }
@@ -731,12 +732,13 @@ int infdev_attention(infdev_ctx* ctx, const float* q, const float* qg, const voi
     take_capture(ctx);
     return INFDEV_OK;
   }
-  (void)queryCount;
+  if (rows > 0 && queryCount < 1)
+    return fail(ctx, INFDEV_E_ARGUMENT, "attention: rows without queries");
   if (blockTokens <= 0 || blockTokens % 16 || maxSplits < 1 || maxSplits > 64)
     return fail(ctx, INFDEV_E_ARGUMENT, "attention: blockTokens must be a multiple of 16 and maxSplits in 1..64");
   ctx->launches += 2;
   return check(ctx,
-               infdev::attention_launch(q, qg, cacheK, cacheV, queries, table, tableStride, blockTokens, rows, maxSplits, partials, out,
+               infdev::attention_launch(q, qg, cacheK, cacheV, queries, queryCount, table, tableStride, blockTokens, rows, maxSplits, partials, out,
                                         take_capture(ctx), ctx->stream),
                "attention");
 }
@@ -753,14 +755,15 @@ int infdev_mtp_fuse(infdev_ctx* ctx, const float* embedding, const float* hidden
 int infdev_attention_static(infdev_ctx* ctx, const float* q, const float* qg, const void* cacheK, const void* cacheV, const infdev_query* queries,
                             int queryCount, int64_t rows, const int32_t* table, int32_t tableStride, int32_t blockTokens, float* out) {
   Bind bind(ctx);  // the symbol lookup of the first call on a device needs that device current
-  (void)queryCount;
+  if (rows > 0 && queryCount < 1)
+    return fail(ctx, INFDEV_E_ARGUMENT, "attention: rows without queries");
   if (blockTokens <= 0 || blockTokens % 16)
     return fail(ctx, INFDEV_E_ARGUMENT, "attention_static: blockTokens must be a positive multiple of 16");
   if (rows > infdev::attention_static_max_rows())
     return fail(ctx, INFDEV_E_ARGUMENT, "attention_static: at most " + std::to_string(infdev::attention_static_max_rows()) +
                                             " packed rows fit the built-in scratch; use infdev_attention with a caller-provided buffer");
   ctx->launches += 2;
-  return check(ctx, infdev::attention_static_launch(q, qg, cacheK, cacheV, queries, table, tableStride, blockTokens, rows, ctx->device, out, ctx->stream),
+  return check(ctx, infdev::attention_static_launch(q, qg, cacheK, cacheV, queries, queryCount, table, tableStride, blockTokens, rows, ctx->device, out, ctx->stream),
                "attention_static");
 }
 

@@ -26,13 +26,13 @@ cudaError_t gdn_decode_launch(const float* x, const float* mixed, const float* w
                               uint64_t convStateOffset, uint64_t stateOffset, uint64_t stateBytes, float* out, uint8_t* image, int* counters,
                               cudaStream_t stream);
 cudaError_t attention_prepare_launch(const float* qg, const float* rawK, const float* rawV, const float* qNorm, const float* kNorm, const float* rope,
-                                     const infdev_query* queries, const int32_t* table, int tableStride, int blockTokens, int64_t rows, float* q,
+                                     const infdev_query* queries, int queryCount, const int32_t* table, int tableStride, int blockTokens, int64_t rows, float* q,
                                      void* cacheK, void* cacheV, cudaStream_t stream);
 cudaError_t attention_launch(const float* q, const float* qg, const void* cacheK, const void* cacheV, const infdev_query* queries,
-                             const int32_t* table, int tableStride, int blockTokens, int64_t rows, uint32_t maxSplits, float* partials, float* out,
+                             int queryCount, const int32_t* table, int tableStride, int blockTokens, int64_t rows, uint32_t maxSplits, float* partials, float* out,
                              uint8_t* image, cudaStream_t stream);
 cudaError_t attention_static_launch(const float* q, const float* qg, const void* cacheK, const void* cacheV, const infdev_query* queries,
-                                    const int32_t* table, int tableStride, int blockTokens, int64_t rows, int device, float* out,
+                                    int queryCount, const int32_t* table, int tableStride, int blockTokens, int64_t rows, int device, float* out,
                                     cudaStream_t stream);
 int attention_static_max_rows();
 cudaError_t sample_launch(const float* logits, int vocab, infdev_query* queries, int64_t count, uint32_t mode, int32_t* tokens,
