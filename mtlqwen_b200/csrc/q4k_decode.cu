@@ -9,9 +9,13 @@
 // scale and the -dmin * m term (one fp16 MMA against the sub-block sums) are applied once per super-block.
 // The only approximation is the 16-bit activation grid: absolute error at most 1.6e-5 of the block maximum.
 //
-// One persistent CTA per SM: 16 consumer warps, 4 finisher warps and 1 producer warp. The producer streams 16-row x 8-super-block
-// weight slabs with one tiled TMA copy each into a shared-memory ring, and bulk-copies the activation image of the
-// current K chunk; every wait on an mbarrier is bounded and ends in an abort flag plus a device status code.
+// One persistent CTA per SM: 16 consumer warps, 1 finisher warp and 1 producer warp. The producer streams 16-row x
+// 8-super-block weight slabs with one tiled TMA copy each into a shared-memory ring. A consumer warp works on the
+// same super-block of every tile (warp w of a half takes super-block w of the half's slab), so it keeps the activation
+// fragments of that super-block in registers for a whole K chunk, loaded straight from the image in global memory:
+// shared memory is read for the weights only, which is what bounds the rate of this kernel (the activation fragments
+// of a unit are 4 KB against 2.3 KB of weights). Every wait on an mbarrier is bounded and ends in an abort flag plus a
+// device status code.
 #include "act_image.cuh"
 #include "kernels.h"
 
@@ -20,30 +24,27 @@ namespace {
 
 constexpr int kConsumerWarps = 16;  // two halves of 8; consecutive ring stages alternate between the halves
 constexpr int kStageWarps = 8;       // one warp per super-block of a stage
-constexpr int kFinisherWarps = 4;    // sum the consumers' partial results of a tile and store it, off the consumers' path
-constexpr int kProducerWarp = kConsumerWarps + kFinisherWarps;
+constexpr int kFinisherWarp = kConsumerWarps;  // sums the consumers' partial results of a tile and stores it
+constexpr int kProducerWarp = kConsumerWarps + 1;
 constexpr int kThreads = (kProducerWarp + 1) * kWarp;
-constexpr int kHandoffThreads = (kConsumerWarps + kFinisherWarps) * kWarp;  // parties of the named barriers between the two roles
-constexpr int kChunkBlocks = 16;  // super-blocks of K whose image is resident at a time
+constexpr int kChunkBlocks = 16;  // super-blocks of K per pass over the tiles: two slabs, one per half
 constexpr int kStageBlocks = kGemvStageBlocks;
 constexpr int kTileRows = kGemvTileRows;
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = 12;
 constexpr int kBlockBytes = 144;
 constexpr int kRowPitch = kStageBlocks * kBlockBytes + kDecodePadBytes;  // 1184
 constexpr int kStageBytes = kTileRows * kRowPitch;                       // 18,944
-constexpr int kImagePieceBlocks = 4;                                      // blocks per bulk copy of the image
+static_assert(kChunkBlocks == 2 * kStageBlocks, "a consumer warp's super-block within a chunk is fixed by its half");
 
 struct Control {
   uint64_t full[kMaxStages], empty[kMaxStages];
-  uint64_t imageFull, imageEmpty;
+  uint64_t partialReady[2], partialFree[2];  // per partial-sum buffer: consumers -> finisher, finisher -> consumers
   int abort;
 };
 constexpr int kControlBytes = 256;
-static_assert(sizeof(Control) <= kControlBytes, "control block overlaps the image");
+static_assert(sizeof(Control) <= kControlBytes, "control block overlaps the partial sums");
 
-template <int NMAT> constexpr size_t fixed_bytes() {
-  return kControlBytes + size_t(kChunkBlocks) * kImageBlockBytes + size_t(2) * NMAT * kConsumerWarps * 128 * 4;
-}
+template <int NMAT> constexpr size_t fixed_bytes() { return kControlBytes + size_t(2) * NMAT * kConsumerWarps * 128 * 4; }
 template <int NMAT> constexpr int stage_count() {
   int stages = int((size_t(227) * 1024 - fixed_bytes<NMAT>()) / kStageBytes);
   return stages > kMaxStages ? kMaxStages : stages;
@@ -67,14 +68,32 @@ __device__ __forceinline__ void imma_u8u8(int (&d)[4], const uint32_t (&a)[4], u
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
 }
 
-// One 16-row x 256-k unit. Lane (g = lane/4, t = lane%4) owns weight rows g and g+8 (shared-memory addresses pA, pB)
-// and, in each 32-byte quant chunk c, bytes 8t .. 8t+7: their low nibbles are values 8t .. 8t+7 of sub-block 2c,
-// their high nibbles the same values of sub-block 2c+1 (GGUF layout as read by dequant_tile,
-// quant_linear.metal:39-46). The four bytes of a word fill four consecutive summation slots of the MMA, which is
-// the order the image stores the activations in. `image` is the block's image offset by this lane's fragment
-// (row g, quarter t); `sums` and `scales` address the lane's entries of the other two tables.
-__device__ __forceinline__ void q4k_unit(const uint8_t* pA, const uint8_t* pB, int t, const uint8_t* image, const uint8_t* sums, const uint8_t* scales,
-                                         float (&total)[4]) {
+// What one lane keeps of the image of one super-block (act_image.cuh) while its warp walks the tiles: lane
+// (g = lane/4, t = lane%4) holds, per sub-block j, the B fragments of activation row g, quarter t: registers b0, b1 of
+// the high-byte MMA in x, y and of the low-byte MMA in z, w.
+struct Fragments {
+  uint4 quant[8];
+  uint2 sums;    // min-term fragment: fp16 pairs of S_j / 32, high halves in x, low halves in y
+  uint2 scales;  // fp32 bits of the activation scales of rows 2t and 2t+1
+};
+
+__device__ __forceinline__ Fragments load_fragments(const uint8_t* block, int lane) {
+  Fragments f;
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    f.quant[j] = *reinterpret_cast<const uint4*>(block + j * 512 + g * 64 + t * 16);
+  f.sums = *reinterpret_cast<const uint2*>(block + kImageSumOffset + lane * 8);
+  f.scales = *reinterpret_cast<const uint2*>(block + kImageScaleOffset + t * 8);
+  return f;
+}
+
+// One 16-row x 256-k unit. Lane (g, t) owns weight rows g and g+8 (shared-memory addresses pA, pB) and, in each
+// 32-byte quant chunk c, bytes 8t .. 8t+7: their low nibbles are values 8t .. 8t+7 of sub-block 2c, their high
+// nibbles the same values of sub-block 2c+1 (GGUF layout as read by dequant_tile, quant_linear.metal:39-46). The four
+// bytes of a word fill four consecutive summation slots of the MMA, which is the order the image stores the
+// activations in.
+__device__ __forceinline__ void q4k_unit(const uint8_t* pA, const uint8_t* pB, int t, const Fragments& f, float (&total)[4]) {
   const uint4 hA = lds128(pA), hB = lds128(pB);
   // 6-bit scales / mins of the 8 sub-blocks, four per word (scale_min_k4, quant_linear.metal:12-20).
   const uint32_t scA[2] = {hA.y & 0x3f3f3f3fu, (hA.w & 0x0f0f0f0fu) | ((hA.y >> 2) & 0x30303030u)};
@@ -96,7 +115,7 @@ __device__ __forceinline__ void q4k_unit(const uint8_t* pA, const uint8_t* pB, i
       } else {
         a[0] = (qA.x >> 4) & 0x0f0f0f0fu, a[1] = (qB.x >> 4) & 0x0f0f0f0fu, a[2] = (qA.y >> 4) & 0x0f0f0f0fu, a[3] = (qB.y >> 4) & 0x0f0f0f0fu;
       }
-      const uint4 b = lds128(image + j * 512);
+      const uint4 b = f.quant[j];
       int high[4], low[4];
       imma_u8s8(high, a, b.x, b.y);
       imma_u8u8(low, a, b.z, b.w);
@@ -116,11 +135,9 @@ __device__ __forceinline__ void q4k_unit(const uint8_t* pA, const uint8_t* pB, i
     uint32_t a[4];
     a[0] = a[2] = hsub2_u32(__byte_perm(pairA, 0x64u, 0x4140), k1024);
     a[1] = a[3] = hsub2_u32(__byte_perm(pairB, 0x64u, 0x4140), k1024);
-    const uint2 b = lds64(sums);
-    mma_16816(accm, a, b.x, b.y);
+    mma_16816(accm, a, f.sums.x, f.sums.y);
   }
-  const uint2 xsBits = lds64(scales);
-  const float xs0 = __uint_as_float(xsBits.x), xs1 = __uint_as_float(xsBits.y);
+  const float xs0 = __uint_as_float(f.scales.x), xs1 = __uint_as_float(f.scales.y);
   const float2 dA = __half22float2(*reinterpret_cast<const __half2*>(&hA.x)), dB = __half22float2(*reinterpret_cast<const __half2*>(&hB.x));
   const float mA = 32.f * dA.y, mB = 32.f * dB.y;
   total[0] += xs0 * (dA.x * fmaf(float(sumHigh[0]), 256.f, float(sumLow[0])) - mA * accm[0]);
@@ -140,8 +157,7 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
   constexpr int kStages = stage_count<NMAT>();
   extern __shared__ __align__(128) uint8_t smemRaw[];
   Control& ctl = *reinterpret_cast<Control*>(smemRaw);
-  uint8_t* image = smemRaw + kControlBytes;
-  float* partial = reinterpret_cast<float*>(image + size_t(kChunkBlocks) * kImageBlockBytes);
+  float* partial = reinterpret_cast<float*>(smemRaw + kControlBytes);
   uint8_t* ring = reinterpret_cast<uint8_t*>(partial + 2 * NMAT * kConsumerWarps * 128);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -153,8 +169,10 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
       mbar_init(&ctl.full[s], 1);
       mbar_init(&ctl.empty[s], kStageWarps);
     }
-    mbar_init(&ctl.imageFull, 1);
-    mbar_init(&ctl.imageEmpty, kConsumerWarps);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&ctl.partialReady[b], kConsumerWarps);
+      mbar_init(&ctl.partialFree[b], 1);
+    }
     ctl.abort = 0;
     mbar_fence_init();
   }
@@ -163,71 +181,25 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
   volatile int* abortFlag = &ctl.abort;
 
   if (warp == kProducerWarp) {
-    // ---- producer (one thread): weight slabs into the ring, and the activation image of each K chunk ----
-    // The weights do not depend on the kernels before this one, so the ring is filled before the wait for them; the
-    // first image does, so it is requested after that wait, once the ring is full. The image of a later chunk
-    // replaces the one the consumers are still reading: the weights of that chunk are streamed into the ring
-    // regardless, and the image is requested at the first moment the consumers have released the old one, which the
-    // wait for a ring slot polls for (the consumers cannot free a slot of the new chunk before they have its image).
+    // ---- producer (one thread): weight slabs into the ring. The weights do not depend on the kernels before this
+    // one, so the ring fills while they finish.
     if (lane == 0) {
       uint32_t it = 0;
-      int pendingChunk = -1, pendingBlocks = 0;  // image not yet requested
-      bool firstImage = false, ok = true;
-      auto load_image = [&](int chunk, int chunkBlocks) {
-        mbar_arrive_expect_tx(&ctl.imageFull, uint32_t(chunkBlocks) * kImageBlockBytes);
-        for (int first = 0; first < chunkBlocks; first += kImagePieceBlocks) {
-          const int count = min(kImagePieceBlocks, chunkBlocks - first);
-          bulk_load(image + size_t(first) * kImageBlockBytes, p.image + size_t(chunk * kChunkBlocks + first) * kImageBlockBytes,
-                    uint32_t(count) * kImageBlockBytes, &ctl.imageFull);
-        }
-      };
-      auto load_pending_if_free = [&]() {
-        if (pendingChunk >= 0 && mbar_test_wait(&ctl.imageEmpty, (pendingChunk - 1) & 1)) {
-          load_image(pendingChunk, pendingBlocks);
-          pendingChunk = -1;
-        }
-      };
-      auto give_up = [&]() {
-        *abortFlag = 1;
-        atomicExch(p.status, kStatusBarrierTimeout);
-        ok = false;
-      };
-      for (int chunk = 0; chunk < chunks && ok && !*abortFlag; ++chunk) {
+      bool ok = true;
+      for (int chunk = 0; chunk < chunks && ok; ++chunk) {
         const int chunkBlocks = min(kChunkBlocks, blocksPerRow - chunk * kChunkBlocks);
         const int groups = (chunkBlocks + kStageBlocks - 1) / kStageBlocks;
-        if (pendingChunk >= 0) {  // a chunk so short that its image was never asked for while its slabs were issued
-          if (!mbar_wait_bounded(&ctl.imageEmpty, (pendingChunk - 1) & 1, abortFlag)) {
-            give_up();
-            break;
-          }
-          load_pending_if_free();
-        }
-        if (chunk > 0)
-          pendingChunk = chunk, pendingBlocks = chunkBlocks;
         for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x) {
           const int segment = find_segment(p, tile);
           const int row0 = (tile - p.seg[segment].tile0) * kTileRows;
           for (int mat = 0; mat < NMAT && ok; ++mat) {
             for (int grp = 0; grp < groups; ++grp, ++it) {
               const uint32_t slot = it % kStages, round = it / kStages;
-              if (!firstImage && it == kStages) {  // the ring is full; nothing is released before the consumers have an image
-                pdl_wait();
-                load_image(0, chunkBlocks);
-                firstImage = true;
-              }
-              if (round > 0) {
-                // wait for the slot; bounded like every wait of this kernel
-                bool freed = false;
-                for (uint32_t spin = 0; spin < (1u << 22) && !freed; ++spin) {
-                  load_pending_if_free();
-                  freed = mbar_test_wait(&ctl.empty[slot], (round - 1) & 1);
-                  if (!freed && (spin & 1023u) == 1023u && *abortFlag)
-                    break;
-                }
-                if (!freed) {
-                  give_up();
-                  break;
-                }
+              if (round > 0 && !mbar_wait_bounded(&ctl.empty[slot], (round - 1) & 1, abortFlag)) {
+                *abortFlag = 1;
+                atomicExch(p.status, kStatusBarrierTimeout);
+                ok = false;
+                break;
               }
               // One tiled copy moves the whole slab; bytes past the end of a row are zero-filled and still counted, so
               // the transaction size is always the full box.
@@ -241,17 +213,6 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
             }
           }
         }
-        if (ok && !firstImage) {  // fewer stages than the ring holds
-          pdl_wait();
-          load_image(0, chunkBlocks);
-          firstImage = true;
-        }
-      }
-      if (ok && pendingChunk >= 0) {
-        if (mbar_wait_bounded(&ctl.imageEmpty, (pendingChunk - 1) & 1, abortFlag))
-          load_pending_if_free();
-        else
-          give_up();
       }
     }
     __syncwarp();
@@ -259,60 +220,78 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
     return;
   }
 
-  // Named barriers between consumers and finishers, per partial-sum buffer b = tile parity: 1 + b "partial sums of a
-  // tile are stored" (consumers arrive, finishers wait), 3 + b "the buffer has been read" (finishers arrive,
-  // consumers wait before they store into it again two tiles later).
-  if (warp >= kConsumerWarps) {
-    // ---- finishers: 128 threads, one per element of a tile's 16 x 8 result ----
+  // Consumers and the finisher meet on two mbarriers per partial-sum buffer b = tile parity: partialReady[b] "every
+  // consumer warp has stored its partial sums of the tile" and partialFree[b] "the finisher has read them", which a
+  // consumer tests before it stores into the buffer again two tiles later. Nobody waits for a warp of its own role.
+  if (warp == kFinisherWarp) {
+    // ---- finisher: one warp, four consecutive elements of a tile's 16 x 8 result per lane ----
     pdl_wait();
-    const int element = (warp - kConsumerWarps) * kWarp + lane;
     int tileCounter = 0;
     for (int chunk = 0; chunk < chunks; ++chunk)
       for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++tileCounter) {
-        // What is added to the result (the residual, or the sum over the earlier K chunks) is fetched before the wait.
-        float* destination = nullptr;
-        float addend = 0.f;
-        if ((element >> 4) < p.m) {
-          const GemvSeg& seg = p.nseg == 1 ? p.seg[0] : p.seg[find_segment(p, tile)];
-          const size_t at = size_t(element >> 4) * seg.ldy + size_t(tile - seg.tile0) * kTileRows + (element & 15);
-          destination = seg.y + at;
+        // Lane l owns elements 4l .. 4l+3 of the tile: activation row l/4, weight rows 4(l%4) .. +3, which are 16
+        // consecutive bytes of the result. What is added to it (the residual, or the sum over the earlier K chunks) is
+        // fetched before the wait.
+        const GemvSeg& seg = p.nseg == 1 ? p.seg[0] : p.seg[find_segment(p, tile)];
+        const int row = lane >> 2;
+        float4* destination = nullptr;
+        float4 addend = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row < p.m) {
+          const size_t at = size_t(row) * seg.ldy + size_t(tile - seg.tile0) * kTileRows + (lane & 3) * 4;
+          destination = reinterpret_cast<float4*>(seg.y + at);
           if (NMAT == 1 && chunk > 0)
             addend = *destination;
           else if (NMAT == 1 && seg.res)
-            addend = seg.res[at];
+            addend = *reinterpret_cast<const float4*>(seg.res + at);
         }
         const int buffer = tileCounter & 1;
-        const float* sums = partial + size_t(buffer) * NMAT * kConsumerWarps * 128;
-        named_barrier(1 + buffer, kHandoffThreads);
-        float sum[NMAT];
+        const float4* sums = reinterpret_cast<const float4*>(partial + size_t(buffer) * NMAT * kConsumerWarps * 128) + lane;
+        if (!mbar_wait_bounded(&ctl.partialReady[buffer], (tileCounter >> 1) & 1, abortFlag)) {
+          *abortFlag = 1;
+          atomicExch(p.status, kStatusBarrierTimeout);
+          return;
+        }
+        float4 sum[NMAT];
 #pragma unroll
         for (int mat = 0; mat < NMAT; ++mat) {
-          sum[mat] = 0.f;
+          float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;  // two chains in a fixed order: the result does not depend on timing
 #pragma unroll
-          for (int w = 0; w < kConsumerWarps; ++w)
-            sum[mat] += sums[(mat * kConsumerWarps + w) * 128 + element];
+          for (int w = 0; w < kConsumerWarps; w += 2) {
+            const float4 u = sums[(mat * kConsumerWarps + w) * 32], v = sums[(mat * kConsumerWarps + w + 1) * 32];
+            a.x += u.x, a.y += u.y, a.z += u.z, a.w += u.w;
+            b.x += v.x, b.y += v.y, b.z += v.z, b.w += v.w;
+          }
+          sum[mat] = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
         }
-        named_barrier_arrive(3 + buffer, kHandoffThreads);
-        if (destination)
-          *destination = NMAT == 2 ? silu_f(sum[0]) * sum[1] : sum[0] + addend;
+        __syncwarp();
+        if (lane == 0)
+          mbar_arrive(&ctl.partialFree[buffer]);
+        if (destination) {
+          const float4 first = sum[0], second = sum[NMAT - 1];
+          *destination = NMAT == 2 ? make_float4(silu_f(first.x) * second.x, silu_f(first.y) * second.y, silu_f(first.z) * second.z, silu_f(first.w) * second.w)
+                                   : make_float4(first.x + addend.x, first.y + addend.y, first.z + addend.z, first.w + addend.w);
+        }
       }
     return;
   }
 
   // ---- consumers ----
-  pdl_wait();
+  pdl_wait();  // the image comes from the kernels before this one
   const int g = lane >> 2, t = lane & 3, half = warp / kStageWarps, unit = warp % kStageWarps;
-  const uint8_t *laneImage = image + g * 64 + t * 16, *laneSums = image + kImageSumOffset + lane * 8, *laneScales = image + kImageScaleOffset + t * 8;
   const int laneRow = g * kRowPitch + unit * kBlockBytes;
   uint32_t it = 0, mine = half, slot = half, phase = 0;
   int tileCounter = 0;
   for (int chunk = 0; chunk < chunks; ++chunk) {
     const int chunkBlocks = min(kChunkBlocks, blocksPerRow - chunk * kChunkBlocks);
     const int groups = (chunkBlocks + kStageBlocks - 1) / kStageBlocks;
-    if (!*abortFlag && !mbar_wait_bounded(&ctl.imageFull, chunk & 1, abortFlag)) {
-      *abortFlag = 1;
-      atomicExch(p.status, kStatusBarrierTimeout);
-    }
+    // With two slabs per tile the stages of a tile alternate between the halves (a chunk starts at an even stage,
+    // only the last chunk of a row can be a single slab), with one slab every stage is slab 0: either way this warp
+    // meets the same super-block in every tile of the chunk.
+    const int myBlock = (groups == 2 ? half * kStageBlocks : 0) + unit;
+    const bool live = myBlock < chunkBlocks && !(p.debug & 2);
+    Fragments fragments;
+    if (live)
+      fragments = load_fragments(p.image + size_t(chunk * kChunkBlocks + myBlock) * kImageBlockBytes, lane);
     for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++tileCounter) {
       float total[NMAT][4];
 #pragma unroll
@@ -326,30 +305,30 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
           slot -= kStages;
           phase ^= 1;
         }
-        const int local = int(mine - it), mat = NMAT == 2 && local >= groups, grp = local - mat * groups;
+        const int mat = NMAT == 2 && int(mine - it) >= groups;
         if (!mbar_wait_bounded(&ctl.full[slot], phase, abortFlag)) {  // also leaves when another role raised the abort flag
           *abortFlag = 1;
           atomicExch(p.status, kStatusBarrierTimeout);
           break;
         }
-        const int count = min(kStageBlocks, chunkBlocks - grp * kStageBlocks);
-        if (unit < count && !(p.debug & 2)) {
+        if (live) {
           const uint8_t* rows = ring + slot * kStageBytes + laneRow;
-          const int at = (grp * kStageBlocks + unit) * kImageBlockBytes;
           if (NMAT == 2 && mat)
-            q4k_unit(rows, rows + 8 * kRowPitch, t, laneImage + at, laneSums + at, laneScales + at, total[NMAT - 1]);
+            q4k_unit(rows, rows + 8 * kRowPitch, t, fragments, total[NMAT - 1]);
           else
-            q4k_unit(rows, rows + 8 * kRowPitch, t, laneImage + at, laneSums + at, laneScales + at, total[0]);
+            q4k_unit(rows, rows + 8 * kRowPitch, t, fragments, total[0]);
         }
         __syncwarp();
         if (lane == 0)
           mbar_arrive(&ctl.empty[slot]);
       }
       it += perTile;
-      // Hand the partial sums of the K split to the finishers and go on with the next tile.
+      // Hand the partial sums of the K split to the finisher and go on with the next tile.
       const int buffer = tileCounter & 1;
-      if (tileCounter >= 2)
-        named_barrier(3 + buffer, kHandoffThreads);
+      if (tileCounter >= 2 && !mbar_wait_bounded(&ctl.partialFree[buffer], ((tileCounter >> 1) - 1) & 1, abortFlag)) {
+        *abortFlag = 1;
+        atomicExch(p.status, kStatusBarrierTimeout);
+      }
       float* sums = partial + size_t(buffer) * NMAT * kConsumerWarps * 128;
 #pragma unroll
       for (int mat = 0; mat < NMAT; ++mat) {
@@ -359,12 +338,10 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
         dst[(2 * t) * 16 + g + 8] = total[mat][2];
         dst[(2 * t + 1) * 16 + g + 8] = total[mat][3];
       }
-      named_barrier_arrive(1 + buffer, kHandoffThreads);
+      __syncwarp();
+      if (lane == 0)
+        mbar_arrive(&ctl.partialReady[buffer]);
     }
-    // This chunk's image may now be overwritten.
-    __syncwarp();
-    if (lane == 0)
-      mbar_arrive(&ctl.imageEmpty);
   }
 }
 
