@@ -9,7 +9,7 @@
 // scale and the -dmin * m term (one fp16 MMA against the sub-block sums) are applied once per super-block.
 // The only approximation is the 16-bit activation grid: absolute error at most 1.6e-5 of the block maximum.
 //
-// One persistent CTA per SM: 16 consumer warps, 1 finisher warp and 1 producer warp. The producer streams 16-row x
+// One persistent CTA per SM: 16 consumer warps, 3 finisher warps and 1 producer warp (five warps per scheduler). The producer streams 16-row x
 // 8-super-block weight slabs with one tiled TMA copy each into a shared-memory ring. A consumer warp works on the
 // same super-block of every tile (warp w of a half takes super-block w of the half's slab), so it keeps the activation
 // fragments of that super-block in registers for a whole K chunk, loaded straight from the image in global memory:
@@ -24,8 +24,8 @@ namespace {
 
 constexpr int kConsumerWarps = 16;  // two halves of 8; consecutive ring stages alternate between the halves
 constexpr int kStageWarps = 8;       // one warp per super-block of a stage
-constexpr int kFinisherWarp = kConsumerWarps;  // sums the consumers' partial results of a tile and stores it
-constexpr int kProducerWarp = kConsumerWarps + 1;
+constexpr int kFinisherWarps = 3;  // each sums the consumers' partial results of every third tile and stores it
+constexpr int kProducerWarp = kConsumerWarps + kFinisherWarps;  // 16 + 3 + 1 warps: five on each scheduler
 constexpr int kThreads = (kProducerWarp + 1) * kWarp;
 constexpr int kChunkBlocks = 16;  // super-blocks of K per pass over the tiles: two slabs, one per half
 constexpr int kStageBlocks = kGemvStageBlocks;
@@ -38,13 +38,13 @@ static_assert(kChunkBlocks == 2 * kStageBlocks, "a consumer warp's super-block w
 
 struct Control {
   uint64_t full[kMaxStages], empty[kMaxStages];
-  uint64_t partialReady[2], partialFree[2];  // per partial-sum buffer: consumers -> finisher, finisher -> consumers
+  uint64_t partialReady[kFinisherWarps], partialFree[kFinisherWarps];  // per partial-sum buffer: consumers -> its finisher and back
   int abort;
 };
 constexpr int kControlBytes = 256;
 static_assert(sizeof(Control) <= kControlBytes, "control block overlaps the partial sums");
 
-template <int NMAT> constexpr size_t fixed_bytes() { return kControlBytes + size_t(2) * NMAT * kConsumerWarps * 128 * 4; }
+template <int NMAT> constexpr size_t fixed_bytes() { return kControlBytes + size_t(kFinisherWarps) * NMAT * kConsumerWarps * 128 * 4; }
 template <int NMAT> constexpr int stage_count() {
   int stages = int((size_t(227) * 1024 - fixed_bytes<NMAT>()) / kStageBytes);
   return stages > kMaxStages ? kMaxStages : stages;
@@ -158,7 +158,7 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
   extern __shared__ __align__(128) uint8_t smemRaw[];
   Control& ctl = *reinterpret_cast<Control*>(smemRaw);
   float* partial = reinterpret_cast<float*>(smemRaw + kControlBytes);
-  uint8_t* ring = reinterpret_cast<uint8_t*>(partial + 2 * NMAT * kConsumerWarps * 128);
+  uint8_t* ring = reinterpret_cast<uint8_t*>(partial + kFinisherWarps * NMAT * kConsumerWarps * 128);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int blocksPerRow = p.k / 256;
@@ -169,7 +169,7 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
       mbar_init(&ctl.full[s], 1);
       mbar_init(&ctl.empty[s], kStageWarps);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kFinisherWarps; ++b) {
       mbar_init(&ctl.partialReady[b], kConsumerWarps);
       mbar_init(&ctl.partialFree[b], 1);
     }
@@ -220,15 +220,18 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
     return;
   }
 
-  // Consumers and the finisher meet on two mbarriers per partial-sum buffer b = tile parity: partialReady[b] "every
-  // consumer warp has stored its partial sums of the tile" and partialFree[b] "the finisher has read them", which a
-  // consumer tests before it stores into the buffer again two tiles later. Nobody waits for a warp of its own role.
-  if (warp == kFinisherWarp) {
-    // ---- finisher: one warp, four consecutive elements of a tile's 16 x 8 result per lane ----
+  // The partial sums of a tile go through one of three buffers, taken in turn within a K chunk, and each buffer has
+  // its own finisher warp and two mbarriers: partialReady[b] "every consumer warp has stored its partial sums" and
+  // partialFree[b] "the finisher has read them", which a consumer tests before it stores into the buffer again.
+  // Nobody waits for a warp of its own role, each barrier is watched phase by phase by the same warps, and a tile of
+  // the result has the same finisher in every K chunk, so the sum over the earlier chunks it adds is its own store.
+  if (warp >= kConsumerWarps) {
+    // ---- finishers: four consecutive elements of a tile's 16 x 8 result per lane ----
     pdl_wait();
-    int tileCounter = 0;
+    const int buffer = warp - kConsumerWarps;
+    uint32_t uses = 0;
     for (int chunk = 0; chunk < chunks; ++chunk)
-      for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++tileCounter) {
+      for (int tile = blockIdx.x + buffer * gridDim.x; tile < p.tiles; tile += kFinisherWarps * gridDim.x, ++uses) {
         // Lane l owns elements 4l .. 4l+3 of the tile: activation row l/4, weight rows 4(l%4) .. +3, which are 16
         // consecutive bytes of the result. What is added to it (the residual, or the sum over the earlier K chunks) is
         // fetched before the wait.
@@ -244,9 +247,8 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
           else if (NMAT == 1 && seg.res)
             addend = *reinterpret_cast<const float4*>(seg.res + at);
         }
-        const int buffer = tileCounter & 1;
         const float4* sums = reinterpret_cast<const float4*>(partial + size_t(buffer) * NMAT * kConsumerWarps * 128) + lane;
-        if (!mbar_wait_bounded(&ctl.partialReady[buffer], (tileCounter >> 1) & 1, abortFlag)) {
+        if (!mbar_wait_bounded(&ctl.partialReady[buffer], uses & 1, abortFlag)) {
           *abortFlag = 1;
           atomicExch(p.status, kStatusBarrierTimeout);
           return;
@@ -280,7 +282,7 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
   const int g = lane >> 2, t = lane & 3, half = warp / kStageWarps, unit = warp % kStageWarps;
   const int laneRow = g * kRowPitch + unit * kBlockBytes;
   uint32_t it = 0, mine = half, slot = half, phase = 0;
-  int tileCounter = 0;
+  uint32_t bufferState = 0;  // bit b: parity of the next use of partial-sum buffer b; bit 4 + b: it has been used before
   for (int chunk = 0; chunk < chunks; ++chunk) {
     const int chunkBlocks = min(kChunkBlocks, blocksPerRow - chunk * kChunkBlocks);
     const int groups = (chunkBlocks + kStageBlocks - 1) / kStageBlocks;
@@ -292,7 +294,8 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
     Fragments fragments;
     if (live)
       fragments = load_fragments(p.image + size_t(chunk * kChunkBlocks + myBlock) * kImageBlockBytes, lane);
-    for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++tileCounter) {
+    int buffer = 0;
+    for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, buffer = buffer == kFinisherWarps - 1 ? 0 : buffer + 1) {
       float total[NMAT][4];
 #pragma unroll
       for (int mat = 0; mat < NMAT; ++mat)
@@ -323,12 +326,13 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
           mbar_arrive(&ctl.empty[slot]);
       }
       it += perTile;
-      // Hand the partial sums of the K split to the finisher and go on with the next tile.
-      const int buffer = tileCounter & 1;
-      if (tileCounter >= 2 && !mbar_wait_bounded(&ctl.partialFree[buffer], ((tileCounter >> 1) - 1) & 1, abortFlag)) {
+      // Hand the partial sums of the K split to the buffer's finisher and go on with the next tile.
+      const uint32_t parity = (bufferState >> buffer) & 1u;
+      if (((bufferState >> (4 + buffer)) & 1u) && !mbar_wait_bounded(&ctl.partialFree[buffer], parity ^ 1u, abortFlag)) {
         *abortFlag = 1;
         atomicExch(p.status, kStatusBarrierTimeout);
       }
+      bufferState = (bufferState ^ (1u << buffer)) | (16u << buffer);
       float* sums = partial + size_t(buffer) * NMAT * kConsumerWarps * 128;
 #pragma unroll
       for (int mat = 0; mat < NMAT; ++mat) {
