@@ -89,7 +89,7 @@ class ClockSampler:
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one q4k_decode_kernel launch at the config-1 shape, from the ncu capture
 # summarised in profiles/q4k_decode_12288x4096_m8.md (the same shape and launch as the roofline leg below).
-GEMV_DRAM_BYTES_PER_LAUNCH = 28_402_176
+GEMV_DRAM_BYTES_PER_LAUNCH = 28_399_488
 
 
 def gemv_roofline(device_index, copies=24, replays=20, xsplit=None, qtype=None, n=12288, k=4096, m=8):
