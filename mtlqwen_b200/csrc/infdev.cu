@@ -502,9 +502,7 @@ static int linear_run(infdev_ctx* ctx, int type, bool pair, int count, const voi
   infdev::GemvParams p{};
   p.nseg = count;
   int tiles = 0;
-  bool integer = type == INFDEV_Q4_K && ctx->integerDecode && k <= 16384;
-  for (int i = 0; i < count; ++i)  // the integer kernel stores 16 bytes at a time
-    integer = integer && aligned16(y[i]) && (!residual || aligned16(residual[i]));
+  const bool integer = type == INFDEV_Q4_K && ctx->integerDecode && k <= 16384;
   const int pad = integer ? infdev::kDecodePadBytes : 0;
   for (int i = 0; i < count; ++i) {
     if (n[i] <= 0 || n[i] % 16 || !aligned16(w[i]) || (pair && !aligned16(w2[i])))

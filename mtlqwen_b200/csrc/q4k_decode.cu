@@ -100,8 +100,8 @@ __device__ __forceinline__ void q4k_unit(const uint8_t* pA, const uint8_t* pB, i
   const uint32_t mnA[2] = {hA.z & 0x3f3f3f3fu, ((hA.w >> 4) & 0x0f0f0f0fu) | ((hA.z >> 2) & 0x30303030u)};
   const uint32_t scB[2] = {hB.y & 0x3f3f3f3fu, (hB.w & 0x0f0f0f0fu) | ((hB.y >> 2) & 0x30303030u)};
   const uint32_t mnB[2] = {hB.z & 0x3f3f3f3fu, ((hB.w >> 4) & 0x0f0f0f0fu) | ((hB.z >> 2) & 0x30303030u)};
-  // sum over the 8 sub-blocks of scale * (integer dot product), separately for the low and the high activation byte:
-  // |low| <= 8 * 63 * 15 * 32 * 255 and |high| <= 8 * 63 * 15 * 32 * 128 both stay far inside int32.
+  // 16 x the sum over the 8 sub-blocks of scale * (integer dot product), separately for the low and the high activation
+  // byte: |low| <= 16 * 8 * 63 * 15 * 32 * 255 < 2^30 and |high| <= 16 * 8 * 63 * 15 * 32 * 128 both stay inside int32.
   int sumLow[4] = {0, 0, 0, 0}, sumHigh[4] = {0, 0, 0, 0};
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
@@ -110,16 +110,16 @@ __device__ __forceinline__ void q4k_unit(const uint8_t* pA, const uint8_t* pB, i
     for (int h = 0; h < 2; ++h) {
       const int j = 2 * c + h;
       uint32_t a[4];
-      if (h == 0) {
-        a[0] = qA.x & 0x0f0f0f0fu, a[1] = qB.x & 0x0f0f0f0fu, a[2] = qA.y & 0x0f0f0f0fu, a[3] = qB.y & 0x0f0f0f0fu;
-      } else {
-        a[0] = (qA.x >> 4) & 0x0f0f0f0fu, a[1] = (qB.x >> 4) & 0x0f0f0f0fu, a[2] = (qA.y >> 4) & 0x0f0f0f0fu, a[3] = (qB.y >> 4) & 0x0f0f0f0fu;
-      }
+      // Low nibbles as they are, high nibbles in place as 16 q (still a byte); the sub-block scale of the low ones is
+      // taken 16-fold instead, and the common factor leaves with d at the end.
+      const uint32_t mask = h == 0 ? 0x0f0f0f0fu : 0xf0f0f0f0u;
+      a[0] = qA.x & mask, a[1] = qB.x & mask, a[2] = qA.y & mask, a[3] = qB.y & mask;
       const uint4 b = f.quant[j];
       int high[4], low[4];
       imma_u8s8(high, a, b.x, b.y);
       imma_u8u8(low, a, b.z, b.w);
-      const int sA = int(__byte_perm(scA[j >> 2], 0u, 0x4440 + (j & 3))), sB = int(__byte_perm(scB[j >> 2], 0u, 0x4440 + (j & 3)));
+      const int byteA = int(__byte_perm(scA[j >> 2], 0u, 0x4440 + (j & 3))), byteB = int(__byte_perm(scB[j >> 2], 0u, 0x4440 + (j & 3)));
+      const int sA = h == 0 ? byteA * 16 : byteA, sB = h == 0 ? byteB * 16 : byteB;
       sumLow[0] += sA * low[0], sumHigh[0] += sA * high[0];
       sumLow[1] += sA * low[1], sumHigh[1] += sA * high[1];
       sumLow[2] += sB * low[2], sumHigh[2] += sB * high[2];
@@ -139,11 +139,11 @@ __device__ __forceinline__ void q4k_unit(const uint8_t* pA, const uint8_t* pB, i
   }
   const float xs0 = __uint_as_float(f.scales.x), xs1 = __uint_as_float(f.scales.y);
   const float2 dA = __half22float2(*reinterpret_cast<const __half2*>(&hA.x)), dB = __half22float2(*reinterpret_cast<const __half2*>(&hB.x));
-  const float mA = 32.f * dA.y, mB = 32.f * dB.y;
-  total[0] += xs0 * (dA.x * fmaf(float(sumHigh[0]), 256.f, float(sumLow[0])) - mA * accm[0]);
-  total[1] += xs1 * (dA.x * fmaf(float(sumHigh[1]), 256.f, float(sumLow[1])) - mA * accm[1]);
-  total[2] += xs0 * (dB.x * fmaf(float(sumHigh[2]), 256.f, float(sumLow[2])) - mB * accm[2]);
-  total[3] += xs1 * (dB.x * fmaf(float(sumHigh[3]), 256.f, float(sumLow[3])) - mB * accm[3]);
+  const float mA = 32.f * dA.y, mB = 32.f * dB.y, sixteenthA = 0.0625f * dA.x, sixteenthB = 0.0625f * dB.x;
+  total[0] += xs0 * (sixteenthA * fmaf(float(sumHigh[0]), 256.f, float(sumLow[0])) - mA * accm[0]);
+  total[1] += xs1 * (sixteenthA * fmaf(float(sumHigh[1]), 256.f, float(sumLow[1])) - mA * accm[1]);
+  total[2] += xs0 * (sixteenthB * fmaf(float(sumHigh[2]), 256.f, float(sumLow[2])) - mB * accm[2]);
+  total[3] += xs1 * (sixteenthB * fmaf(float(sumHigh[3]), 256.f, float(sumLow[3])) - mB * accm[3]);
 }
 
 __device__ __forceinline__ int find_segment(const GemvParams& p, int tile) {
@@ -226,27 +226,29 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
   // Nobody waits for a warp of its own role, each barrier is watched phase by phase by the same warps, and a tile of
   // the result has the same finisher in every K chunk, so the sum over the earlier chunks it adds is its own store.
   if (warp >= kConsumerWarps) {
-    // ---- finishers: four consecutive elements of a tile's 16 x 8 result per lane ----
+    // ---- finishers: four elements of a tile's 16 x 8 result per lane ----
     pdl_wait();
     const int buffer = warp - kConsumerWarps;
     uint32_t uses = 0;
     for (int chunk = 0; chunk < chunks; ++chunk)
       for (int tile = blockIdx.x + buffer * gridDim.x; tile < p.tiles; tile += kFinisherWarps * gridDim.x, ++uses) {
-        // Lane l owns elements 4l .. 4l+3 of the tile: activation row l/4, weight rows 4(l%4) .. +3, which are 16
-        // consecutive bytes of the result. What is added to it (the residual, or the sum over the earlier K chunks) is
+        // Lane (g = lane/4, t = lane%4) sums what the same lane of every consumer warp holds: weight rows g and g+8 for
+        // activation rows 2t and 2t+1. What is added to them (the residual, or the sum over the earlier K chunks) is
         // fetched before the wait.
         const GemvSeg& seg = p.nseg == 1 ? p.seg[0] : p.seg[find_segment(p, tile)];
-        const int row = lane >> 2;
-        float4* destination = nullptr;
-        float4 addend = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (row < p.m) {
-          const size_t at = size_t(row) * seg.ldy + size_t(tile - seg.tile0) * kTileRows + (lane & 3) * 4;
-          destination = reinterpret_cast<float4*>(seg.y + at);
-          if (NMAT == 1 && chunk > 0)
-            addend = *destination;
-          else if (NMAT == 1 && seg.res)
-            addend = *reinterpret_cast<const float4*>(seg.res + at);
-        }
+        const int g = lane >> 2, t = lane & 3;
+        float* destination[2] = {nullptr, nullptr};  // activation rows 2t, 2t+1 at weight row g; g + 8 is 8 floats on
+        float addend[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+          if (2 * t + r < p.m) {
+            const size_t at = size_t(2 * t + r) * seg.ldy + size_t(tile - seg.tile0) * kTileRows + g;
+            destination[r] = seg.y + at;
+            if (NMAT == 1 && chunk > 0)
+              addend[r] = destination[r][0], addend[2 + r] = destination[r][8];
+            else if (NMAT == 1 && seg.res)
+              addend[r] = seg.res[at], addend[2 + r] = seg.res[at + 8];
+          }
         const float4* sums = reinterpret_cast<const float4*>(partial + size_t(buffer) * NMAT * kConsumerWarps * 128) + lane;
         if (!mbar_wait_bounded(&ctl.partialReady[buffer], uses & 1, abortFlag)) {
           *abortFlag = 1;
@@ -268,11 +270,13 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
         __syncwarp();
         if (lane == 0)
           mbar_arrive(&ctl.partialFree[buffer]);
-        if (destination) {
-          const float4 first = sum[0], second = sum[NMAT - 1];
-          *destination = NMAT == 2 ? make_float4(silu_f(first.x) * second.x, silu_f(first.y) * second.y, silu_f(first.z) * second.z, silu_f(first.w) * second.w)
-                                   : make_float4(first.x + addend.x, first.y + addend.y, first.z + addend.z, first.w + addend.w);
-        }
+        const float4 first = sum[0], second = sum[NMAT - 1];
+        const float lowRows[2] = {NMAT == 2 ? silu_f(first.x) * second.x : first.x + addend[0], NMAT == 2 ? silu_f(first.y) * second.y : first.y + addend[1]};
+        const float highRows[2] = {NMAT == 2 ? silu_f(first.z) * second.z : first.z + addend[2], NMAT == 2 ? silu_f(first.w) * second.w : first.w + addend[3]};
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+          if (destination[r])
+            destination[r][0] = lowRows[r], destination[r][8] = highRows[r];
       }
     return;
   }
@@ -336,11 +340,7 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
       float* sums = partial + size_t(buffer) * NMAT * kConsumerWarps * 128;
 #pragma unroll
       for (int mat = 0; mat < NMAT; ++mat) {
-        float* dst = sums + (mat * kConsumerWarps + warp) * 128;
-        dst[(2 * t) * 16 + g] = total[mat][0];
-        dst[(2 * t + 1) * 16 + g] = total[mat][1];
-        dst[(2 * t) * 16 + g + 8] = total[mat][2];
-        dst[(2 * t + 1) * 16 + g + 8] = total[mat][3];
+        reinterpret_cast<float4*>(sums + (mat * kConsumerWarps + warp) * 128)[lane] = make_float4(total[mat][0], total[mat][1], total[mat][2], total[mat][3]);
       }
       __syncwarp();
       if (lane == 0)
