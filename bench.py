@@ -280,6 +280,10 @@ def run_ours(args, rank, world):
     "config": workload_config(), "clocks": clocks, "gpu_launches": int(totals[2]),
     "e2e": {"value": totals[1] / worst[1], "unit": "tok/s", "h2d_bytes_per_step": SEQUENCES * (64 + 4) + 128,
             "d2h_bytes_per_step": SEQUENCES * 4 + 4,
+            # rank 0: wall ms per step seen by the readers, and the part of it the scheduler spends inside a pass
+            # (record, graph launch, wait for the stream); the rest is batch building and token hand-over
+            "wall_ms_per_step": 1e3 * wall / max(1, passes), "in_pass_ms_per_step": (c1["micros"] - c0["micros"]) / 1e3 / max(1, passes),
+            "scheduler_ms_per_step": {key: (c1[key + "_micros"] - c0[key + "_micros"]) / 1e3 / max(1, passes) for key in ("build", "lock", "publish")},
             "note": "through infeng_sequence_append/read with host token buffers; token ids, query records and sampled tokens cross PCIe every step"},
     "roofline": {"bound": "hbm", "kernel": "q4k_decode_kernel 12288x4096 M=8 (BASELINE config 1)", "achieved": algorithmic / kernel_seconds / 1e9,
                  "peak": peak, "unit": "GB/s", "frac": algorithmic / kernel_seconds / 1e9 / peak, "of": peak_kind, "traffic": GEMV_DRAM_BYTES_PER_LAUNCH,

@@ -42,7 +42,8 @@ int32_t infeng_sequence_read(infeng_sequence* sequence, uint32_t cursor);
 /* engine.cpp:294-297: 0 parameter count, 1 weight bytes, 2 K/V bytes ever bound, 3 drafter (0 none, 1 MTP),
  * 4 draft width. Additions for throughput accounting: 5 passes run, 6 rows processed, 7 microseconds spent in
  * passes (host clock, commit included), 8 decoder layers, 9 vocabulary size, 10 nanoseconds of device time of
- * the passes (CUDA events on the stream), 11 kernels launched. */
+ * the passes (CUDA events on the stream), 11 kernels launched, 12 to 14 microseconds the scheduler spent outside
+ * the passes: building batches, waiting for the engine lock after a pass, handing sampled tokens over. */
 uint64_t infeng_engine_info(infeng_engine* engine, uint32_t field);
 /* engine.cpp:299-303: 0 drafted tokens, 1 accepted tokens, 2 tokens held in the K/V cache. */
 uint64_t infeng_sequence_info(infeng_sequence* sequence, uint32_t field);

@@ -84,6 +84,9 @@ struct Engine {
   std::list<HybridCheckpoint> checkpointCache;
   std::array<Sequence*, maxBatchSequences> sequences{};
   std::array<std::pair<Tensor, Tensor>, maxBatchSequences> statePool;
+  // State records nobody refers to any more (evicted checkpoints, replaced inputs): kept for the next sequence that
+  // needs one, because returning 52 MB to the driver and asking for it again costs milliseconds of scheduler time.
+  std::vector<Tensor> spareStates;
   std::mutex mutex;
   std::condition_variable condition;
   std::thread worker;
@@ -92,6 +95,9 @@ struct Engine {
   uint64_t parameterCount = 0, modelBytes = 0;
   // step counters for roofline reporting
   std::atomic_uint64_t passes{0}, passRows{0}, passMicros{0}, passDeviceNanos{0};
+  // host microseconds of the scheduler outside the passes: building a batch, waiting for the engine lock after a
+  // pass, handing the sampled tokens over
+  std::atomic_uint64_t buildMicros{0}, lockMicros{0}, publishMicros{0};
   void* passEvents[2] = {nullptr, nullptr};  // CUDA events bracketing each pass on the stream
   // Pure-decode passes (every query one row, nothing speculative) have a fixed launch sequence for a given number of
   // live sequences; from its second occurrence such a pass is captured once into a CUDA graph and then replayed.
@@ -107,6 +113,8 @@ struct Engine {
   void bind(Sequence& sequence, uint32_t physical);
   void restorePrefix(Sequence& sequence);
   void publishPrefix(Sequence& sequence);
+  void retire(Tensor& state);
+  Tensor freshState();
   void schedule();
 };
 

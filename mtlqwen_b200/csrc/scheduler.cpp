@@ -67,15 +67,35 @@ bool Engine::reserve(const Batch& batch) {
           return false;
         kv->ensure(victim + 1);
         // A checkpoint that references the evicted block can no longer be restored.
-        checkpointCache.remove_if([victim](const HybridCheckpoint& checkpoint) {
-          return std::find(checkpoint.bindings.begin(), checkpoint.bindings.end(), victim) != checkpoint.bindings.end();
-        });
+        for (auto entry = checkpointCache.begin(); entry != checkpointCache.end();)
+          if (std::find(entry->bindings.begin(), entry->bindings.end(), victim) != entry->bindings.end()) {
+            retire(entry->arena);
+            entry = checkpointCache.erase(entry);
+          } else
+            ++entry;
         bind(sequence, victim);
       }
       blocks[sequence.bindings[logical]].touch = ++clock;
     }
   }
   return true;
+}
+
+// Drops a reference to a state record; the last one hands the record to the spare list instead of the driver.
+void Engine::retire(Tensor& state) {
+  if (state.buffer && state.buffer.use_count() == 1 && state.offset == 0 && state.bytes == stateBytes && spareStates.size() < 3 * maxBatchSequences)
+    spareStates.push_back(std::move(state));
+  state = Tensor{};
+}
+
+// A zeroed state record: a spare one if there is any.
+Tensor Engine::freshState() {
+  if (spareStates.empty())
+    return device.empty(stateBytes);
+  Tensor state = std::move(spareStates.back());
+  spareStates.pop_back();
+  device.check(infdev_fill(device.ctx, state.as<void>(), 0, state.bytes));
+  return state;
 }
 
 // Finds the deepest published prefix of the request and adopts its state arena and K/V bindings
@@ -97,6 +117,7 @@ void Engine::restorePrefix(Sequence& sequence) {
   checkpointCache.splice(checkpointCache.end(), checkpointCache, best);
   sequence.prefixHash = best->hash;
   const uint64_t touch = ++clock;
+  retire(statePool[sequence.slot].first);
   statePool[sequence.slot].first = best->arena;
   for (uint32_t physical : best->bindings) {
     bind(sequence, physical);
@@ -115,8 +136,10 @@ void Engine::publishPrefix(Sequence& sequence) {
       checkpointCache.splice(checkpointCache.end(), checkpointCache, entry);
       return;
     }
-  if (checkpointCache.size() == maxCheckpoints)
+  if (checkpointCache.size() == maxCheckpoints) {
+    retire(checkpointCache.front().arena);
     checkpointCache.pop_front();
+  }
   checkpointCache.push_back({sequence.prefixHash, statePool[sequence.slot].first, sequence.bindings});
 }
 
@@ -196,9 +219,20 @@ void Engine::schedule() {
   std::unique_lock<std::mutex> lock(mutex);
   auto ready = [](Sequence* sequence) { return sequence && sequence->active; };
   while (true) {
+    // The readers hear of the tokens of a pass once the next pass has been launched (below): woken while this thread
+    // still holds the lock and has a batch to build, they would only queue up behind it, and on a busy host push it
+    // off its core for milliseconds. With nothing left to launch they are told here, before this thread sleeps.
+    if (!closing && std::none_of(sequences.begin(), sequences.end(), ready))
+      condition.notify_all();
     condition.wait(lock, [&] { return closing || std::any_of(sequences.begin(), sequences.end(), ready); });
     if (closing)
       return;
+    auto stamp = std::chrono::steady_clock::now();
+    auto lap = [&stamp](std::atomic_uint64_t& counter) {
+      const auto now = std::chrono::steady_clock::now();
+      counter += uint64_t(std::chrono::duration_cast<std::chrono::microseconds>(now - stamp).count());
+      stamp = now;
+    };
     Batch batch;
     batch.queries = queryInput.contents<infdev_query>();
     std::array<infdev_query*, maxBatchSequences> prefills{};
@@ -211,7 +245,7 @@ void Engine::schedule() {
         restorePrefix(*sequence);
       // The output state must not be an arena that a checkpoint still shares.
       if (statePool[sequence->slot].second.buffer.use_count() > 1)
-        statePool[sequence->slot].second = device.empty(stateBytes);
+        statePool[sequence->slot].second = freshState();
       infdev_query& query = batch.queries[batch.size++];
       query = infdev_query{};
       query.count = 1;
@@ -245,7 +279,14 @@ void Engine::schedule() {
     }
     bool success = reserve(batch);
     lock.unlock();
+    lap(buildMicros);
     PassShape shape;
+    bool announced = false;
+    auto announce = [&] {  // the results of the pass before this one
+      if (!announced)
+        condition.notify_all();
+      announced = true;
+    };
     if (success) {
       try {
         if (stateBytes * batch.candidateRows > candidateStates.bytes)
@@ -271,6 +312,7 @@ void Engine::schedule() {
           shape = forward(*this, batch);
         }
         infdev_event_record(device.ctx, passEvents[1]);
+        announce();
         device.check(device.commit());
         passDeviceNanos += uint64_t(double(infdev_event_elapsed_ms(device.ctx, passEvents[0], passEvents[1])) * 1.0e6);
         passMicros += uint64_t(std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - started).count());
@@ -280,7 +322,10 @@ void Engine::schedule() {
         success = false;  // a device failure is reported to every sequence of the batch like a capacity failure
       }
     }
+    announce();
+    stamp = std::chrono::steady_clock::now();
     lock.lock();
+    lap(lockMicros);
     const int32_t *sampled = outputTokens.contents<int32_t>(), *proposed = draftTokens.contents<int32_t>();
     bool copied = false;
     for (uint32_t i = 0; i < batch.size; ++i) {
@@ -315,7 +360,7 @@ void Engine::schedule() {
     }
     if (copied)
       device.commit();
-    condition.notify_all();
+    lap(publishMicros);
   }
 }
 
@@ -418,6 +463,9 @@ uint64_t infeng_engine_info(infeng_engine* engine, uint32_t field) {
     case 9: return engine->vocab;
     case 10: return engine->passDeviceNanos.load();
     case 11: return infdev_launch_count(engine->device.ctx);
+    case 12: return engine->buildMicros.load();
+    case 13: return engine->lockMicros.load();
+    case 14: return engine->publishMicros.load();
     default: return 0;
   }
 }

@@ -107,11 +107,13 @@ class InferenceEngine:
     return _lib().infeng_engine_info(self.handle, 2)
 
   def step_counters(self):
-    """Passes run, packed rows processed, host microseconds and device nanoseconds spent in passes, and kernels
-    launched since the engine started."""
+    """Passes run, packed rows processed, host microseconds and device nanoseconds spent in passes, kernels launched,
+    and the scheduler's host microseconds outside the passes (batch building, waiting for the engine lock, handing
+    tokens over) since the engine started."""
     return {"passes": _lib().infeng_engine_info(self.handle, 5), "rows": _lib().infeng_engine_info(self.handle, 6),
             "micros": _lib().infeng_engine_info(self.handle, 7), "device_ns": _lib().infeng_engine_info(self.handle, 10),
-            "launches": _lib().infeng_engine_info(self.handle, 11)}
+            "launches": _lib().infeng_engine_info(self.handle, 11), "build_micros": _lib().infeng_engine_info(self.handle, 12),
+            "lock_micros": _lib().infeng_engine_info(self.handle, 13), "publish_micros": _lib().infeng_engine_info(self.handle, 14)}
 
   def close(self):
     if getattr(self, "handle", 0): _lib().infeng_engine_release(self.handle)
