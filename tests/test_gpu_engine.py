@@ -129,6 +129,27 @@ def test_prefix_restore_reproduces_the_token(model):
     second.close()
 
 
+def test_evicted_checkpoints_hand_their_state_records_on(model):
+  """Eleven different 520-token prompts publish eleven checkpoints into a cache of eight: the evicted ones' state
+  records are reused by later sequences, and neither a restored nor a recomputed prefix changes the token."""
+  tokens = []
+  for seed in range(11):
+    sequence = model.sequence()
+    try:
+      tokens.append(one(sequence, prompt_tokens(100 + seed, 520)))
+    finally:
+      sequence.close()
+  for seed in (10, 0, 5):  # still cached; evicted long ago; in between
+    sequence = model.sequence()
+    try:
+      rows_before = model.step_counters()["rows"]
+      assert one(sequence, prompt_tokens(100 + seed, 520)) == tokens[seed]
+      rows = model.step_counters()["rows"] - rows_before
+      assert rows <= 16 if seed == 10 else rows >= 520, (seed, rows)
+    finally:
+      sequence.close()
+
+
 def test_mixed_batch_sampling_matches_greedy(model):
   """temperature 1 with top_k 1 is greedy (test_qwen35.py:207-230)."""
   greedy = [model.sequence() for _ in range(4)]
