@@ -39,7 +39,7 @@ def model_path():
 
 
 def ensure_model(path, layers=LAYERS, vocab=VOCAB):
-  from mtlqwen_b200 import synth
+  from mtlqwen_b200.testing import synth
   if not path.exists():
     temporary = path.with_suffix(f".{os.getpid()}.tmp")
     synth.write_gguf(temporary, layers=layers, vocab=vocab, mtp=False, seed=SEED)
@@ -96,7 +96,7 @@ def gemv_roofline(device_index, copies=24, replays=20, xsplit=None, qtype=None, 
   """The dominant kernel alone: Q4_K GEMV 12288 x 4096 with 8 activation rows (BASELINE config 1), launched over a
   ring of 24 distinct weight copies (680 MB, larger than L2) and timed with CUDA events on the launching stream."""
   from mtlqwen_b200 import device as D
-  from mtlqwen_b200 import synth
+  from mtlqwen_b200.testing import synth
   dev = D.Device(device_index)
   qtype = qtype or D.Q4_K
   if xsplit:  # asks for the fp16-MMA kernel with this activation split
@@ -151,7 +151,7 @@ def cpu_decode(path, seconds_budget, steps=None, warmup=0):
   """Times the CPU oracle decoding one sequence of the same model, one token per step, with every host core
   (OpenMP over output rows). Returns tokens/s, steps timed, seconds."""
   import oracle
-  from mtlqwen_b200 import synth
+  from mtlqwen_b200.testing import synth
   model = oracle.Model(synth.read_gguf(path), LAYERS, VOCAB, 4096)
   token = 17
   for _ in range(warmup):

@@ -73,10 +73,6 @@ void* infdev_event_create(infdev_ctx* ctx);
 void infdev_event_destroy(infdev_ctx* ctx, void* event);
 int infdev_event_record(infdev_ctx* ctx, void* event);
 float infdev_event_elapsed_ms(infdev_ctx* ctx, void* start, void* stop);
-/* Overwrites `bytes` of scratch (>= L2 size) so the next launch starts with a cold L2. */
-int infdev_flush_l2(infdev_ctx* ctx);
-/* cudaProfilerStart / cudaProfilerStop, so a profiler started with its capture off records only a chosen region. */
-int infdev_profiler_range(infdev_ctx* ctx, int on);
 /* Which quantised-linear kernel serves Q4_K matrices with n % 128 == 0 and k % 2048 == 0: 0 = always the mma.sync GEMV,
  * 1 (default) = the tcgen05 / TMEM GEMM for more than 8 activation rows (prefill, speculative rows) and the GEMV for
  * decode, 2 = tcgen05 for every row count. Environment: INFENG_UMMA. */
@@ -212,12 +208,16 @@ int infdev_sample(infdev_ctx* ctx, const float* logits, int64_t vocab, infdev_qu
  * requested-token count. meta[4] receives rows, logit rows, flags (1 sequential, 2 prefill), packed count. */
 int infdev_pack_queries(infdev_ctx* ctx, const infdev_query* in, int count, int drafting, uint32_t draftWidth, const uint64_t* statePrevious,
                         const uint64_t* stateNext, uint64_t candidateBase, uint64_t stateBytes, infdev_query* out, uint32_t* meta);
-/* The acceptance loop of Engine::schedule (engine.cpp:205-216) on the device. stops: all slots' stop tokens,
- * stopOffsets[slot..slot+1] their range. accepted[i] per query. */
+/* The acceptance loop of Engine::schedule (engine.cpp:205-216) on the device, for every query of a target pass:
+ * sampled[query.logit + s] is emitted; a stop token ends the query after it; a speculative query continues while the
+ * sampled token equals proposed[(s + 1) * 8 + query.state / query.count] and s < draftWidth. stops[slot * stopStride
+ * .. + stopCounts[slot]) are the slot's stop tokens. verdict[3 i], [3 i + 1], [3 i + 2] = accepted proposals, emitted
+ * tokens, stopped (0 / 1) of query i. */
 int infdev_verify_drafts(infdev_ctx* ctx, const infdev_query* queries, int count, const int32_t* sampled, const int32_t* proposed,
-                         uint32_t draftWidth, const int32_t* stops, const uint32_t* stopOffsets, uint32_t* accepted);
-/* Copies each speculative query's accepted candidate state row to the slot's next state (engine.cpp:217-218). */
-int infdev_commit_states(infdev_ctx* ctx, const infdev_query* queries, int count, const uint32_t* accepted, const uint64_t* stateNext,
+                         uint32_t draftWidth, const int32_t* stops, uint32_t stopStride, const uint32_t* stopCounts, uint32_t* verdict);
+/* Copies each speculative query's candidate state row number verdict[3 i] (the row after the last accepted proposal) to
+ * the slot's next state record, stateNext[slot] (engine.cpp:217-218). */
+int infdev_commit_states(infdev_ctx* ctx, const infdev_query* queries, int count, const uint32_t* verdict, const uint64_t* stateNext,
                          uint64_t candidateBase, uint64_t stateBytes);
 
 #ifdef __cplusplus

@@ -3,6 +3,7 @@
 #pragma once
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <atomic>
 #include <cstdint>
 
 namespace infdev {
@@ -40,6 +41,28 @@ cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size
   config.attrs = attribute;
   config.numAttrs = (pdl_mode() == 1 || (pdl_mode() == 2 && EARLY == 1) || (pdl_mode() == 3 && EARLY >= 1)) ? 1 : 0;
   return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
+// A kernel's opt-in to more than 48 KB of dynamic shared memory is a property of the (kernel, device) pair, and one
+// process may hold contexts on several GPUs: the attribute is set once per device, for the device that is current.
+constexpr int kMaxDevices = 64;
+struct PerDeviceOnce {
+  std::atomic<unsigned char> done[kMaxDevices] = {};
+};
+
+template <class Kernel> cudaError_t configure_shared_memory(Kernel kernel, size_t bytes, PerDeviceOnce& once) {
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess)
+    return e;
+  if (device < 0 || device >= kMaxDevices)
+    return cudaErrorInvalidDevice;
+  if (once.done[device].load(std::memory_order_acquire))
+    return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes));
+  if (e == cudaSuccess)
+    once.done[device].store(1, std::memory_order_release);
+  return e;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

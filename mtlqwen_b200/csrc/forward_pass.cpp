@@ -336,6 +336,16 @@ PassShape forward(Engine& engine, Batch& batch, bool drafting, bool launch) {
                                        engine.kv->blockTable(), int32_t(engine.kv->tableStride()), int32_t(engine.blockTokens), nullptr,
                                        engine.kv->key(engine.kvLayers).as<void>(), engine.kv->value(engine.kvLayers).as<void>()));
   }
+  if (!drafting && shape.logits) {
+    // Acceptance of the proposals and the copy of the accepted candidate states (the MTP seeds of the candidate rows
+    // included, hence after the tail above), without a round trip to the host (engine.cpp:205-218).
+    ops.check(infdev_verify_drafts(ctx, deviceQueries, int(shape.queries), engine.outputTokens.as<int32_t>(), engine.draftTokens.as<int32_t>(),
+                                   engine.draftWidth, engine.stopTokens.as<int32_t>(), maxStopTokens, engine.stopCounts.as<uint32_t>(),
+                                   engine.verdicts.as<uint32_t>()));
+    if (batch.candidateRows)
+      ops.check(infdev_commit_states(ctx, deviceQueries, int(shape.queries), engine.verdicts.as<uint32_t>(), addresses + maxBatchSequences,
+                                     engine.candidateStates.address(), engine.stateBytes));
+  }
   return shape;
 }
 

@@ -476,13 +476,9 @@ cudaError_t delta_rule_launch(const float* q, const float* k, const float* v, co
   if (queryCount <= 0)
     return cudaSuccess;
   if (chunkedFrom) {
-    static bool configured = false;
-    if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(delta_rule_chunked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(ChunkShared)));
-      if (e != cudaSuccess)
-        return e;
-      configured = true;
-    }
+    static PerDeviceOnce configured;
+    if (cudaError_t e = configure_shared_memory(delta_rule_chunked_kernel, sizeof(ChunkShared), configured))
+      return e;
     launch_kernel(delta_rule_chunked_kernel, dim3(kValueHeads, unsigned(queryCount)), 256, sizeof(ChunkShared), stream, q, k, v, g, beta, z, normWeight,
                   queries, stateOffset, out, chunkedFrom);
   }

@@ -306,8 +306,7 @@ template <class Q, int NMAT, int XSPLIT> __global__ void __launch_bounds__(kThre
     // 64-value span of all 8 rows at a time: lane (row = lane/4, jj = lane%4) loads four float4 at
     // 16*e + 4*jj, so each row contributes whole 64-byte pieces. Q4_K fragments are stored rotated by jj
     // inside their 32-entry line, which makes both these writes and the MMA-time reads conflict-free.
-    if (!(p.debug & 1))
-      for (int span = warp; span < chunkBlocks * 4; span += kConsumerWarps) {
+    for (int span = warp; span < chunkBlocks * 4; span += kConsumerWarps) {
         const int row = lane >> 2, jj = lane & 3, sb = span >> 2, tq = span & 3;
         float4 v[4];
 #pragma unroll
@@ -372,7 +371,7 @@ template <class Q, int NMAT, int XSPLIT> __global__ void __launch_bounds__(kThre
             continue;
           }
           const int count = min(kStageBlocks, chunkBlocks - grp * kStageBlocks);
-          if (warp < count && !(p.debug & 2)) {
+          if (warp < count) {
             const uint8_t* base = ring + size_t(slot) * Q::kStageBytes + warp * Q::kBlockBytes;
             const int sb = grp * kStageBlocks + warp;
             if (Q::kMinTerm) {
@@ -429,14 +428,10 @@ template <class Q, int NMAT, int XSPLIT> __global__ void __launch_bounds__(kThre
 }
 
 template <class Q, int NMAT, int XSPLIT> cudaError_t launch(const GemvParams& p, int sms, cudaStream_t stream) {
-  static bool configured = false;
+  static PerDeviceOnce configured;
   constexpr size_t bytes = smem_bytes<Q, NMAT, XSPLIT>();
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<Q, NMAT, XSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes));
-    if (e != cudaSuccess)
-      return e;
-    configured = true;
-  }
+  if (cudaError_t e = configure_shared_memory(gemv_kernel<Q, NMAT, XSPLIT>, bytes, configured))
+    return e;
   const int grid = p.tiles < sms ? p.tiles : sms;
   launch_kernel<1>(gemv_kernel<Q, NMAT, XSPLIT>, grid, kThreads, bytes, stream, p);
   return cudaGetLastError();

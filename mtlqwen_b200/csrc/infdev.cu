@@ -10,15 +10,14 @@
 #include <mutex>
 #include <string>
 #include <thread>
-#include <cuda_profiler_api.h>
 #include <unordered_map>
 #include <vector>
 #include "kernels.h"
 #include "ops.h"
 
 struct infdev_ctx {
-  int device = 0, sms = 0, xsplit = 2, debug = 0, umma = 1;
-  int skip = 0;  // probe (INFENG_SKIP): bit mask of kernel classes whose launches are dropped, to time a pass without them  // umma: 0 never, 1 for more than 8 rows, 2 always
+  int device = 0, sms = 0, xsplit = 2;
+  int umma = 1;  // tcgen05 GEMM for Q4_K: 0 never, 1 for more than 8 rows, 2 always
   int integerDecode = 1;     // Q4_K decode GEMV: 1 integer-MMA kernel over an activation image, 0 fp16-MMA kernel
   uint8_t* image = nullptr;  // activation image for the integer decode kernel (K up to 16384)
   int* imageCounters = nullptr;        // arrival counters of the kernels that write images block by block (zero between launches)
@@ -32,8 +31,6 @@ struct infdev_ctx {
   cudaEvent_t done = nullptr;
   int* status = nullptr;      // device status word written by kernels that abort a bounded wait
   int* statusHost = nullptr;  // pinned mirror
-  void* flush = nullptr;
-  size_t flushBytes = 0;
   std::mutex mutex;
   std::unordered_map<void*, int> allocations;  // pointer -> hostVisible
   std::unordered_map<std::string, CUtensorMap> tensorMaps;  // weight matrix -> tiled-TMA descriptor
@@ -167,12 +164,8 @@ infdev_ctx* infdev_create(int device, char* error) {
   ctx->sms = prop.multiProcessorCount;
   if (const char* env = std::getenv("INFENG_XSPLIT"))
     ctx->xsplit = std::atoi(env) == 1 ? 1 : 2;
-  if (const char* env = std::getenv("INFENG_GEMV_DEBUG"))
-    ctx->debug = std::atoi(env);
   if (const char* env = std::getenv("INFENG_UMMA"))
     ctx->umma = std::atoi(env);
-  if (const char* env = std::getenv("INFENG_SKIP"))
-    ctx->skip = std::atoi(env);
   if (const char* env = std::getenv("INFENG_INTEGER_DECODE"))
     ctx->integerDecode = std::atoi(env) != 0;
   if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess ||
@@ -200,8 +193,6 @@ void infdev_destroy(infdev_ctx* ctx) {
   cudaStreamSynchronize(ctx->stream);
   for (auto& entry : ctx->allocations)
     entry.second ? cudaFreeHost(entry.first) : cudaFree(entry.first);
-  if (ctx->flush)
-    cudaFree(ctx->flush);
   cudaFree(ctx->status);
   cudaFree(ctx->image);
   cudaFree(ctx->imageCounters);
@@ -340,21 +331,6 @@ float infdev_event_elapsed_ms(infdev_ctx* ctx, void* start, void* stop) {
   return ms;
 }
 
-int infdev_flush_l2(infdev_ctx* ctx) {
-  Bind bind(ctx);
-  if (!ctx->flush) {
-    ctx->flushBytes = size_t(256) << 20;
-    if (int r = check(ctx, cudaMalloc(&ctx->flush, ctx->flushBytes), "infdev_flush_l2"))
-      return r;
-  }
-  return check(ctx, cudaMemsetAsync(ctx->flush, 1, ctx->flushBytes, ctx->stream), "infdev_flush_l2");
-}
-
-int infdev_profiler_range(infdev_ctx* ctx, int on) {  // ctx may be null: the switch is process-wide
-  const cudaError_t e = on ? cudaProfilerStart() : cudaProfilerStop();
-  return ctx ? check(ctx, e, "infdev_profiler_range") : (e == cudaSuccess ? INFDEV_OK : INFDEV_E_CUDA);
-}
-
 int infdev_set_umma(infdev_ctx* ctx, int enabled) {
   ctx->umma = enabled < 0 ? 0 : enabled > 2 ? 2 : enabled;
   return INFDEV_OK;
@@ -490,7 +466,6 @@ static int linear_run(infdev_ctx* ctx, int type, bool pair, int count, const voi
     u.acts = static_cast<const uint8_t*>(ctx->ummaActs);
     u.actSums = ctx->ummaSums;
     u.status = ctx->status;
-    u.debug = ctx->debug;
     const int64_t slice = m <= 8 ? 8 : 128;  // exact decode mode up to 8 rows, fp16-weight GEMM mode up to 128 rows per launch
     for (int64_t row = 0; row < m; row += slice) {
       u.m = int(m - row < slice ? m - row : slice);
@@ -526,7 +501,6 @@ static int linear_run(infdev_ctx* ctx, int type, bool pair, int count, const voi
   p.ldx = int(k);
   p.k = int(k);
   p.status = ctx->status;
-  p.debug = ctx->debug;
   // More than 8 activation rows: 8-row slices re-use the weights out of L2.
   for (int64_t row = 0; row < m; row += 8) {
     p.x = x + row * k;
@@ -563,11 +537,8 @@ static int linear_common(infdev_ctx* ctx, int type, bool pair, int count, const 
   uint8_t* captured = take_capture(ctx);
   if (captured && (count != 1 || n[0] % 256))
     return fail(ctx, INFDEV_E_ARGUMENT, "linear: an image of the result needs a single matrix with n a multiple of 256");
-  if (!(ctx->skip & (type == INFDEV_Q6_K ? 32 : 128)))
-    if (int r = linear_run(ctx, type, pair, count, w, w2, n, k, x, m, y, residual, supplied))
-      return r;
-  if (ctx->skip & 64)
-    return INFDEV_OK;
+  if (int r = linear_run(ctx, type, pair, count, w, w2, n, k, x, m, y, residual, supplied))
+    return r;
   // A GEMV tile is 16 outputs wide, a 256-value image block spans 16 tiles on different SMs: the image of the result
   // takes a launch of its own.
   return captured ? quantize_rows(ctx, y[0], m, n[0], captured) : INFDEV_OK;
@@ -610,8 +581,6 @@ int infdev_rms_norm(infdev_ctx* ctx, const float* x, const float* w, int64_t row
     return fail(ctx, INFDEV_E_ARGUMENT, "rms_norm: dim must be a multiple of 4 and buffers 16-byte aligned");
   ctx->launches += 1;
   uint8_t* image = take_capture(ctx);
-  if (ctx->skip & 1)
-    return INFDEV_OK;
   if (image && dim % 256)
     return fail(ctx, INFDEV_E_ARGUMENT, "rms_norm: an image needs dim to be a multiple of 256");
   return check(ctx, infdev::rms_norm_launch(x, w, nullptr, rows, dim, y, image, ctx->stream), "rms_norm");
@@ -630,10 +599,6 @@ int infdev_gdn_prepare(infdev_ctx* ctx, const float* x, const float* mixed, cons
                        const float* ssmDt, const float* convWeight, const infdev_query* queries, int queryCount, int64_t rows,
                        uint64_t stateOffset, uint64_t stateBytes, float* q, float* k, float* v, float* beta, float* g) {
   Bind bind(ctx);
-  if (ctx->skip & 2) {
-    take_capture(ctx);
-    return INFDEV_OK;
-  }
   (void)queryCount;
   if (stateOffset % 16 || stateBytes % 16)
     return fail(ctx, INFDEV_E_ARGUMENT, "gdn_prepare: state offsets must be multiples of 16 bytes");
@@ -648,10 +613,6 @@ int infdev_gdn_decode(infdev_ctx* ctx, const float* x, const float* mixed, const
                       const float* ssmDt, const float* convWeight, const float* z, const float* normWeight, const infdev_query* queries,
                       int queryCount, uint64_t convStateOffset, uint64_t stateOffset, uint64_t stateBytes, float* out) {
   Bind bind(ctx);
-  if (ctx->skip & 6) {
-    take_capture(ctx);
-    return INFDEV_OK;
-  }
   if (convStateOffset % 16 || stateOffset % 16 || stateBytes % 16)
     return fail(ctx, INFDEV_E_ARGUMENT, "gdn_decode: state offsets must be multiples of 16 bytes");
   ctx->launches += 1;
@@ -665,10 +626,6 @@ static int delta_rule_common(infdev_ctx* ctx, const float* q, const float* k, co
                              const float* normWeight, const infdev_query* queries, int queryCount, uint64_t stateOffset, uint64_t stateBytes,
                              float* out, uint32_t chunkedFrom) {
   Bind bind(ctx);
-  if (ctx->skip & 4) {
-    take_capture(ctx);
-    return INFDEV_OK;
-  }
   if (stateOffset % 16 || stateBytes % 16)
     return fail(ctx, INFDEV_E_ARGUMENT, "delta_rule: state offsets must be multiples of 16 bytes");
   if (chunkedFrom && ctx->captureImage) {
@@ -712,10 +669,6 @@ int infdev_attention_prepare(infdev_ctx* ctx, const float* qg, const float* k, c
                              const float* rope, const infdev_query* queries, int queryCount, int64_t rows, const int32_t* table,
                              int32_t tableStride, int32_t blockTokens, float* q, void* cacheK, void* cacheV) {
   Bind bind(ctx);
-  if (ctx->skip & 16) {
-    take_capture(ctx);
-    return INFDEV_OK;
-  }
   if (rows > 0 && queryCount < 1)
     return fail(ctx, INFDEV_E_ARGUMENT, "attention: rows without queries");
   if (blockTokens <= 0 || blockTokens % 16)
@@ -733,10 +686,6 @@ int infdev_attention(infdev_ctx* ctx, const float* q, const float* qg, const voi
                      int queryCount, int64_t rows, const int32_t* table, int32_t tableStride, int32_t blockTokens, uint32_t maxSplits,
                      float* partials, float* out) {
   Bind bind(ctx);
-  if (ctx->skip & 8) {
-    take_capture(ctx);
-    return INFDEV_OK;
-  }
   if (rows > 0 && queryCount < 1)
     return fail(ctx, INFDEV_E_ARGUMENT, "attention: rows without queries");
   if (blockTokens <= 0 || blockTokens % 16 || maxSplits < 1 || maxSplits > 64)
@@ -792,20 +741,22 @@ int infdev_pack_queries(infdev_ctx* ctx, const infdev_query* in, int count, int 
 }
 
 int infdev_verify_drafts(infdev_ctx* ctx, const infdev_query* queries, int count, const int32_t* sampled, const int32_t* proposed,
-                         uint32_t draftWidth, const int32_t* stops, const uint32_t* stopOffsets, uint32_t* accepted) {
+                         uint32_t draftWidth, const int32_t* stops, uint32_t stopStride, const uint32_t* stopCounts, uint32_t* verdict) {
   Bind bind(ctx);
   if (count > 32)
     return fail(ctx, INFDEV_E_ARGUMENT, "verify_drafts: at most 32 queries");
   ctx->launches += 1;
-  return check(ctx, infdev::verify_drafts_launch(queries, count, sampled, proposed, draftWidth, stops, stopOffsets, accepted, ctx->stream),
+  return check(ctx, infdev::verify_drafts_launch(queries, count, sampled, proposed, draftWidth, stops, stopStride, stopCounts, verdict, ctx->stream),
                "verify_drafts");
 }
 
-int infdev_commit_states(infdev_ctx* ctx, const infdev_query* queries, int count, const uint32_t* accepted, const uint64_t* stateNext,
+int infdev_commit_states(infdev_ctx* ctx, const infdev_query* queries, int count, const uint32_t* verdict, const uint64_t* stateNext,
                          uint64_t candidateBase, uint64_t stateBytes) {
   Bind bind(ctx);
+  if (stateBytes % 16 || candidateBase % 16)
+    return fail(ctx, INFDEV_E_ARGUMENT, "commit_states: state records must be 16-byte aligned");
   ctx->launches += 1;
-  return check(ctx, infdev::commit_states_launch(queries, count, accepted, stateNext, candidateBase, stateBytes, ctx->stream), "commit_states");
+  return check(ctx, infdev::commit_states_launch(queries, count, verdict, stateNext, candidateBase, stateBytes, ctx->stream), "commit_states");
 }
 
 }  // extern "C"

@@ -25,7 +25,6 @@ struct GemvParams {
   const uint8_t* image;  // quantised activations (act_image.cuh) of all k/256 blocks, for the integer Q4_K kernel
   int ldx, m, k;
   int* status;
-  int debug;  // probe switches: 1 skips activation staging, 2 skips the MMA units, 4 skips the weight copies (integer kernel)
 };
 
 // Box geometry shared by the host encoder and the kernel.
@@ -52,7 +51,6 @@ struct UmmaParams {
   const uint8_t* acts;   // prepared activations: k/256 blocks of kUmmaActBytesPerBlock
   const float* actSums;  // [k/256][8 sub-blocks][8 rows]
   int* status;
-  int debug;  // probe switches: 1 no MMA issue, 2 no dequant arithmetic, 4 no prepare kernel
 };
 
 cudaError_t umma_launch(bool pair, const UmmaParams& p, const float* x, int ldx, int sms, cudaStream_t stream);

@@ -41,8 +41,8 @@ cudaError_t pack_queries_launch(const infdev_query* in, int count, int drafting,
                                 const uint64_t* stateNext, uint64_t candidateBase, uint64_t stateBytes, infdev_query* out, uint32_t* meta,
                                 cudaStream_t stream);
 cudaError_t verify_drafts_launch(const infdev_query* queries, int count, const int32_t* sampled, const int32_t* proposed, uint32_t draftWidth,
-                                 const int32_t* stops, const uint32_t* stopOffsets, uint32_t* accepted, cudaStream_t stream);
-cudaError_t commit_states_launch(const infdev_query* queries, int count, const uint32_t* accepted, const uint64_t* stateNext,
+                                 const int32_t* stops, uint32_t stopStride, const uint32_t* stopCounts, uint32_t* verdict, cudaStream_t stream);
+cudaError_t commit_states_launch(const infdev_query* queries, int count, const uint32_t* verdict, const uint64_t* stateNext,
                                  uint64_t candidateBase, uint64_t stateBytes, cudaStream_t stream);
 
 }  // namespace infdev

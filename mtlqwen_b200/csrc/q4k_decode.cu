@@ -203,13 +203,9 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
               }
               // One tiled copy moves the whole slab; bytes past the end of a row are zero-filled and still counted, so
               // the transaction size is always the full box.
-              if (p.debug & 4) {
-                mbar_arrive(&ctl.full[slot]);  // probe: the consumers run on whatever the ring holds
-              } else {
-                mbar_arrive_expect_tx(&ctl.full[slot], uint32_t(kStageBytes));
-                tma_load_2d(ring + size_t(slot) * kStageBytes, &p.map[segment][mat], (chunk * (kChunkBlocks / kStageBlocks) + grp) * (kStageBlocks * kBlockBytes / 8),
-                            row0, &ctl.full[slot]);
-              }
+              mbar_arrive_expect_tx(&ctl.full[slot], uint32_t(kStageBytes));
+              tma_load_2d(ring + size_t(slot) * kStageBytes, &p.map[segment][mat], (chunk * (kChunkBlocks / kStageBlocks) + grp) * (kStageBlocks * kBlockBytes / 8),
+                          row0, &ctl.full[slot]);
             }
           }
         }
@@ -294,7 +290,7 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) q4k_decode_ke
     // only the last chunk of a row can be a single slab), with one slab every stage is slab 0: either way this warp
     // meets the same super-block in every tile of the chunk.
     const int myBlock = (groups == 2 ? half * kStageBlocks : 0) + unit;
-    const bool live = myBlock < chunkBlocks && !(p.debug & 2);
+    const bool live = myBlock < chunkBlocks;
     Fragments fragments;
     if (live)
       fragments = load_fragments(p.image + size_t(chunk * kChunkBlocks + myBlock) * kImageBlockBytes, lane);
@@ -369,14 +365,10 @@ __global__ void __launch_bounds__(256) activation_image_kernel(const float* x, i
 }
 
 template <int NMAT> cudaError_t launch(const GemvParams& p, int sms, cudaStream_t stream) {
-  static bool configured = false;
+  static PerDeviceOnce configured;
   constexpr size_t bytes = smem_bytes<NMAT>();
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(q4k_decode_kernel<NMAT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes));
-    if (e != cudaSuccess)
-      return e;
-    configured = true;
-  }
+  if (cudaError_t e = configure_shared_memory(q4k_decode_kernel<NMAT>, bytes, configured))
+    return e;
   const int grid = p.tiles < sms ? p.tiles : sms;
   launch_kernel<1>(q4k_decode_kernel<NMAT>, grid, kThreads, bytes, stream, p);
   return cudaGetLastError();

@@ -22,6 +22,7 @@ inline constexpr uint32_t hiddenSize = 4096, intermediateSize = 12288, fullAtten
 inline constexpr uint32_t maxDraftTokens = 7, maxBatchSequences = 8, maxBatchTokens = 128;
 inline constexpr uint32_t maxLogitRows = maxBatchSequences * (maxDraftTokens + 1);
 inline constexpr uint32_t checkpointTokens = 512, maxCheckpoints = 8, maxAttentionSplits = 32;
+inline constexpr uint32_t maxStopTokens = 64;  // per sequence: the stop lists live in a device-visible table
 inline constexpr uint32_t unbound = UINT32_MAX;
 inline constexpr uint64_t seedBytes = hiddenSize * sizeof(float);  // MTP seed (last target hidden) at the end of a state record
 
@@ -79,7 +80,13 @@ struct Engine {
   Scratch workspace;
   Tensor requestData, queryInput, queryData, passMeta, stateAddresses;
   Tensor draftTokens, outputTokens;
-  uint64_t seeds[maxBatchSequences]{};
+  // Read by the device-side acceptance step: every slot's stop tokens [slot][maxStopTokens] with their counts, and the
+  // verdicts it writes per query of a pass (accepted proposals, emitted tokens, stopped).
+  Tensor stopTokens, stopCounts, verdicts;
+  // Philox keys. A slot's key is renewed for every sequence that takes the slot, from the base seed and the number of
+  // sequences created so far, so a repeated request draws new variates (the reference keeps advancing rng[slot] across
+  // sequences, engine.cpp:210-211) while a run with a fixed base seed stays reproducible.
+  uint64_t seeds[maxBatchSequences]{}, baseSeed = 0, sequencesCreated = 0;
   std::vector<PhysicalBlock> blocks;
   std::list<HybridCheckpoint> checkpointCache;
   std::array<Sequence*, maxBatchSequences> sequences{};
@@ -101,8 +108,9 @@ struct Engine {
   void* passEvents[2] = {nullptr, nullptr};  // CUDA events bracketing each pass on the stream
   // Pure-decode passes (every query one row, nothing speculative) have a fixed launch sequence for a given number of
   // live sequences; from its second occurrence such a pass is captured once into a CUDA graph and then replayed.
-  void* decodeGraphs[maxBatchSequences + 1] = {};
-  uint32_t decodeSeen[maxBatchSequences + 1] = {};
+  // The same holds for passes in which every query is a speculative decode of draftWidth + 1 rows (second index 1).
+  void* decodeGraphs[maxBatchSequences + 1][2] = {};
+  uint32_t decodeSeen[maxBatchSequences + 1][2] = {};
   bool useGraphs = true;
 
   Engine(const std::filesystem::path& weights, uint32_t maxContext, const std::filesystem::path& draftWeights);
@@ -131,6 +139,9 @@ struct Sequence {
   float temperature, topP;
   int32_t topK;
   bool speculative, active = false, busy = false;
+  // The latest speculative step of this sequence: position of its anchor token and the drafter's proposals.
+  uint32_t draftAnchor = 0;
+  int32_t draftProposals[maxDraftTokens] = {};
   Sequence(Engine&, const int32_t* stops, uint32_t stopCount, float temperature, float topP, int32_t topK, bool speculative);
   ~Sequence();
 };

@@ -316,42 +316,46 @@ __global__ void pack_queries_kernel(const infdev_query* in, int count, int draft
   meta[3] = packed;
 }
 
-// Accepts draft proposals on the device (engine.cpp:205-216): for query i, accepted[i] = number of leading
-// sampled tokens that equal the next proposal, stopping at a stop token or at draftWidth.
+// The acceptance loop of Engine::schedule (engine.cpp:205-216) on the device, one thread per query. For query i it
+// walks the sampled rows exactly as the host loop does: a sampled token is emitted; a stop token ends the walk after
+// this token; a speculative query goes on to the next row only while the sampled token equals the drafter's proposal
+// for that row and fewer than draftWidth proposals have been accepted. verdict[3 i .. 3 i + 2] = accepted proposals,
+// emitted tokens, stopped (0 / 1). stops: [slot][stopStride] token ids, stopCounts[slot] of them valid.
 __global__ void verify_drafts_kernel(const infdev_query* queries, int count, const int32_t* sampled, const int32_t* proposed, uint32_t draftWidth,
-                                     const int32_t* stops, const uint32_t* stopOffsets, uint32_t* accepted) {
+                                     const int32_t* stops, uint32_t stopStride, const uint32_t* stopCounts, uint32_t* verdict) {
   pdl_launch_dependents();
   pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= count)
     return;
   const infdev_query& query = queries[i];
-  uint32_t ok = 0;
-  if (query.state != kUnbound) {
-    const uint32_t column = query.state / query.count;
-    for (uint32_t s = 0; s < query.samples; ++s) {
-      const int32_t token = sampled[query.logit + s];
-      bool stopped = false;
-      for (uint32_t k = stopOffsets[query.slot]; k < stopOffsets[query.slot + 1]; ++k)
-        stopped |= stops[k] == token;
-      if (stopped || s == draftWidth || token != proposed[(s + 1) * 8 + column])
-        break;
-      ++ok;
-    }
+  const bool speculative = query.state != kUnbound;
+  const uint32_t column = speculative ? query.state / query.count : 0;
+  uint32_t accepted = 0, emitted = 0, stopped = 0;
+  for (uint32_t s = 0; s < query.samples && !stopped; ++s) {
+    const int32_t token = sampled[query.logit + s];
+    ++emitted;
+    for (uint32_t k = 0; k < stopCounts[query.slot]; ++k)
+      stopped |= stops[size_t(query.slot) * stopStride + k] == token ? 1u : 0u;
+    if (!speculative || s == draftWidth || token != proposed[(s + 1) * 8 + column])
+      break;
+    ++accepted;
   }
-  accepted[i] = ok;
+  verdict[3 * i] = accepted;
+  verdict[3 * i + 1] = emitted;
+  verdict[3 * i + 2] = stopped;
 }
 
 // Copies the accepted candidate state row of each speculative query to the slot's next state buffer
-// (engine.cpp:217-218), driven by the device-side accepted counts. grid (chunks, queries).
-__global__ void __launch_bounds__(256) commit_states_kernel(const infdev_query* queries, const uint32_t* accepted, const uint64_t* stateNext,
+// (engine.cpp:217-218), driven by the verdicts of verify_drafts_kernel. grid (chunks, queries).
+__global__ void __launch_bounds__(256) commit_states_kernel(const infdev_query* queries, const uint32_t* verdict, const uint64_t* stateNext,
                                                             uint64_t candidateBase, uint64_t stateBytes) {
   pdl_launch_dependents();
   pdl_wait();
   const infdev_query& query = queries[blockIdx.y];
   if (query.state == kUnbound)
     return;
-  const uint4* src = reinterpret_cast<const uint4*>(candidateBase + uint64_t(query.state + accepted[blockIdx.y]) * stateBytes);
+  const uint4* src = reinterpret_cast<const uint4*>(candidateBase + uint64_t(query.state + verdict[3 * blockIdx.y]) * stateBytes);
   uint4* dst = reinterpret_cast<uint4*>(stateNext[query.slot]);
   const size_t total = stateBytes / 16;
   for (size_t at = size_t(blockIdx.x) * blockDim.x + threadIdx.x; at < total; at += size_t(gridDim.x) * blockDim.x)
@@ -376,18 +380,18 @@ cudaError_t pack_queries_launch(const infdev_query* in, int count, int drafting,
 }
 
 cudaError_t verify_drafts_launch(const infdev_query* queries, int count, const int32_t* sampled, const int32_t* proposed, uint32_t draftWidth,
-                                 const int32_t* stops, const uint32_t* stopOffsets, uint32_t* accepted, cudaStream_t stream) {
+                                 const int32_t* stops, uint32_t stopStride, const uint32_t* stopCounts, uint32_t* verdict, cudaStream_t stream) {
   if (count <= 0)
     return cudaSuccess;
-  launch_kernel(verify_drafts_kernel, 1, 32, 0, stream, queries, count, sampled, proposed, draftWidth, stops, stopOffsets, accepted);
+  launch_kernel(verify_drafts_kernel, 1, 32, 0, stream, queries, count, sampled, proposed, draftWidth, stops, stopStride, stopCounts, verdict);
   return cudaGetLastError();
 }
 
-cudaError_t commit_states_launch(const infdev_query* queries, int count, const uint32_t* accepted, const uint64_t* stateNext,
+cudaError_t commit_states_launch(const infdev_query* queries, int count, const uint32_t* verdict, const uint64_t* stateNext,
                                  uint64_t candidateBase, uint64_t stateBytes, cudaStream_t stream) {
   if (count <= 0)
     return cudaSuccess;
-  launch_kernel(commit_states_kernel, dim3(64, unsigned(count)), 256, 0, stream, queries, accepted, stateNext, candidateBase, stateBytes);
+  launch_kernel(commit_states_kernel, dim3(64, unsigned(count)), 256, 0, stream, queries, verdict, stateNext, candidateBase, stateBytes);
   return cudaGetLastError();
 }
 

@@ -28,6 +28,14 @@ uint32_t environment(const char* name, uint32_t fallback) {
   return text && *text ? uint32_t(std::strtoul(text, nullptr, 10)) : fallback;
 }
 
+// splitmix64: spreads (base seed, creation index) over the 64-bit Philox key space.
+uint64_t mixSeed(uint64_t value) {
+  value += 0x9e3779b97f4a7c15ull;
+  value = (value ^ (value >> 30)) * 0xbf58476d1ce4e5b9ull;
+  value = (value ^ (value >> 27)) * 0x94d049bb133111ebull;
+  return value ^ (value >> 31);
+}
+
 int deviceIndex() {
   if (const char* text = std::getenv("INFENG_DEVICE"))
     return std::atoi(text);
@@ -161,13 +169,15 @@ Engine::Engine(const std::filesystem::path& path, uint32_t context, const std::f
   stateAddresses = device.empty(2 * maxBatchSequences * sizeof(uint64_t), true);
   queryData = device.empty(2 * maxBatchSequences * sizeof(infdev_query));
   passMeta = device.empty(8 * sizeof(uint32_t));
+  stopTokens = device.empty(maxBatchSequences * maxStopTokens * sizeof(int32_t), true);
+  stopCounts = device.empty(maxBatchSequences * sizeof(uint32_t), true);
+  verdicts = device.empty(3 * maxBatchSequences * sizeof(uint32_t), true);
   for (auto& states : statePool)
     states = {device.empty(stateBytes), device.empty(stateBytes)};
-  uint64_t seed = environment("INFENG_SEED", 0);
-  if (!std::getenv("INFENG_SEED"))
-    seed = uint64_t(std::chrono::high_resolution_clock::now().time_since_epoch().count());
-  for (uint32_t i = 0; i < maxBatchSequences; ++i)
-    seeds[i] = ++seed;
+  if (const char* text = std::getenv("INFENG_SEED"))
+    baseSeed = std::strtoull(text, nullptr, 10);
+  else
+    baseSeed = uint64_t(std::chrono::high_resolution_clock::now().time_since_epoch().count());
   kv = std::make_unique<PagedKV>(device, maxBatchSequences, perSlot, uint32_t(blocks.size()), kvLayers + (drafter == Drafter::mtp ? 1 : 0), blockTokens);
   device.check(device.commit());
   passEvents[0] = infdev_event_create(device.ctx);
@@ -183,8 +193,9 @@ Engine::~Engine() {
   condition.notify_all();
   if (worker.joinable())
     worker.join();
-  for (void* graph : decodeGraphs)
-    infdev_graph_destroy(device.ctx, graph);
+  for (auto& graphs : decodeGraphs)
+    for (void* graph : graphs)
+      infdev_graph_destroy(device.ctx, graph);
   infdev_event_destroy(device.ctx, passEvents[0]);
   infdev_event_destroy(device.ctx, passEvents[1]);
 }
@@ -193,11 +204,17 @@ Sequence::Sequence(Engine& owner, const int32_t* stopTokens, uint32_t stopCount,
                    bool useSpeculation)
     : engine(owner), temperature(samplingTemperature), topP(samplingTopP), topK(samplingTopK), speculative(useSpeculation) {
   std::lock_guard<std::mutex> lock(engine.mutex);
+  if (stopCount > maxStopTokens)
+    throw std::runtime_error("a sequence takes at most " + std::to_string(maxStopTokens) + " stop tokens");
   stops.assign(stopTokens, stopTokens + stopCount);
   slot = uint32_t(std::find(engine.sequences.begin(), engine.sequences.end(), nullptr) - engine.sequences.begin());
   if (slot == maxBatchSequences)
     throw std::runtime_error("maximum live sequence count reached");
   request = engine.requestData.contents<int32_t>() + uint64_t(slot) * (engine.maxContext + 1);
+  // No pass in flight reads this slot's rows of the tables: the previous owner left only after its last pass.
+  std::copy_n(stopTokens, stopCount, engine.stopTokens.contents<int32_t>() + uint64_t(slot) * maxStopTokens);
+  engine.stopCounts.contents<uint32_t>()[slot] = stopCount;
+  engine.seeds[slot] = mixSeed(engine.baseSeed + engine.sequencesCreated++);
   engine.sequences[slot] = this;
   ++engine.owners;
 }
@@ -289,23 +306,29 @@ void Engine::schedule() {
     };
     if (success) {
       try {
-        if (stateBytes * batch.candidateRows > candidateStates.bytes)
-          candidateStates = device.empty(stateBytes * batch.candidateRows);
+        // Candidate rows: sized once for the largest speculative pass, because captured graphs hold its address.
+        if (batch.candidateRows && !candidateStates)
+          candidateStates = device.empty(stateBytes * maxBatchSequences * (draftWidth + 1));
         const auto started = std::chrono::steady_clock::now();
         infdev_event_record(device.ctx, passEvents[0]);
-        bool pureDecode = useGraphs && !batch.candidateRows;
-        for (uint32_t i = 0; i < batch.size && pureDecode; ++i)
-          pureDecode = batch.queries[i].count == 1;
-        if (pureDecode && decodeGraphs[batch.size]) {
+        // Uniform passes have a fixed launch sequence: every query one decode row, or every query a speculative decode.
+        const uint32_t kind = batch.candidateRows ? 1 : 0, rowsEach = kind ? draftWidth + 1 : 1;
+        bool uniform = useGraphs && batch.candidateRows == kind * batch.size * rowsEach;
+        for (uint32_t i = 0; i < batch.size && uniform; ++i)
+          uniform = batch.queries[i].count == rowsEach;
+        void*& graph = decodeGraphs[batch.size][kind];
+        if (uniform && graph) {
           shape = forward(*this, batch, false, false);  // host bookkeeping only
-          device.check(infdev_graph_launch(device.ctx, decodeGraphs[batch.size]));
-        } else if (pureDecode && decodeSeen[batch.size]++ >= 1) {
+          device.check(infdev_graph_launch(device.ctx, graph));
+        } else if (uniform && decodeSeen[batch.size][kind]++ >= 1) {
           device.check(infdev_graph_begin(device.ctx));
+          if (kind)
+            forward(*this, batch, true);
           shape = forward(*this, batch);
-          decodeGraphs[batch.size] = infdev_graph_end(device.ctx);
-          if (!decodeGraphs[batch.size])
+          graph = infdev_graph_end(device.ctx);
+          if (!graph)
             throw std::runtime_error(infdev_error(device.ctx));
-          device.check(infdev_graph_launch(device.ctx, decodeGraphs[batch.size]));
+          device.check(infdev_graph_launch(device.ctx, graph));
         } else {
           if (batch.candidateRows)
             forward(*this, batch, true);
@@ -326,8 +349,11 @@ void Engine::schedule() {
     stamp = std::chrono::steady_clock::now();
     lock.lock();
     lap(lockMicros);
+    // The device has already walked the sampled rows of every query (infdev_verify_drafts, the loop of engine.cpp:205-216)
+    // and copied the accepted candidate states (infdev_commit_states, engine.cpp:217-218); what is left for the host is
+    // to hand the emitted tokens over and to advance the bookkeeping.
     const int32_t *sampled = outputTokens.contents<int32_t>(), *proposed = draftTokens.contents<int32_t>();
-    bool copied = false;
+    const uint32_t* verdict = verdicts.contents<uint32_t>();
     for (uint32_t i = 0; i < batch.size; ++i) {
       const infdev_query& query = success ? batch.finished[i] : batch.queries[i];
       Sequence& sequence = *sequences[query.slot];
@@ -337,19 +363,19 @@ void Engine::schedule() {
       if (!sequence.active)
         continue;
       const bool speculative = query.state != unbound;
-      uint32_t accepted = 0;
+      uint32_t accepted = 0, emitted = 0;
       bool stopped = false;
-      for (uint32_t s = 0; s < query.samples && !stopped; ++s) {
-        const int32_t token = sampled[query.logit + s];
-        sequence.request[sequence.requested++] = token;
-        stopped = std::find(sequence.stops.begin(), sequence.stops.end(), token) != sequence.stops.end();
-        if (!speculative || s == draftWidth || token != proposed[(s + 1) * maxBatchSequences + query.state / query.count])
-          break;
-        ++accepted;
+      if (query.samples) {
+        accepted = std::min(verdict[3 * i], draftWidth);
+        emitted = std::min(verdict[3 * i + 1], query.samples);
+        stopped = verdict[3 * i + 2] != 0;
       }
+      for (uint32_t s = 0; s < emitted; ++s)
+        sequence.request[sequence.requested++] = sampled[query.logit + s];
       if (speculative) {
-        device.copy(candidateStates.view(query.state + accepted, 1, stateBytes), statePool[query.slot].second);
-        copied = true;
+        sequence.draftAnchor = query.position;
+        for (uint32_t s = 0; s < draftWidth; ++s)
+          sequence.draftProposals[s] = proposed[(s + 1) * maxBatchSequences + query.state / query.count];
       }
       sequence.kvValid += speculative ? 1 + accepted : query.count;
       sequence.drafted += speculative ? draftWidth : 0;
@@ -358,8 +384,6 @@ void Engine::schedule() {
       sequence.active = sequence.kvValid < maxContext && !stopped;
       publishPrefix(sequence);
     }
-    if (copied)
-      device.commit();
     lap(publishMicros);
   }
 }
@@ -432,6 +456,10 @@ int32_t infeng_sequence_append(infeng_sequence* sequence, const int32_t* tokens,
     return -3;
   if ((!count && sequence->requested == sequence->kvValid) || uint64_t(sequence->requested) + count > engine.maxContext)
     return -4;
+  // The embedding gather indexes the table with these ids; the reference trusts its tokenizer here.
+  for (uint32_t i = 0; i < count; ++i)
+    if (tokens[i] < 0 || uint32_t(tokens[i]) >= engine.vocab)
+      return -4;
   std::copy_n(tokens, count, sequence->request + sequence->requested);
   sequence->requested += count;
   sequence->error = false;
@@ -476,7 +504,11 @@ uint64_t infeng_sequence_info(infeng_sequence* sequence, uint32_t field) {
     case 0: return sequence->drafted;
     case 1: return sequence->accepted;
     case 2: return sequence->kvValid;
-    default: return 0;
+    case 3: return sequence->draftAnchor;
+    default:
+      if (field >= 4 && field < 4 + maxDraftTokens)
+        return uint64_t(uint32_t(sequence->draftProposals[field - 4]));
+      return 0;
   }
 }
 

@@ -221,10 +221,9 @@ template <int NMAT, int NACT> __global__ void __launch_bounds__(kThreads, 1) umm
               const uint32_t dColumn = tmem + kColD + buffer * 128 + (kDecode ? j * 16 : 0);
               if (kDecode) {
                 const uint32_t actBase = smem_u32(ring + size_t(slot) * kStageBytes + kSlabBytes);
-                if (!(p.debug & 1))
 #pragma unroll
-                  for (int step = 0; step < 16; ++step)
-                    umma_ts(dColumn, tmem + kColA + aBuffer * 128 + step * 8, smem_descriptor(actBase + step * (NACT * 32), 128, 256), M::kInstruction,
+                for (int step = 0; step < 16; ++step)
+                  umma_ts(dColumn, tmem + kColA + aBuffer * 128 + step * 8, smem_descriptor(actBase + step * (NACT * 32), 128, 256), M::kInstruction,
                             step != 0);
                 umma_commit(&ctl.aFree[aBuffer]);
                 umma_commit(&ctl.slotFree[slot]);
@@ -236,10 +235,9 @@ template <int NMAT, int NACT> __global__ void __launch_bounds__(kThreads, 1) umm
                     break;
                   fence_after_sync();
                   const uint32_t actBase = smem_u32(actRing + size_t(actSlot) * M::kActHalfBytes);
-                  if (!(p.debug & 1))
 #pragma unroll
-                    for (int step = 0; step < 8; ++step)
-                      umma_ts(dColumn, tmem + kColA + aBuffer * 128 + (8 * h + step) * 8, smem_descriptor(actBase + step * (NACT * 32), 128, 256),
+                  for (int step = 0; step < 8; ++step)
+                    umma_ts(dColumn, tmem + kColA + aBuffer * 128 + (8 * h + step) * 8, smem_descriptor(actBase + step * (NACT * 32), 128, 256),
                               M::kInstruction, (j | h | step) != 0);
                   umma_commit(&ctl.actFree[actSlot]);
                 }
@@ -304,9 +302,8 @@ template <int NMAT, int NACT> __global__ void __launch_bounds__(kThreads, 1) umm
               mine[1] = make_float4(minAcc[4], minAcc[5], minAcc[6], minAcc[7]);
             }
             const uint32_t aAddress = tmem + (uint32_t(quadrant * 32) << 16) + kColA + (it & 1) * 128;
-            if (!(p.debug & 2))
 #pragma unroll
-              for (int t = 0; t < 4; ++t) {
+            for (int t = 0; t < 4; ++t) {
                 // 32 quant bytes: low nibbles belong to sub-block 2t, high nibbles to sub-block 2t+1
                 const uint32_t pair = (scales[t >> 1] >> (16 * (t & 1))) & 0xffffu;
                 const uint4 q0 = *reinterpret_cast<const uint4*>(block + 16 + 32 * t), q1 = *reinterpret_cast<const uint4*>(block + 32 + 32 * t);
@@ -542,15 +539,11 @@ __global__ void __launch_bounds__(256) umma_reduce_kernel(const float* partial, 
 }
 
 template <int NMAT, int NACT> cudaError_t launch_mode(const UmmaParams& p, const float* x, int ldx, int sms, cudaStream_t stream) {
-  static bool configured = false;
+  static PerDeviceOnce configured;
   constexpr size_t bytes = smem_bytes<NACT>();
-  if (!configured) {
-    const cudaError_t e = cudaFuncSetAttribute(umma_linear_kernel<NMAT, NACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes));
-    if (e != cudaSuccess)
-      return e;
-    configured = true;
-  }
-  if (!(p.debug & 4)) {
+  if (const cudaError_t e = configure_shared_memory(umma_linear_kernel<NMAT, NACT>, bytes, configured))
+    return e;
+  {
     if (NACT == 128 && ldx % 4 == 0)
       umma_prepare_rows_kernel<<<dim3(p.k / 256, 4), 256, 0, stream>>>(x, ldx, p.m, reinterpret_cast<__half*>(const_cast<uint8_t*>(p.acts)));
     else

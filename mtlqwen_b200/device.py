@@ -52,7 +52,6 @@ def library():
     "infdev_event_destroy": (None, (vp, vp)),
     "infdev_event_record": (i32, (vp, vp)),
     "infdev_event_elapsed_ms": (ctypes.c_float, (vp, vp, vp)),
-    "infdev_flush_l2": (i32, (vp, )),
     "infdev_set_xsplit": (i32, (vp, i32)),
     "infdev_set_integer_decode": (i32, (vp, i32)),
     "infdev_image_bytes": (ctypes.c_size_t, (i64, i64)),
@@ -60,7 +59,6 @@ def library():
     "infdev_image_capture": (i32, (vp, vp)),
     "infdev_image_supply": (i32, (vp, vp)),
     "infdev_set_umma": (i32, (vp, i32)),
-    "infdev_profiler_range": (i32, (vp, i32)),
     "infdev_graph_begin": (i32, (vp, )),
     "infdev_graph_end": (vp, (vp, )),
     "infdev_graph_launch": (i32, (vp, vp)),
@@ -85,7 +83,7 @@ def library():
     "infdev_mtp_fuse": (i32, (vp, f32p, f32p, vp, i32, f32p, f32p, i64, u32, u64, u64, f32p)),
     "infdev_sample": (i32, (vp, f32p, i64, vp, i32, i64, u32, vp)),
     "infdev_pack_queries": (i32, (vp, vp, i32, i32, u32, vp, vp, u64, u64, vp, vp)),
-    "infdev_verify_drafts": (i32, (vp, vp, i32, vp, vp, u32, vp, vp, vp)),
+    "infdev_verify_drafts": (i32, (vp, vp, i32, vp, vp, u32, vp, u32, vp, vp)),
     "infdev_commit_states": (i32, (vp, vp, i32, vp, vp, u64, u64)),
   }
   for name, (restype, argtypes) in proto.items():
@@ -180,9 +178,6 @@ class Device:
   def elapsed_ms(self, start, stop):
     return float(self.lib.infdev_event_elapsed_ms(self.ctx, start, stop))
 
-  def flush_l2(self):
-    self.check(self.lib.infdev_flush_l2(self.ctx))
-
   def set_umma(self, enabled):
     self.check(self.lib.infdev_set_umma(self.ctx, int(enabled)))
 
@@ -263,3 +258,14 @@ class Device:
 
   def sample(self, logits, vocab, queries, nq, count, mode, tokens):
     self.check(self.lib.infdev_sample(self.ctx, logits.ptr, vocab, queries.ptr, nq, count, mode, tokens.ptr))
+
+  def mtp_fuse(self, embedding, hidden, queries, nq, enorm, hnorm, rows, mode, seed_offset, state_bytes, y):
+    self.check(self.lib.infdev_mtp_fuse(self.ctx, embedding.ptr, hidden.ptr, queries.ptr, nq, enorm.ptr, hnorm.ptr, rows, mode, seed_offset,
+                                        state_bytes, y.ptr))
+
+  def verify_drafts(self, queries, nq, sampled, proposed, draft_width, stops, stop_stride, stop_counts, verdict):
+    self.check(self.lib.infdev_verify_drafts(self.ctx, queries.ptr, nq, sampled.ptr, proposed.ptr, draft_width, stops.ptr, stop_stride,
+                                             stop_counts.ptr, verdict.ptr))
+
+  def commit_states(self, queries, nq, verdict, state_next, candidate_base, state_bytes):
+    self.check(self.lib.infdev_commit_states(self.ctx, queries.ptr, nq, verdict.ptr, state_next.ptr, candidate_base, state_bytes))

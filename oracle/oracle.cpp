@@ -135,15 +135,20 @@ void orc_dequant_q6k(const uint8_t* blocks, int64_t count, float* out) {
 // quant_linear.metal:245-327 (Q4_K decode), :436-512 (Q6_K decode), :151-233 (prefill GEMM);
 // epilogue `post` 0/1 as linear_decode_store :237-243. W is row-major by n, k/256 super-blocks per row.
 void orc_linear(const uint8_t* w, int type, int64_t n, int64_t k, const float* x, int64_t m, float* y, const float* residual) {
+  // Activation rows are taken 32 at a time so that a block of them stays in cache while the weight rows stream by;
+  // every (row, column) dot product is computed independently, so the blocking does not change a single bit.
+  for (int64_t r0 = 0; r0 < m; r0 += 32) {
+    const int64_t r1 = std::min<int64_t>(m, r0 + 32);
 #pragma omp parallel
-  {
-    std::vector<float> row(k);
+    {
+      std::vector<float> row(k);
 #pragma omp for schedule(static)
-    for (int64_t i = 0; i < n; ++i) {
-      dequant_row(w, type, i, k, row.data());
-      for (int64_t r = 0; r < m; ++r) {
-        float v = float(dot(x + r * k, row.data(), k));
-        y[r * n + i] = residual ? v + residual[r * n + i] : v;
+      for (int64_t i = 0; i < n; ++i) {
+        dequant_row(w, type, i, k, row.data());
+        for (int64_t r = r0; r < r1; ++r) {
+          float v = float(dot(x + r * k, row.data(), k));
+          y[r * n + i] = residual ? v + residual[r * n + i] : v;
+        }
       }
     }
   }
@@ -152,15 +157,18 @@ void orc_linear(const uint8_t* w, int type, int64_t n, int64_t k, const float* x
 // y[m,n] = silu(x.Wg[n]) * (x.Wu[n]). fused_kernels.metal:48-78 (decode) and the `post == 2` epilogue of
 // quant_linear.metal:224-232 (prefill).
 void orc_gate_up(const uint8_t* wg, const uint8_t* wu, int type, int64_t n, int64_t k, const float* x, int64_t m, float* y) {
+  for (int64_t r0 = 0; r0 < m; r0 += 32) {
+    const int64_t r1 = std::min<int64_t>(m, r0 + 32);
 #pragma omp parallel
-  {
-    std::vector<float> g(k), u(k);
+    {
+      std::vector<float> g(k), u(k);
 #pragma omp for schedule(static)
-    for (int64_t i = 0; i < n; ++i) {
-      dequant_row(wg, type, i, k, g.data());
-      dequant_row(wu, type, i, k, u.data());
-      for (int64_t r = 0; r < m; ++r)
-        y[r * n + i] = silu(float(dot(x + r * k, g.data(), k))) * float(dot(x + r * k, u.data(), k));
+      for (int64_t i = 0; i < n; ++i) {
+        dequant_row(wg, type, i, k, g.data());
+        dequant_row(wu, type, i, k, u.data());
+        for (int64_t r = r0; r < r1; ++r)
+          y[r * n + i] = silu(float(dot(x + r * k, g.data(), k))) * float(dot(x + r * k, u.data(), k));
+      }
     }
   }
 }
@@ -464,9 +472,9 @@ int32_t orc_sample(const float* logits, int64_t vocab, float temperature, float 
 }
 
 // ---- whole model -----------------------------------------------------------------------------
-// One token of one sequence through the decoder stack, following Ops::decoder (forward.cpp:77-120) and the
-// per-row math summarised from the kernels above. All tensor pointers are filled by the test harness from
-// a GGUF file; quantised projections carry their ggml type.
+// T tokens of one sequence through the decoder stack, following Ops::decoder (forward.cpp:77-120) and the
+// per-row math of the kernels above. All tensor pointers are filled by the test harness from a GGUF file;
+// quantised projections carry their ggml type.
 struct OrcLayer {
   const float *attnNorm, *postNorm;
   const uint8_t *gate, *up, *down;
@@ -483,86 +491,186 @@ struct OrcModel {
   const uint8_t *embd, *output;
   const float* outputNorm;
   const float* rope;  // [maxContext,32,2]
-  OrcLayer layer[64];
+  OrcLayer layer[64];  // layer[layers] is the attention layer of the MTP block when the file carries one
+  // MTP block blk.<layers>.nextn.* (forward.cpp:122-130, 210): input norms, 8192 -> 4096 projection, head norm
+  const float *mtpEnorm, *mtpHnorm, *mtpHeadNorm;
+  const uint8_t* mtpProj;
 };
 
 // Per-sequence state: conv [gdn layers][8192][4], S [gdn layers][32][128][128], K/V fp16
-// [attention layers][maxContext][4][256] stored as floats already rounded through fp16.
+// [attention layers][maxContext][4][256] stored as floats already rounded through fp16; the MTP layer has a
+// cache of its own [maxContext][4][256] (K/V layer index 8 of the reference, forward.cpp:228).
 struct OrcState {
   float *conv, *S, *keys, *values;
   int32_t length;
+  float *mtpKeys, *mtpValues;
 };
 
-// Appends one token, returns the final hidden state (before output_norm) in hidden[4096] and, when logits is
-// non-null, rmsnorm(hidden; output_norm) . output^T in logits[vocab] (forward.cpp:72-75).
-void orc_model_step(const OrcModel* model, OrcState* state, int32_t token, float* hidden, float* logits) {
+}  // extern "C"
+
+namespace {
+
+// Gated full attention of Ops::decoder (forward.cpp:84-96) for T rows at positions pos .. pos + T - 1 of one
+// sequence: q/k/v projections, attention_prepare, cache append (attention.metal:126-133), causal softmax over the
+// cache, sigmoid gate, output projection added to h. keys / values: this layer's [maxContext][1024] cache.
+void attention_rows(const OrcModel* model, const OrcLayer& w, float* keys, float* values, int pos, int64_t T, const float* x, float* h) {
+  const int64_t H = 4096;
+  std::vector<float> qg(T * 8192), k(T * 1024), v(T * 1024), q(T * 4096), kr(T * 1024), o(T * 4096), y(T * H);
+  std::vector<int32_t> positions(T);
+  for (int64_t t = 0; t < T; ++t)
+    positions[t] = pos + int32_t(t);
+  orc_linear(w.wq, model->projType, 8192, H, x, T, qg.data(), nullptr);
+  orc_linear(w.wk, model->projType, 1024, H, x, T, k.data(), nullptr);
+  orc_linear(w.wv, model->projType, 1024, H, x, T, v.data(), nullptr);
+  orc_attention_prepare(qg.data(), k.data(), w.qNorm, w.kNorm, model->rope, positions.data(), T, q.data(), kr.data());
+  for (int64_t t = 0; t < T; ++t)
+    for (int i = 0; i < 1024; ++i) {
+      keys[size_t(pos + t) * 1024 + i] = half_round(kr[t * 1024 + i]);
+      values[size_t(pos + t) * 1024 + i] = half_round(v[t * 1024 + i]);
+    }
+#pragma omp parallel for collapse(2)
+  for (int64_t t = 0; t < T; ++t)
+    for (int head = 0; head < 16; ++head) {
+      const int kvHead = head / 4, last = pos + int(t);
+      const float* qv = q.data() + (t * 16 + head) * 256;
+      std::vector<float> score(last + 1);
+      float maximum = -INFINITY;
+      for (int c = 0; c <= last; ++c) {
+        float sum = 0.0f;
+        for (int d = 0; d < 256; ++d)
+          sum = std::fma(qv[d], keys[size_t(c) * 1024 + kvHead * 256 + d], sum);
+        score[c] = sum * (1.0f / 16.0f);
+        maximum = std::max(maximum, score[c]);
+      }
+      double norm = 0.0, numerator[256] = {0};
+      for (int c = 0; c <= last; ++c) {
+        double weight = std::exp(double(score[c] - maximum));
+        norm += weight;
+        for (int d = 0; d < 256; ++d)
+          numerator[d] += weight * values[size_t(c) * 1024 + kvHead * 256 + d];
+      }
+      for (int d = 0; d < 256; ++d)
+        o[(t * 16 + head) * 256 + d] = float(numerator[d] / norm) * sigmoid(qg[(t * 16 + head) * 512 + 256 + d]);
+    }
+  orc_linear(w.wo, model->projType, H, H, o.data(), T, y.data(), h);
+  std::memcpy(h, y.data(), size_t(T) * H * 4);
+}
+
+// Gated delta network of Ops::decoder (forward.cpp:97-107) for T rows: projections, beta / g, causal conv with the
+// carried taps, the sequential delta rule, gated norm, output projection added to h.
+void gdn_rows(const OrcModel* model, const OrcLayer& w, float* convState, float* S, bool fresh, int64_t T, const float* x, float* h) {
+  const int64_t H = 4096;
+  std::vector<float> mixed(T * 8192), z(T * H), beta(T * 32), g(T * 32), q(T * 2048), k(T * 2048), v(T * 4096), o(T * 4096), gated(T * 4096),
+      conv(8192 * 4), y(T * H);
+  orc_linear(w.wqkv, model->projType, 8192, H, x, T, mixed.data(), nullptr);
+  orc_linear(w.wz, model->projType, H, H, x, T, z.data(), nullptr);
+  orc_gdn_ba(x, w.wBeta, w.wAlpha, w.ssmA, w.ssmDt, T, beta.data(), g.data());
+  orc_gdn_conv(mixed.data(), w.conv, fresh ? nullptr : convState, T, q.data(), k.data(), v.data(), conv.data(), 0);
+  std::memcpy(convState, conv.data(), conv.size() * 4);
+  orc_delta_rule(q.data(), k.data(), v.data(), g.data(), beta.data(), T, S, o.data(), nullptr);
+  orc_gated_rms_norm(o.data(), z.data(), w.ssmNorm, T * 32, gated.data());
+  orc_linear(w.wout, model->projType, H, H, gated.data(), T, y.data(), h);
+  std::memcpy(h, y.data(), size_t(T) * H * 4);
+}
+
+// SwiGLU block (forward.cpp:109-119): h += down(silu(gate(x)) * up(x)), x = rmsnorm(h; post_attention_norm).
+void mlp_rows(const OrcModel* model, const OrcLayer& w, int64_t T, float* h) {
   const int64_t H = 4096, I = 12288;
-  std::vector<float> h(H), x(H), t0(8192), t1(I), t2(I), t3(H);
-  int pos = state->length;
-  orc_embedding(model->embd, model->embdType, H, &token, 1, h.data());
+  std::vector<float> x(T * H), t(T * I), y(T * H);
+  orc_rms_norm(h, w.postNorm, T, H, 1.0e-6f, x.data());
+  orc_gate_up(w.gate, w.up, model->projType, I, H, x.data(), T, t.data());
+  orc_linear(w.down, model->projType, H, I, t.data(), T, y.data(), h);
+  std::memcpy(h, y.data(), size_t(T) * H * 4);
+}
+
+}  // namespace
+
+extern "C" {
+
+// Appends T tokens to the sequence in one pass. hidden (nullable) receives the final hidden state (before
+// output_norm) of every row [T][4096]; the last `logitRows` rows also get rmsnorm(hidden; output_norm) . output^T
+// in logits[logitRows][vocab] (forward.cpp:72-75). Row t is computed with exactly the arithmetic of a one-token
+// call at its position, so one pass of T tokens and T passes of one token give identical bits.
+void orc_model_forward(const OrcModel* model, OrcState* state, const int32_t* tokens, int64_t T, float* hidden, int64_t logitRows,
+                       float* logits) {
+  const int64_t H = 4096;
+  std::vector<float> h(T * H), x(T * H);
+  const int pos = state->length;
+  orc_embedding(model->embd, model->embdType, H, tokens, T, h.data());
   int gdn = 0, att = 0;
   for (int L = 0; L < model->layers; ++L) {
     const OrcLayer& w = model->layer[L];
-    orc_rms_norm(h.data(), w.attnNorm, 1, H, 1.0e-6f, x.data());
+    orc_rms_norm(h.data(), w.attnNorm, T, H, 1.0e-6f, x.data());
     if ((L + 1) % 4 == 0) {
-      std::vector<float> qg(8192), k(1024), v(1024), q(4096), kr(1024), o(4096);
-      orc_linear(w.wq, model->projType, 8192, H, x.data(), 1, qg.data(), nullptr);
-      orc_linear(w.wk, model->projType, 1024, H, x.data(), 1, k.data(), nullptr);
-      orc_linear(w.wv, model->projType, 1024, H, x.data(), 1, v.data(), nullptr);
-      int32_t position = pos;
-      orc_attention_prepare(qg.data(), k.data(), w.qNorm, w.kNorm, model->rope, &position, 1, q.data(), kr.data());
-      float* keys = state->keys + (size_t(att) * model->maxContext) * 1024;
-      float* values = state->values + (size_t(att) * model->maxContext) * 1024;
-      for (int i = 0; i < 1024; ++i) {
-        keys[size_t(pos) * 1024 + i] = half_round(kr[i]);
-        values[size_t(pos) * 1024 + i] = half_round(v[i]);
-      }
-      for (int head = 0; head < 16; ++head) {
-        int kvHead = head / 4;
-        std::vector<float> score(pos + 1);
-        float maximum = -INFINITY;
-        for (int t = 0; t <= pos; ++t) {
-          float s = 0.0f;
-          for (int d = 0; d < 256; ++d)
-            s = std::fma(q[head * 256 + d], keys[size_t(t) * 1024 + kvHead * 256 + d], s);
-          score[t] = s * (1.0f / 16.0f);
-          maximum = std::max(maximum, score[t]);
-        }
-        double norm = 0.0, numerator[256] = {0};
-        for (int t = 0; t <= pos; ++t) {
-          double weight = std::exp(double(score[t] - maximum));
-          norm += weight;
-          for (int d = 0; d < 256; ++d)
-            numerator[d] += weight * values[size_t(t) * 1024 + kvHead * 256 + d];
-        }
-        for (int d = 0; d < 256; ++d)
-          o[head * 256 + d] = float(numerator[d] / norm) * sigmoid(qg[head * 512 + 256 + d]);
-      }
-      orc_linear(w.wo, model->projType, H, H, o.data(), 1, t3.data(), h.data());
+      attention_rows(model, w, state->keys + size_t(att) * model->maxContext * 1024, state->values + size_t(att) * model->maxContext * 1024, pos,
+                     T, x.data(), h.data());
       ++att;
     } else {
-      std::vector<float> mixed(8192), z(H), beta(32), g(32), q(2048), k(2048), v(4096), o(4096), y(4096), conv(8192 * 4);
-      orc_linear(w.wqkv, model->projType, 8192, H, x.data(), 1, mixed.data(), nullptr);
-      orc_linear(w.wz, model->projType, H, H, x.data(), 1, z.data(), nullptr);
-      orc_gdn_ba(x.data(), w.wBeta, w.wAlpha, w.ssmA, w.ssmDt, 1, beta.data(), g.data());
-      float* convState = state->conv + size_t(gdn) * 8192 * 4;
-      orc_gdn_conv(mixed.data(), w.conv, pos ? convState : nullptr, 1, q.data(), k.data(), v.data(), conv.data(), 0);
-      std::memcpy(convState, conv.data(), conv.size() * 4);
-      orc_delta_rule(q.data(), k.data(), v.data(), g.data(), beta.data(), 1, state->S + size_t(gdn) * 32 * 128 * 128, o.data(), nullptr);
-      orc_gated_rms_norm(o.data(), z.data(), w.ssmNorm, 32, y.data());
-      orc_linear(w.wout, model->projType, H, H, y.data(), 1, t3.data(), h.data());
+      gdn_rows(model, w, state->conv + size_t(gdn) * 8192 * 4, state->S + size_t(gdn) * 32 * 128 * 128, pos == 0, T, x.data(), h.data());
       ++gdn;
     }
-    h = t3;
-    orc_rms_norm(h.data(), w.postNorm, 1, H, 1.0e-6f, x.data());
-    orc_gate_up(w.gate, w.up, model->projType, I, H, x.data(), 1, t1.data());
-    orc_linear(w.down, model->projType, H, I, t1.data(), 1, t3.data(), h.data());
-    h = t3;
+    mlp_rows(model, w, T, h.data());
   }
-  state->length = pos + 1;
-  std::memcpy(hidden, h.data(), H * 4);
+  state->length = pos + int(T);
+  if (hidden)
+    std::memcpy(hidden, h.data(), size_t(T) * H * 4);
+  if (logits && logitRows > 0) {
+    const float* rows = h.data() + (T - logitRows) * H;
+    orc_rms_norm(rows, model->outputNorm, logitRows, H, 1.0e-6f, x.data());
+    orc_linear(model->output, model->outType, model->vocab, H, x.data(), logitRows, logits, nullptr);
+  }
+}
+
+// One token (the decode step): orc_model_forward with T = 1.
+void orc_model_step(const OrcModel* model, OrcState* state, int32_t token, float* hidden, float* logits) {
+  orc_model_forward(model, state, &token, 1, hidden, logits ? 1 : 0, logits);
+}
+
+// ---- MTP drafter -----------------------------------------------------------------------------
+// native_ops.metal:43-87 for one row: y[8192] = [rmsnorm(embedding) * enorm | rmsnorm(h) * hnorm]. h == null stands
+// for the first row of a fresh sequence, which has no predecessor (`initial`, :57): that half is zero.
+void orc_mtp_fuse(const float* embedding, const float* h, const float* enorm, const float* hnorm, float* y) {
+  std::vector<float> zero(4096, 0.0f);
+  orc_rms_norm(embedding, enorm, 1, 4096, 1.0e-6f, y);
+  orc_rms_norm(h ? h : zero.data(), hnorm, 1, 4096, 1.0e-6f, y + 4096);
+}
+
+// One row of the MTP block at `position` of the sequence: Ops::mtpInput (forward.cpp:122-130: embedding of `token`,
+// mtp_fuse with `previousHidden`, eh_proj 8192 -> 4096), then
+//  * storeOnly != 0: the tail of a target pass (forward.cpp:218-232): attn_norm, K / V projections and mtp_store_kv
+//    (attention.metal:53-100: K RMS norm + RoPE, fp16 store) into the MTP cache at `position`;
+//  * storeOnly == 0: one drafting step (forward.cpp:197-217): the whole attention layer blk.<layers> over the MTP
+//    cache (which it appends to at `position`), its MLP, and when logits is non-null shared_head_norm + lm_head.
+// previousHidden is what the step fuses with: the target's hidden state of position - 1 for the tail and for the
+// first drafting step (the stored seed), the MTP block's own previous output for later drafting steps (the
+// reference passes the embedding a second time there, forward.cpp:125-128, 199; proposals only affect the
+// acceptance rate, never the emitted tokens). hidden (nullable) receives the block's output.
+void orc_mtp_step(const OrcModel* model, OrcState* state, int32_t token, const float* previousHidden, int32_t position, int32_t storeOnly,
+                  float* hidden, float* logits) {
+  const int64_t H = 4096;
+  const OrcLayer& w = model->layer[model->layers];
+  std::vector<float> embedding(H), fused(2 * H), h(H), x(H);
+  orc_embedding(model->embd, model->embdType, H, &token, 1, embedding.data());
+  orc_mtp_fuse(embedding.data(), previousHidden, model->mtpEnorm, model->mtpHnorm, fused.data());
+  orc_linear(model->mtpProj, model->projType, H, 2 * H, fused.data(), 1, h.data(), nullptr);
+  orc_rms_norm(h.data(), w.attnNorm, 1, H, 1.0e-6f, x.data());
+  if (storeOnly) {
+    std::vector<float> k(1024), v(1024), kr(1024), qg(8192, 0.0f), q(4096);
+    orc_linear(w.wk, model->projType, 1024, H, x.data(), 1, k.data(), nullptr);
+    orc_linear(w.wv, model->projType, 1024, H, x.data(), 1, v.data(), nullptr);
+    orc_attention_prepare(qg.data(), k.data(), w.kNorm, w.kNorm, model->rope, &position, 1, q.data(), kr.data());
+    for (int i = 0; i < 1024; ++i) {
+      state->mtpKeys[size_t(position) * 1024 + i] = half_round(kr[i]);
+      state->mtpValues[size_t(position) * 1024 + i] = half_round(v[i]);
+    }
+    return;
+  }
+  attention_rows(model, w, state->mtpKeys, state->mtpValues, position, 1, x.data(), h.data());
+  mlp_rows(model, w, 1, h.data());
+  if (hidden)
+    std::memcpy(hidden, h.data(), H * 4);
   if (logits) {
-    orc_rms_norm(h.data(), model->outputNorm, 1, H, 1.0e-6f, x.data());
+    orc_rms_norm(h.data(), model->mtpHeadNorm, 1, H, 1.0e-6f, x.data());
     orc_linear(model->output, model->outType, model->vocab, H, x.data(), 1, logits, nullptr);
   }
 }

@@ -14,7 +14,7 @@ from gguf import GGMLQuantizationType
 from gguf.quants import dequantize
 
 sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
-from mtlqwen_b200 import synth
+from mtlqwen_b200.testing import synth
 
 
 def main():

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 
 import oracle
-from mtlqwen_b200 import synth
+from mtlqwen_b200.testing import synth
 from mtlqwen_b200.inference import InferenceEngine
 
 pytestmark = pytest.mark.gpu
@@ -164,18 +164,51 @@ def test_mixed_batch_sampling_matches_greedy(model):
       sequence.close()
 
 
-def test_seeded_sampling_is_reproducible_and_batching_invariant(model):
-  """A slot's i-th emitted token uses the i-th variate of its own Philox stream whatever else is batched."""
+def test_seeded_sampling_is_reproducible_and_batching_invariant(plain_weights):
+  """The i-th emitted token of a sequence uses the i-th variate of its own Philox stream whatever else is batched, the
+  key of that stream depends only on the engine's base seed and on how many sequences were created before it, and
+  the next sequence in the same slot draws from a new key (the reference keeps advancing rng[slot] across
+  sequences, runtime/engine.cpp:210-211, so a repeated request does not repeat its completion)."""
   prompt = prompt_tokens(20, 24)
-  alone = model.sequence(temperature=0.7, top_p=0.9, top_k=40)
-  tokens_alone = complete(alone, prompt, 8)
-  alone.close()
-  again = model.sequence(temperature=0.7, top_p=0.9, top_k=40)  # takes the same slot, hence the same seed
-  other = model.sequence()
-  got = parallel([lambda: complete(again, prompt, 8), lambda: complete(other, prompt_tokens(21, 90), 8)])
-  again.close()
-  other.close()
-  assert got[0] == tokens_alone
+
+  def run(batched):
+    os.environ["INFENG_SEED"] = "4242"
+    engine = InferenceEngine(plain_weights, max_context=512)
+    try:
+      sampled = engine.sequence(temperature=0.7, top_p=0.9, top_k=40)
+      calls = [lambda: complete(sampled, prompt, 8)]
+      if batched:
+        other = engine.sequence()
+        calls.append(lambda: complete(other, prompt_tokens(21, 90), 8))
+      first = parallel(calls)[0]
+      slot_length = sampled.length
+      sampled.close()
+      again = engine.sequence(temperature=0.7, top_p=0.9, top_k=40)  # takes the slot that was just freed
+      second = complete(again, prompt, 8)
+      again.close()
+      assert slot_length >= len(prompt)
+      return first, second
+    finally:
+      engine.close()
+
+  alone, regenerated = run(False)
+  together, _ = run(True)
+  assert together == alone
+  assert regenerated != alone
+
+
+def test_out_of_range_token_ids_are_refused(model):
+  """The embedding gather indexes the table with the appended ids: ids outside the vocabulary never reach the device."""
+  sequence = model.sequence()
+  try:
+    passes = model.step_counters()["passes"]
+    for bad in ([VOCAB], [5, -1, 7], [2**31 - 1]):
+      with pytest.raises(RuntimeError, match="no available model context"):
+        sequence.append(bad)
+    assert sequence.length == 0 and model.step_counters()["passes"] == passes
+    assert one(sequence, [VOCAB - 1, 0]) is not None
+  finally:
+    sequence.close()
 
 
 def test_all_slots_and_ninth_sequence(model):

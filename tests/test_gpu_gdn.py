@@ -4,7 +4,7 @@ import pytest
 
 import oracle
 from mtlqwen_b200 import device as D
-from mtlqwen_b200 import images
+from mtlqwen_b200.testing import images
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-3  # BASELINE: GDN outputs within 1e-3 relative error in fp32 accumulation

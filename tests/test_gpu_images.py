@@ -5,7 +5,7 @@ import pytest
 
 import oracle
 from mtlqwen_b200 import device as D
-from mtlqwen_b200 import images, synth
+from mtlqwen_b200.testing import images, synth
 
 pytestmark = pytest.mark.gpu
 

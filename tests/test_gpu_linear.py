@@ -6,7 +6,7 @@ import pytest
 
 import oracle
 from mtlqwen_b200 import device as D
-from mtlqwen_b200 import synth
+from mtlqwen_b200.testing import synth
 
 pytestmark = pytest.mark.gpu
 GOLDEN = Path(__file__).resolve().parent / "golden" / "kquant_dequant.npz"

@@ -4,7 +4,7 @@ from pathlib import Path
 import numpy as np
 
 import oracle
-from mtlqwen_b200 import synth
+from mtlqwen_b200.testing import synth
 
 GOLDEN = Path(__file__).resolve().parent / "golden" / "kquant_dequant.npz"
 
