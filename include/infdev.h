@@ -63,6 +63,10 @@ void* infdev_alloc(infdev_ctx* ctx, size_t bytes, int hostVisible);
 void infdev_free(infdev_ctx* ctx, void* pointer);
 int infdev_upload(infdev_ctx* ctx, void* device, const void* host, size_t bytes);
 int infdev_download(infdev_ctx* ctx, void* host, const void* device, size_t bytes);
+/* Reads device memory without touching the context's stream: a synchronous copy that is not ordered with queued work, so
+ * it may be called from any thread while another thread launches (or captures) on the stream. The caller guarantees
+ * that nothing queued writes the range. */
+int infdev_peek(infdev_ctx* ctx, void* host, const void* device, size_t bytes);
 int infdev_copy(infdev_ctx* ctx, void* destination, const void* source, size_t bytes);
 int infdev_fill(infdev_ctx* ctx, void* device, int byte, size_t bytes);
 /* Device::commit (device.cpp:138-145) with a deadline instead of an unbounded wait: blocks until the

@@ -22,8 +22,8 @@ typedef struct infeng_sequence infeng_sequence;
  * Metal build compiles shader sources from that directory); context in (0, 65536]; error: >= 1024 bytes that
  * receive the message when the call returns NULL. Environment: INFENG_DEVICE (GPU index, default LOCAL_RANK or
  * 0), INFENG_KV_BLOCKS (physical 128-token K/V blocks, default ceil(context/128) as engine.cpp:86),
- * INFENG_DRAFT_WIDTH (MTP proposals per step, default 2 as forward.cpp:139), INFENG_SEED (base of the per-slot
- * sampling seeds, default the clock), INFENG_BLOCK_TOKENS, INFENG_COMMIT_TIMEOUT_MS, INFENG_GRAPHS (0 disables CUDA-graph replay of decode passes). */
+ * INFENG_DRAFT_WIDTH (MTP proposals per step, default 2 as forward.cpp:139), INFENG_SEED (base of the sampling
+ * keys: sequence number i of an engine draws from a Philox stream keyed by (seed, i); default the clock), INFENG_BLOCK_TOKENS, INFENG_COMMIT_TIMEOUT_MS, INFENG_GRAPHS (0 disables CUDA-graph replay of decode passes). */
 infeng_engine* infeng_engine_create(const char* weights, const char* draftWeights, const char* kernels, uint32_t context, char* error);
 /* engine.cpp:251-254: drops one reference; the engine dies with its last sequence. */
 void infeng_engine_release(infeng_engine* engine);
@@ -33,8 +33,9 @@ infeng_sequence* infeng_sequence_create(infeng_engine* engine, const int32_t* st
 /* engine.cpp:261-265: waits for the in-flight pass of the sequence, frees its slot and K/V references. */
 void infeng_sequence_release(infeng_sequence* sequence);
 /* engine.cpp:267-284: appends prompt tokens and starts generation; returns the new token count (the first
- * cursor to read). count == UINT32_MAX cancels (returns 0). -3: still generating. -4: nothing to do or the
- * context would overflow. */
+ * cursor to read). count == UINT32_MAX cancels (returns 0). -3: still generating. -4: nothing to do, the
+ * context would overflow, or a token id lies outside the vocabulary (the reference trusts its tokenizer; here the
+ * ids index the embedding table on the device, so they are checked). */
 int32_t infeng_sequence_append(infeng_sequence* sequence, const int32_t* tokens, uint32_t count);
 /* engine.cpp:286-292: blocks until token `cursor` exists or generation stopped. Token id >= 0; -1 finished;
  * -5 the pass failed (no evictable K/V block, or a device error). */
@@ -45,8 +46,25 @@ int32_t infeng_sequence_read(infeng_sequence* sequence, uint32_t cursor);
  * the passes (CUDA events on the stream), 11 kernels launched, 12 to 14 microseconds the scheduler spent outside
  * the passes: building batches, waiting for the engine lock after a pass, handing sampled tokens over. */
 uint64_t infeng_engine_info(infeng_engine* engine, uint32_t field);
-/* engine.cpp:299-303: 0 drafted tokens, 1 accepted tokens, 2 tokens held in the K/V cache. */
+/* engine.cpp:299-303: 0 drafted tokens, 1 accepted tokens, 2 tokens held in the K/V cache. Additions: 3 position of
+ * the anchor token of the sequence's latest speculative step, 4 .. 4 + draft width - 1 the drafter's proposals of
+ * that step. */
 uint64_t infeng_sequence_info(infeng_sequence* sequence, uint32_t field);
+/* No counterpart in the reference (its state records are only reachable from the GPU). Copies `bytes` at `offset` of
+ * the sequence's current state record to `out`: per gated-delta-rule layer the convolution taps fp32 [8192][4] and
+ * the recurrent state fp32 [32][128][128], then the MTP seed fp32 [4096] (the target's final hidden state of the last
+ * committed position, kept when a drafter is loaded). For persisting a conversation and for checking the state
+ * against another implementation. Returns the bytes copied, -3 while the sequence is generating, -4 when the range
+ * lies outside the record. field 0 of the call with bytes == 0 returns the record size. */
+int64_t infeng_sequence_state(infeng_sequence* sequence, uint64_t offset, void* out, uint64_t bytes);
+
+/* The header index of a GGUF file as the engine reads it (the role of ggml's gguf_init_from_buffer and its tensor
+ * getters in loadWeights, forward.cpp:12-23; ggml is not a dependency of this build). Writes one text line per
+ * tensor, "name<TAB>ggml type<TAB>absolute file offset of the data<TAB>bytes (0 = type not loadable)<TAB>ne0,ne1,...",
+ * preceded by a line "gguf<TAB>version<TAB>alignment<TAB>data offset<TAB>tensor count", into `out` (capacity bytes,
+ * NUL-terminated). Needs no GPU. Returns the length of the text, or -1 with the message in `error` (>= 1024 bytes)
+ * when the file cannot be parsed or the text does not fit. */
+int64_t infeng_gguf_describe(const char* path, char* out, uint64_t capacity, char* error);
 
 #ifdef __cplusplus
 }

@@ -4,6 +4,7 @@ The reference compiles its engine on first import with `xcrun clang++` (runtime/
 here the same happens with nvcc, and the shared library lands beside the package so it is found
 without any install step.
 """
+import fcntl
 import os
 import shutil
 import subprocess
@@ -36,6 +37,17 @@ def build(force=False, verbose=False):
     return Path(prebuilt)
   if not force and not stale():
     return LIB
+  # Several ranks of one launch may find the library stale at the same moment: one builds, the others wait and then
+  # find it fresh. The link goes to a temporary name and is moved into place, so nobody loads a half-written file.
+  LIB.parent.mkdir(parents=True, exist_ok=True)
+  with open(LIB.parent / ".build.lock", "w") as lock:
+    fcntl.flock(lock, fcntl.LOCK_EX)
+    if not force and not stale():
+      return LIB
+    return _compile_and_link(force, verbose)
+
+
+def _compile_and_link(force, verbose):
   nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
   if not Path(nvcc).exists():
     raise RuntimeError("nvcc not found: libinfeng.so cannot be built")
@@ -57,10 +69,12 @@ def build(force=False, verbose=False):
       print(output)
     if job.returncode:
       raise RuntimeError(f"nvcc failed on {source.name}:\n{output}")
-  link = [nvcc, *ARCH, "-shared", "-o", str(LIB), *[str(objects / (s.stem + ".o")) for s in sources()], "-Xcompiler", "-pthread"]
+  temporary = LIB.with_name(f".{LIB.name}.{os.getpid()}")
+  link = [nvcc, *ARCH, "-shared", "-o", str(temporary), *[str(objects / (s.stem + ".o")) for s in sources()], "-Xcompiler", "-pthread"]
   result = subprocess.run(link, capture_output=True, text=True)
   if result.returncode:
     raise RuntimeError("link failed:\n" + result.stdout + result.stderr)
+  os.replace(temporary, LIB)
   return LIB
 
 

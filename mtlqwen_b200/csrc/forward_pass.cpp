@@ -12,6 +12,42 @@
 #include "runtime.hpp"
 
 namespace infeng::qwen35 {
+
+// Read-only mapping of a file.
+struct FileMapping {
+  void* data = MAP_FAILED;
+  uint64_t bytes = 0;
+  explicit FileMapping(const std::filesystem::path& path) {
+    const int fd = ::open(path.c_str(), O_RDONLY);
+    if (fd < 0)
+      throw std::runtime_error("cannot open weights file " + path.string());
+    struct stat info{};
+    ::fstat(fd, &info);
+    bytes = uint64_t(info.st_size);
+    data = ::mmap(nullptr, bytes, PROT_READ, MAP_PRIVATE, fd, 0);
+    ::close(fd);
+    if (data == MAP_FAILED)
+      throw std::runtime_error("cannot map weights file " + path.string());
+  }
+  FileMapping(const FileMapping&) = delete;
+  ~FileMapping() { ::munmap(data, bytes); }
+};
+
+std::string describeGguf(const std::filesystem::path& path) {
+  FileMapping mapping(path);
+  const GgufFile file = gguf_parse(static_cast<const uint8_t*>(mapping.data), mapping.bytes);
+  std::string text = "gguf\t" + std::to_string(file.version) + "\t" + std::to_string(file.alignment) + "\t" + std::to_string(file.dataOffset) + "\t" +
+                     std::to_string(file.tensors.size()) + "\n";
+  for (const GgufTensor& tensor : file.tensors) {
+    text += tensor.name + "\t" + std::to_string(tensor.type) + "\t" + std::to_string(file.dataOffset + tensor.offset) + "\t" +
+            std::to_string(tensor.bytes) + "\t";
+    for (size_t d = 0; d < tensor.shape.size(); ++d)
+      text += (d ? "," : "") + std::to_string(tensor.shape[d]);
+    text += "\n";
+  }
+  return text;
+}
+
 namespace {
 
 // Reads a GGUF file: header parsed on the host from a private mapping, tensor data copied once into one
@@ -19,50 +55,36 @@ namespace {
 // memory allows and PCIe does not). Returns name -> {device view, n = shape[1], k = shape[0], type}
 // (loadWeights, forward.cpp:12-23).
 void loadWeights(Engine& engine, const std::filesystem::path& path, Weights& weights, Tensor& storage) {
-  const int fd = ::open(path.c_str(), O_RDONLY);
-  if (fd < 0)
-    throw std::runtime_error("cannot open weights file " + path.string());
-  struct stat info{};
-  ::fstat(fd, &info);
-  const uint64_t bytes = uint64_t(info.st_size);
-  void* mapping = ::mmap(nullptr, bytes, PROT_READ, MAP_PRIVATE, fd, 0);
-  ::close(fd);
-  if (mapping == MAP_FAILED)
-    throw std::runtime_error("cannot map weights file " + path.string());
-  try {
-    const GgufFile file = gguf_parse(static_cast<const uint8_t*>(mapping), bytes);
-    const uint64_t dataBytes = bytes - file.dataOffset;
-    storage = engine.device.empty(dataBytes);
-    // Tensor data goes through two pinned 64 MiB staging buffers: CUDA refuses to copy straight out of a
-    // read-only file mapping, and pinned slices let the copy of one slice overlap the page-in of the next.
-    const uint64_t sliceBytes = 64ull << 20;
-    Tensor staging[2] = {engine.device.empty(sliceBytes, true), engine.device.empty(sliceBytes, true)};
-    uint32_t turn = 0;
-    for (uint64_t at = 0; at < dataBytes; at += sliceBytes, turn ^= 1) {
-      const uint64_t slice = std::min<uint64_t>(sliceBytes, dataBytes - at);
-      if (at >= 2 * sliceBytes)
-        engine.device.check(engine.device.commit());  // the buffer about to be refilled has been consumed
-      std::memcpy(staging[turn].contents<uint8_t>(), static_cast<const uint8_t*>(mapping) + file.dataOffset + at, slice);
-      engine.device.upload(storage.view(at, slice), staging[turn].contents<uint8_t>(), slice);
-    }
-    engine.device.check(engine.device.commit());
-    engine.modelBytes += dataBytes;
-    for (const GgufTensor& tensor : file.tensors) {
-      if (!tensor.bytes)
-        throw std::runtime_error("tensor " + tensor.name + " has unsupported ggml type " + std::to_string(tensor.type));
-      Weight weight;
-      static_cast<Tensor&>(weight) = storage.view(tensor.offset, tensor.bytes);
-      weight.k = uint32_t(tensor.shape[0]);
-      weight.n = tensor.shape.size() > 1 ? uint32_t(tensor.shape[1]) : 1;
-      weight.type = tensor.type;
-      engine.parameterCount += tensor.elements;
-      weights.emplace(tensor.name, weight);
-    }
-  } catch (...) {
-    ::munmap(mapping, bytes);
-    throw;
+  FileMapping mapping(path);
+  const uint8_t* bytesOfFile = static_cast<const uint8_t*>(mapping.data);
+  const GgufFile file = gguf_parse(bytesOfFile, mapping.bytes);
+  const uint64_t dataBytes = mapping.bytes - file.dataOffset;
+  storage = engine.device.empty(dataBytes);
+  // Tensor data goes through two pinned 64 MiB staging buffers: CUDA refuses to copy straight out of a
+  // read-only file mapping, and pinned slices let the copy of one slice overlap the page-in of the next.
+  const uint64_t sliceBytes = 64ull << 20;
+  Tensor staging[2] = {engine.device.empty(sliceBytes, true), engine.device.empty(sliceBytes, true)};
+  uint32_t turn = 0;
+  for (uint64_t at = 0; at < dataBytes; at += sliceBytes, turn ^= 1) {
+    const uint64_t slice = std::min<uint64_t>(sliceBytes, dataBytes - at);
+    if (at >= 2 * sliceBytes)
+      engine.device.check(engine.device.commit());  // the buffer about to be refilled has been consumed
+    std::memcpy(staging[turn].contents<uint8_t>(), bytesOfFile + file.dataOffset + at, slice);
+    engine.device.upload(storage.view(at, slice), staging[turn].contents<uint8_t>(), slice);
   }
-  ::munmap(mapping, bytes);
+  engine.device.check(engine.device.commit());
+  engine.modelBytes += dataBytes;
+  for (const GgufTensor& tensor : file.tensors) {
+    if (!tensor.bytes)
+      throw std::runtime_error("tensor " + tensor.name + " has unsupported ggml type " + std::to_string(tensor.type));
+    Weight weight;
+    static_cast<Tensor&>(weight) = storage.view(tensor.offset, tensor.bytes);
+    weight.k = uint32_t(tensor.shape[0]);
+    weight.n = tensor.shape.size() > 1 ? uint32_t(tensor.shape[1]) : 1;
+    weight.type = tensor.type;
+    engine.parameterCount += tensor.elements;
+    weights.emplace(tensor.name, weight);
+  }
 }
 
 // One pass over `rows` packed tokens (Ops, forward.cpp:25-131).
@@ -228,13 +250,66 @@ void Engine::loadModel(const std::filesystem::path& path, const std::filesystem:
   const bool hasMtp = weights.count("blk." + std::to_string(blocksWithNorm - 1) + ".nextn.eh_proj.weight") != 0;
   if (!draftPath.empty() && !hasMtp)
     throw std::runtime_error("draft weights carry no MTP block (blk.N.nextn.*); the DFlash drafter is not supported by this build");
-  drafter = hasMtp ? Drafter::mtp : Drafter::none;
+  // The drafter runs only when it was asked for through the draft path (forward.cpp:136-139): a file that carries the
+  // MTP block loads as a plain target model when passed as `weights` alone.
+  drafter = hasMtp && !draftPath.empty() ? Drafter::mtp : Drafter::none;
   targetLayers = blocksWithNorm - (hasMtp ? 1 : 0);
   if (targetLayers % fullAttentionInterval)
     throw std::runtime_error("decoder block count must be a multiple of 4");
   kvLayers = targetLayers / fullAttentionInterval;
   gdnLayers = targetLayers - kvLayers;
   vocab = weights.at("token_embd.weight").n;
+  // Every tensor the passes will touch, with the shape the fixed scratch buffers assume and a type the kernels serve:
+  // a file that does not fit is refused here rather than at its first pass.
+  auto require = [&](const std::string& name, uint32_t n, uint32_t k, bool quantised) {
+    auto found = weights.find(name);
+    if (found == weights.end())
+      throw std::runtime_error("missing weight " + name);
+    const Weight& w = found->second;
+    if (w.n != n || w.k != k)
+      throw std::runtime_error("weight " + name + " has shape " + std::to_string(w.n) + " x " + std::to_string(w.k) + ", expected " + std::to_string(n) +
+                               " x " + std::to_string(k));
+    const bool supported = quantised ? (w.type == INFDEV_Q4_K || w.type == INFDEV_Q6_K) : w.type == INFDEV_F32;
+    if (!supported)
+      throw std::runtime_error("weight " + name + " has ggml type " + std::to_string(w.type) + "; this build runs " +
+                               (quantised ? "Q4_K and Q6_K projections" : "F32 norms and GDN parameters"));
+  };
+  require("token_embd.weight", vocab, hiddenSize, true);
+  require("output.weight", vocab, hiddenSize, true);
+  require("output_norm.weight", 1, hiddenSize, false);
+  for (uint32_t layer = 0; layer < blocksWithNorm; ++layer) {
+    const std::string p = "blk." + std::to_string(layer) + ".";
+    require(p + "attn_norm.weight", 1, hiddenSize, false);
+    require(p + "post_attention_norm.weight", 1, hiddenSize, false);
+    require(p + "ffn_gate.weight", intermediateSize, hiddenSize, true);
+    require(p + "ffn_up.weight", intermediateSize, hiddenSize, true);
+    require(p + "ffn_down.weight", hiddenSize, intermediateSize, true);
+    if (layer >= targetLayers || (layer + 1) % fullAttentionInterval == 0) {
+      require(p + "attn_q.weight", 8192, hiddenSize, true);
+      require(p + "attn_k.weight", 1024, hiddenSize, true);
+      require(p + "attn_v.weight", 1024, hiddenSize, true);
+      require(p + "attn_output.weight", hiddenSize, hiddenSize, true);
+      require(p + "attn_q_norm.weight", 1, 256, false);
+      require(p + "attn_k_norm.weight", 1, 256, false);
+    } else {
+      require(p + "attn_qkv.weight", 8192, hiddenSize, true);
+      require(p + "attn_gate.weight", hiddenSize, hiddenSize, true);
+      require(p + "ssm_out.weight", hiddenSize, hiddenSize, true);
+      require(p + "ssm_beta.weight", 32, hiddenSize, false);
+      require(p + "ssm_alpha.weight", 32, hiddenSize, false);
+      require(p + "ssm_a", 1, 32, false);
+      require(p + "ssm_dt.bias", 1, 32, false);
+      require(p + "ssm_conv1d.weight", 8192, 4, false);
+      require(p + "ssm_norm.weight", 1, 128, false);
+    }
+  }
+  if (hasMtp) {
+    const std::string p = "blk." + std::to_string(targetLayers) + ".nextn.";
+    require(p + "enorm.weight", 1, hiddenSize, false);
+    require(p + "hnorm.weight", 1, hiddenSize, false);
+    require(p + "shared_head_norm.weight", 1, hiddenSize, false);
+    require(p + "eh_proj.weight", hiddenSize, 2 * hiddenSize, true);
+  }
   stateBytes = uint64_t(gdnLayers) * INFDEV_GDN_LAYER_STATE_BYTES + seedBytes;
   if (drafter == Drafter::mtp) {
     const char* width = std::getenv("INFENG_DRAFT_WIDTH");

@@ -138,9 +138,13 @@ inline GgufFile gguf_parse(const uint8_t* data, uint64_t bytes) {
     tensor.offset = cursor.read<uint64_t>();
     tensor.bytes = gguf_tensor_bytes(tensor.type, tensor.elements);
   }
+  if (!file.alignment || (file.alignment & (file.alignment - 1)))
+    throw std::runtime_error("GGUF general.alignment must be a power of two, got " + std::to_string(file.alignment));
   file.dataOffset = (cursor.position() + file.alignment - 1) / file.alignment * file.alignment;
+  if (file.dataOffset > bytes)
+    throw std::runtime_error("GGUF header is truncated");
   for (const GgufTensor& tensor : file.tensors)
-    if (tensor.bytes && file.dataOffset + tensor.offset + tensor.bytes > bytes)
+    if (tensor.bytes && (tensor.offset > bytes - file.dataOffset || tensor.bytes > bytes - file.dataOffset - tensor.offset))
       throw std::runtime_error("GGUF tensor " + tensor.name + " extends past the end of the file");
   return file;
 }

@@ -263,6 +263,11 @@ int infdev_download(infdev_ctx* ctx, void* host, const void* device, size_t byte
   return r ? r : check(ctx, cudaStreamSynchronize(ctx->stream), "infdev_download");
 }
 
+int infdev_peek(infdev_ctx* ctx, void* host, const void* device, size_t bytes) {
+  Bind bind(ctx);
+  return check(ctx, cudaMemcpy(host, device, bytes, cudaMemcpyDeviceToHost), "infdev_peek");
+}
+
 int infdev_copy(infdev_ctx* ctx, void* destination, const void* source, size_t bytes) {
   Bind bind(ctx);
   return check(ctx, cudaMemcpyAsync(destination, source, bytes, cudaMemcpyDefault, ctx->stream), "infdev_copy");
@@ -709,6 +714,8 @@ int infdev_mtp_fuse(infdev_ctx* ctx, const float* embedding, const float* hidden
 int infdev_attention_static(infdev_ctx* ctx, const float* q, const float* qg, const void* cacheK, const void* cacheV, const infdev_query* queries,
                             int queryCount, int64_t rows, const int32_t* table, int32_t tableStride, int32_t blockTokens, float* out) {
   Bind bind(ctx);  // the symbol lookup of the first call on a device needs that device current
+  if (take_capture(ctx))  // the one-shot request is consumed by the first call that could honour it; this variant writes no image
+    return fail(ctx, INFDEV_E_ARGUMENT, "attention_static: writes no image of its result; use infdev_attention after infdev_image_capture");
   if (rows > 0 && queryCount < 1)
     return fail(ctx, INFDEV_E_ARGUMENT, "attention: rows without queries");
   if (blockTokens <= 0 || blockTokens % 16)

@@ -196,7 +196,7 @@ __global__ void __launch_bounds__(256) mtp_fuse_kernel(const float* embedding, c
   const uint32_t token = row - info.start;
   const float* seed = reinterpret_cast<const float*>(info.previous + seedOffset);
   const float* h = mode == 2 ? seed : (mode == 1 && !token) ? seed : hidden + size_t(mode == 1 ? row - 1 : row) * 4096;
-  const bool initial = !info.previous && token == 0 && mode != 0;
+  const bool initial = !info.previous && token == 0;
   __shared__ float sums[18];
   float es = 0.f, hs = 0.f;
   for (int d = tid; d < 4096; d += 256) {

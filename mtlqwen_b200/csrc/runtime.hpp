@@ -155,4 +155,7 @@ struct PassShape {
 
 PassShape forward(Engine& engine, Batch& batch, bool drafting = false, bool launch = true);
 
+// Text listing of a GGUF file's header as the loader reads it (one line per tensor); see infeng_gguf_describe.
+std::string describeGguf(const std::filesystem::path& path);
+
 }  // namespace infeng::qwen35

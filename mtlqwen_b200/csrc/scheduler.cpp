@@ -317,22 +317,22 @@ void Engine::schedule() {
         for (uint32_t i = 0; i < batch.size && uniform; ++i)
           uniform = batch.queries[i].count == rowsEach;
         void*& graph = decodeGraphs[batch.size][kind];
+        auto launchAll = [&] {
+          if (batch.candidateRows)
+            forward(*this, batch, true);
+          shape = forward(*this, batch);
+        };
         if (uniform && graph) {
           shape = forward(*this, batch, false, false);  // host bookkeeping only
           device.check(infdev_graph_launch(device.ctx, graph));
-        } else if (uniform && decodeSeen[batch.size][kind]++ >= 1) {
-          device.check(infdev_graph_begin(device.ctx));
-          if (kind)
-            forward(*this, batch, true);
-          shape = forward(*this, batch);
+        } else if (uniform && decodeSeen[batch.size][kind]++ >= 1 && infdev_graph_begin(device.ctx) == INFDEV_OK) {
+          launchAll();
           graph = infdev_graph_end(device.ctx);
           if (!graph)
             throw std::runtime_error(infdev_error(device.ctx));
           device.check(infdev_graph_launch(device.ctx, graph));
         } else {
-          if (batch.candidateRows)
-            forward(*this, batch, true);
-          shape = forward(*this, batch);
+          launchAll();  // also the way of a device layer that cannot capture
         }
         infdev_event_record(device.ctx, passEvents[1]);
         announce();
@@ -510,6 +510,33 @@ uint64_t infeng_sequence_info(infeng_sequence* sequence, uint32_t field) {
         return uint64_t(uint32_t(sequence->draftProposals[field - 4]));
       return 0;
   }
+}
+
+int64_t infeng_gguf_describe(const char* path, char* out, uint64_t capacity, char* error) {
+  try {
+    const std::string text = describeGguf(path);
+    if (text.size() + 1 > capacity)
+      throw std::runtime_error("the listing needs " + std::to_string(text.size() + 1) + " bytes");
+    std::memcpy(out, text.c_str(), text.size() + 1);
+    return int64_t(text.size());
+  } catch (const std::exception& exception) {
+    report(error, exception);
+    return -1;
+  }
+}
+
+int64_t infeng_sequence_state(infeng_sequence* sequence, uint64_t offset, void* out, uint64_t bytes) {
+  Engine& engine = sequence->engine;
+  std::lock_guard<std::mutex> lock(engine.mutex);
+  if (!bytes)
+    return int64_t(engine.stateBytes);
+  if (sequence->active || sequence->busy)
+    return -3;
+  if (offset > engine.stateBytes || bytes > engine.stateBytes - offset)
+    return -4;
+  // No pass touches the records of a sequence that is neither active nor busy, and the copy stays off the stream.
+  const infeng::Tensor& state = engine.statePool[sequence->slot].first;
+  return infdev_peek(engine.device.ctx, out, state.as<uint8_t>() + offset, bytes) == INFDEV_OK ? int64_t(bytes) : -5;
 }
 
 }  // extern "C"

@@ -45,6 +45,7 @@ def library():
     "infdev_free": (None, (vp, vp)),
     "infdev_upload": (i32, (vp, vp, vp, ctypes.c_size_t)),
     "infdev_download": (i32, (vp, vp, vp, ctypes.c_size_t)),
+    "infdev_peek": (i32, (vp, vp, vp, ctypes.c_size_t)),
     "infdev_copy": (i32, (vp, vp, vp, ctypes.c_size_t)),
     "infdev_fill": (i32, (vp, vp, i32, ctypes.c_size_t)),
     "infdev_commit": (i32, (vp, u32)),

@@ -194,3 +194,27 @@ def read_gguf(path):
     view = raw[data_offset + offset:data_offset + offset + size]
     tensors[name] = (np.frombuffer(view, dtype=np.float32) if qtype == F32 else np.frombuffer(view, dtype=np.uint8), qtype)
   return tensors
+
+
+# ---- the full-size model of the benchmark configurations, written once per machine ----
+FULL_LAYERS, FULL_VOCAB, FULL_SEED = 32, 248320, 1234
+
+
+def full_model_path():
+  """Where the random-init Qwen3.5-9B-shaped GGUF (with the MTP block) lives; MTLQWEN_BENCH_GGUF overrides."""
+  import os
+  from pathlib import Path
+  override = os.environ.get("MTLQWEN_BENCH_GGUF")
+  return Path(override) if override else Path(f"/tmp/mtlqwen_b200_{FULL_LAYERS}x{FULL_VOCAB}_seed{FULL_SEED}_mtp.gguf")
+
+
+def ensure_full_model():
+  """Writes the file if it is not there yet (about 5.7 GB, some twenty seconds) and returns its path. Passed as
+  `weights` alone it loads as the plain target model; passed as `draft_weights` the MTP drafter is active."""
+  import os
+  path = full_model_path()
+  if not path.exists():
+    temporary = path.with_suffix(f".{os.getpid()}.tmp")
+    write_gguf(temporary, layers=FULL_LAYERS, vocab=FULL_VOCAB, mtp=True, seed=FULL_SEED)
+    os.replace(temporary, path)
+  return path

@@ -185,17 +185,26 @@ class _Layer(ctypes.Structure):
 class _Model(ctypes.Structure):
   _fields_ = [("layers", ctypes.c_int32), ("vocab", ctypes.c_int32), ("embdType", ctypes.c_int32), ("outType", ctypes.c_int32),
               ("projType", ctypes.c_int32), ("maxContext", ctypes.c_int32), ("embd", ctypes.c_void_p), ("output", ctypes.c_void_p),
-              ("outputNorm", ctypes.c_void_p), ("rope", ctypes.c_void_p), ("layer", _Layer * 64)]
+              ("outputNorm", ctypes.c_void_p), ("rope", ctypes.c_void_p), ("layer", _Layer * 64), ("mtpEnorm", ctypes.c_void_p),
+              ("mtpHnorm", ctypes.c_void_p), ("mtpHeadNorm", ctypes.c_void_p), ("mtpProj", ctypes.c_void_p)]
 
 
 class _State(ctypes.Structure):
   _fields_ = [("conv", ctypes.c_void_p), ("S", ctypes.c_void_p), ("keys", ctypes.c_void_p), ("values", ctypes.c_void_p),
-              ("length", ctypes.c_int32)]
+              ("length", ctypes.c_int32), ("mtpKeys", ctypes.c_void_p), ("mtpValues", ctypes.c_void_p)]
+
+
+def mtp_fuse(embedding, hidden, enorm, hnorm):
+  """One row of mtp_fuse; hidden None = the first row of a fresh sequence."""
+  y = np.empty(8192, np.float32)
+  lib().orc_mtp_fuse(_p(_f32(embedding)), _p(_f32(hidden)) if hidden is not None else None, _p(_f32(enorm)), _p(_f32(hnorm)), _p(y))
+  return y
 
 
 class Model:
   """Whole-decoder oracle over tensors read from a GGUF file: `tensors` maps reference tensor names to
-  (numpy array, ggml type). One instance = one sequence's state; `step(token)` appends a token."""
+  (numpy array, ggml type). One instance = one sequence's state; `step(token)` appends a token, `forward(tokens)`
+  several in one pass. When the file carries an MTP block (blk.<layers>.nextn.*) the drafter is available too."""
 
   def __init__(self, tensors, layers, vocab, max_context):
     self._keep = tensors
@@ -215,19 +224,27 @@ class Model:
       "wout": "ssm_out.weight", "wBeta": "ssm_beta.weight", "wAlpha": "ssm_alpha.weight", "ssmA": "ssm_a", "ssmDt": "ssm_dt.bias",
       "conv": "ssm_conv1d.weight", "ssmNorm": "ssm_norm.weight"
     }
-    for L in range(layers):
+    self.has_mtp = f"blk.{layers}.nextn.eh_proj.weight" in tensors
+    for L in range(layers + (1 if self.has_mtp else 0)):
       for field, name in names.items():
         key = f"blk.{L}.{name}"
         if key in tensors:
           setattr(m.layer[L], field, ptr(key))
+    if self.has_mtp:
+      nextn = f"blk.{layers}.nextn."
+      m.mtpEnorm, m.mtpHnorm = ptr(nextn + "enorm.weight"), ptr(nextn + "hnorm.weight")
+      m.mtpHeadNorm, m.mtpProj = ptr(nextn + "shared_head_norm.weight"), ptr(nextn + "eh_proj.weight")
     self._model = m
     gdn, att = layers - layers // 4, layers // 4
     self._conv = np.zeros((max(gdn, 1), 8192, 4), np.float32)
     self._S = np.zeros((max(gdn, 1), 32, 128, 128), np.float32)
     self._keys = np.zeros((max(att, 1), max_context, 1024), np.float32)
     self._values = np.zeros((max(att, 1), max_context, 1024), np.float32)
+    self._mtp_keys = np.zeros((max_context if self.has_mtp else 1, 1024), np.float32)
+    self._mtp_values = np.zeros_like(self._mtp_keys)
     s = _State()
     s.conv, s.S, s.keys, s.values, s.length = (self._conv.ctypes.data, self._S.ctypes.data, self._keys.ctypes.data, self._values.ctypes.data, 0)
+    s.mtpKeys, s.mtpValues = self._mtp_keys.ctypes.data, self._mtp_values.ctypes.data
     self._state = s
 
   @property
@@ -238,4 +255,24 @@ class Model:
     hidden = np.empty(4096, np.float32)
     logits = np.empty(self.vocab, np.float32) if want_logits else None
     lib().orc_model_step(ctypes.byref(self._model), ctypes.byref(self._state), ctypes.c_int32(int(token)), _p(hidden), _p(logits))
+    return hidden, logits
+
+  def forward(self, tokens, logit_rows=1):
+    """Appends `tokens` in one pass; returns (hidden [T,4096], logits of the last `logit_rows` rows)."""
+    tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+    hidden = np.empty((tokens.size, 4096), np.float32)
+    logits = np.empty((logit_rows, self.vocab), np.float32) if logit_rows else None
+    lib().orc_model_forward(ctypes.byref(self._model), ctypes.byref(self._state), _p(tokens), _i64(tokens.size), _p(hidden), _i64(logit_rows),
+                            _p(logits))
+    return hidden, logits
+
+  def mtp_step(self, token, previous_hidden, position, store_only=False, want_logits=True):
+    """One row of the MTP block at `position` (orc_mtp_step): the K/V store of a target pass's tail, or a drafting
+    step returning (block output, logits)."""
+    assert self.has_mtp
+    hidden = None if store_only else np.empty(4096, np.float32)
+    logits = np.empty(self.vocab, np.float32) if want_logits and not store_only else None
+    previous = _f32(previous_hidden) if previous_hidden is not None else None
+    lib().orc_mtp_step(ctypes.byref(self._model), ctypes.byref(self._state), ctypes.c_int32(int(token)), _p(previous), ctypes.c_int32(int(position)),
+                       ctypes.c_int32(int(store_only)), _p(hidden), _p(logits))
     return hidden, logits
