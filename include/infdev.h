@@ -72,6 +72,12 @@ int infdev_fill(infdev_ctx* ctx, void* device, int byte, size_t bytes);
 /* Device::commit (device.cpp:138-145) with a deadline instead of an unbounded wait: blocks until the
  * stream drains or timeoutMs passes (0 = no deadline), then reports the device status word. */
 int infdev_commit(infdev_ctx* ctx, uint32_t timeoutMs);
+/* Health check of the failure path behind INFDEV_E_DEVICE (no reference counterpart: Device::wait waits for ever,
+ * device.cpp:66-70). Every kernel here that waits on a barrier does so with an iteration limit and, when the limit runs
+ * out, records a status code and returns instead of spinning. This launches a one-warp kernel whose wait cannot be
+ * satisfied and gives up after `spins` polls (1 .. 65536, milliseconds at most): the next infdev_commit must return
+ * INFDEV_E_DEVICE, and the one after it INFDEV_OK, with the context fully usable. Nothing faults or hangs. */
+int infdev_check_abort_path(infdev_ctx* ctx, uint32_t spins);
 /* Timing on the context's stream. */
 void* infdev_event_create(infdev_ctx* ctx);
 void infdev_event_destroy(infdev_ctx* ctx, void* event);

@@ -23,13 +23,20 @@ typedef struct infeng_sequence infeng_sequence;
  * receive the message when the call returns NULL. Environment: INFENG_DEVICE (GPU index, default LOCAL_RANK or
  * 0), INFENG_KV_BLOCKS (physical 128-token K/V blocks, default ceil(context/128) as engine.cpp:86),
  * INFENG_DRAFT_WIDTH (MTP proposals per step, default 2 as forward.cpp:139), INFENG_SEED (base of the sampling
- * keys: sequence number i of an engine draws from a Philox stream keyed by (seed, i); default the clock), INFENG_BLOCK_TOKENS, INFENG_COMMIT_TIMEOUT_MS, INFENG_GRAPHS (0 disables CUDA-graph replay of decode passes). */
+ * keys: sequence number i of an engine draws from a Philox stream keyed by (seed, i); default the clock), INFENG_CHECKPOINTS (entries of the prefix-checkpoint cache, default 8 as qwen35.hpp:24; each holds one state record),
+ * INFENG_BLOCK_TOKENS, INFENG_COMMIT_TIMEOUT_MS, INFENG_GRAPHS (0 disables CUDA-graph replay of decode passes). */
 infeng_engine* infeng_engine_create(const char* weights, const char* draftWeights, const char* kernels, uint32_t context, char* error);
 /* engine.cpp:251-254: drops one reference; the engine dies with its last sequence. */
 void infeng_engine_release(infeng_engine* engine);
 /* engine.cpp:256-259: takes the first free of 8 slots; NULL + "maximum live sequence count reached" when none. */
 infeng_sequence* infeng_sequence_create(infeng_engine* engine, const int32_t* stops, uint32_t stopCount, float temperature, float topP, int32_t topK,
                                         uint32_t speculative, char* error);
+/* No counterpart in the reference (its generator is seeded from the clock, engine.cpp:96-99). Gives the sequence a
+ * sampling key of the client's choice instead of the one derived from the engine's base seed and the creation order:
+ * with the same key, prompt and sampling parameters a sequence emits the same tokens whatever slot it holds and
+ * whatever else is batched with it (the variate of its i-th token is Philox(key, i)). To be called before the first
+ * append; returns 0, or -3 once the sequence has started generating. */
+int32_t infeng_sequence_seed(infeng_sequence* sequence, uint64_t seed);
 /* engine.cpp:261-265: waits for the in-flight pass of the sequence, frees its slot and K/V references. */
 void infeng_sequence_release(infeng_sequence* sequence);
 /* engine.cpp:267-284: appends prompt tokens and starts generation; returns the new token count (the first
@@ -44,7 +51,9 @@ int32_t infeng_sequence_read(infeng_sequence* sequence, uint32_t cursor);
  * 4 draft width. Additions for throughput accounting: 5 passes run, 6 rows processed, 7 microseconds spent in
  * passes (host clock, commit included), 8 decoder layers, 9 vocabulary size, 10 nanoseconds of device time of
  * the passes (CUDA events on the stream), 11 kernels launched, 12 to 14 microseconds the scheduler spent outside
- * the passes: building batches, waiting for the engine lock after a pass, handing sampled tokens over. */
+ * the passes: building batches, waiting for the engine lock after a pass, handing sampled tokens over, 15 rows of
+ * prompt chunks among the rows of field 6 (prompt tokens restored from the prefix-checkpoint cache are not computed
+ * and do not count). */
 uint64_t infeng_engine_info(infeng_engine* engine, uint32_t field);
 /* engine.cpp:299-303: 0 drafted tokens, 1 accepted tokens, 2 tokens held in the K/V cache. Additions: 3 position of
  * the anchor token of the sequence's latest speculative step, 4 .. 4 + draft width - 1 the drafter's proposals of

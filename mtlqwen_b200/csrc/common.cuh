@@ -60,6 +60,9 @@ template <class Kernel> cudaError_t configure_shared_memory(Kernel kernel, size_
   if (once.done[device].load(std::memory_order_acquire))
     return cudaSuccess;
   e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes));
+  // Ask for the largest shared-memory carve-out: kernels sized for two CTAs per SM get both only with all of it.
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, int(cudaSharedmemCarveoutMaxShared));
   if (e == cudaSuccess)
     once.done[device].store(1, std::memory_order_release);
   return e;
@@ -113,10 +116,10 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 
 // Waits for a phase with an iteration limit. Returns false when the limit ran out; the caller then
 // raises the abort flag so every role of the kernel leaves its loops instead of spinning forever.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abortFlag) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abortFlag, uint32_t limit = 1u << 20) {
   if (mbar_test_wait(bar, parity))  // the common case: the phase has already completed
     return true;
-  for (uint32_t spin = 0; spin < (1u << 20); ++spin) {
+  for (uint32_t spin = 0; spin < limit; ++spin) {
     if (mbar_try_wait(bar, parity))
       return true;
     if ((spin & 1023u) == 1023u && *abortFlag)

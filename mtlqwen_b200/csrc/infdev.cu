@@ -310,6 +310,14 @@ int infdev_commit(infdev_ctx* ctx, uint32_t timeoutMs) {
   return INFDEV_OK;
 }
 
+int infdev_check_abort_path(infdev_ctx* ctx, uint32_t spins) {
+  Bind bind(ctx);
+  if (!spins || spins > (1u << 16))
+    return fail(ctx, INFDEV_E_ARGUMENT, "check_abort_path: 1 to 65536 polls");
+  ctx->launches += 1;
+  return check(ctx, infdev::bounded_wait_probe_launch(spins, ctx->status, ctx->stream), "check_abort_path");
+}
+
 void* infdev_event_create(infdev_ctx* ctx) {
   Bind bind(ctx);
   cudaEvent_t event = nullptr;

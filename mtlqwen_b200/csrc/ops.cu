@@ -196,7 +196,9 @@ __global__ void __launch_bounds__(256) mtp_fuse_kernel(const float* embedding, c
   const uint32_t token = row - info.start;
   const float* seed = reinterpret_cast<const float*>(info.previous + seedOffset);
   const float* h = mode == 2 ? seed : (mode == 1 && !token) ? seed : hidden + size_t(mode == 1 ? row - 1 : row) * 4096;
-  const bool initial = !info.previous && token == 0;
+  // Without a predecessor record there is no seed to read: the first row of a fresh sequence (`initial`,
+  // native_ops.metal:57), and every row that would take the seed in a frame the engine never builds that way.
+  const bool initial = !info.previous && (token == 0 || mode == 2);
   __shared__ float sums[18];
   float es = 0.f, hs = 0.f;
   for (int d = tid; d < 4096; d += 256) {
@@ -233,7 +235,33 @@ __global__ void __launch_bounds__(256) mtp_fuse_kernel(const float* embedding, c
   }
 }
 
+// Health check of the abort path every waiting kernel shares: one thread waits, with an iteration limit, for a barrier
+// phase that cannot complete (two arrivals expected, one made). The wait must give up, raise the abort flag and leave
+// kStatusBarrierTimeout in the status word; the kernel returns normally and the context stays usable.
+__global__ void bounded_wait_probe_kernel(uint32_t limit, int* status) {
+  __shared__ uint64_t barrier;
+  __shared__ int abortFlag;
+  if (threadIdx.x == 0) {
+    mbar_init(&barrier, 2);
+    abortFlag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    mbar_arrive(&barrier);
+    if (!mbar_wait_bounded(&barrier, 0, &abortFlag, limit)) {
+      abortFlag = 1;
+      atomicExch(status, kStatusBarrierTimeout);
+    }
+  }
+}
+
 }  // namespace
+
+cudaError_t bounded_wait_probe_launch(uint32_t limit, int* status, cudaStream_t stream) {
+  bounded_wait_probe_kernel<<<1, 32, 0, stream>>>(limit, status);
+  return cudaGetLastError();
+}
 
 cudaError_t mtp_fuse_launch(const float* embedding, const float* hidden, const infdev_query* queries, const float* enorm, const float* hnorm,
                             int64_t rows, uint32_t mode, uint64_t seedOffset, uint64_t stateBytes, float* y, cudaStream_t stream) {

@@ -6,6 +6,7 @@
 
 namespace infdev {
 
+cudaError_t bounded_wait_probe_launch(uint32_t limit, int* status, cudaStream_t stream);
 cudaError_t dequant_launch(int type, const void* blocks, int64_t count, float* out, cudaStream_t stream);
 cudaError_t embedding_launch(int type, const void* table, int64_t k, const int32_t* tokens, int64_t rows, float* out, cudaStream_t stream);
 cudaError_t gather_tokens_launch(const infdev_query* queries, int queryCount, const int32_t* requestData, uint32_t capacity,

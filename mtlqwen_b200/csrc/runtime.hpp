@@ -21,7 +21,7 @@ namespace infeng::qwen35 {
 inline constexpr uint32_t hiddenSize = 4096, intermediateSize = 12288, fullAttentionInterval = 4;
 inline constexpr uint32_t maxDraftTokens = 7, maxBatchSequences = 8, maxBatchTokens = 128;
 inline constexpr uint32_t maxLogitRows = maxBatchSequences * (maxDraftTokens + 1);
-inline constexpr uint32_t checkpointTokens = 512, maxCheckpoints = 8, maxAttentionSplits = 32;
+inline constexpr uint32_t checkpointTokens = 512, maxAttentionSplits = 32;
 inline constexpr uint32_t maxStopTokens = 64;  // per sequence: the stop lists live in a device-visible table
 inline constexpr uint32_t unbound = UINT32_MAX;
 inline constexpr uint64_t seedBytes = hiddenSize * sizeof(float);  // MTP seed (last target hidden) at the end of a state record
@@ -71,6 +71,7 @@ struct Engine {
   Device device;
   uint32_t maxContext, draftWidth = 0;
   uint32_t targetLayers = 0, kvLayers = 0, gdnLayers = 0, vocab = 0, blockTokens = 128;
+  uint32_t maxCheckpoints = 8;  // entries of the prefix-checkpoint cache (qwen35.hpp:24); INFENG_CHECKPOINTS overrides
   uint64_t stateBytes = 0;
   std::unique_ptr<PagedKV> kv;
   Weights weights;
@@ -102,6 +103,7 @@ struct Engine {
   uint64_t parameterCount = 0, modelBytes = 0;
   // step counters for roofline reporting
   std::atomic_uint64_t passes{0}, passRows{0}, passMicros{0}, passDeviceNanos{0};
+  std::atomic_uint64_t prefillRows{0};  // rows of prompt chunks among passRows (what a prefix-cache hit saves)
   // host microseconds of the scheduler outside the passes: building a batch, waiting for the engine lock after a
   // pass, handing the sampled tokens over
   std::atomic_uint64_t buildMicros{0}, lockMicros{0}, publishMicros{0};
@@ -120,6 +122,7 @@ struct Engine {
   bool reserve(const Batch& batch);
   void bind(Sequence& sequence, uint32_t physical);
   void restorePrefix(Sequence& sequence);
+  bool waitsForSibling(const Sequence& sequence) const;
   void publishPrefix(Sequence& sequence);
   void retire(Tensor& state);
   Tensor freshState();

@@ -106,13 +106,17 @@ Tensor Engine::freshState() {
   return state;
 }
 
-// Finds the deepest published prefix of the request and adopts its state arena and K/V bindings
-// (Engine::restorePrefix, engine.cpp:48-68). The match is by chained hash only.
+// Finds the deepest published prefix of the request beyond what the sequence already holds and adopts its state arena
+// and K/V bindings (Engine::restorePrefix, engine.cpp:48-68). The match is by chained hash only. The reference looks
+// once, before a sequence's first pass; here a sequence looks again at every 512-token boundary of its prompt, so it
+// also picks up checkpoints that another sequence published while both were being prefilled.
 void Engine::restorePrefix(Sequence& sequence) {
-  uint64_t hash = 0;
+  if (sequence.kvValid % checkpointTokens || sequence.bindings.size() != sequence.kvValid / blockTokens)
+    return;
+  uint64_t hash = sequence.prefixHash;
   auto best = checkpointCache.end();
   const uint32_t fullBlocks = (sequence.requested - 1) / checkpointTokens;
-  for (uint32_t index = 0; index < fullBlocks; ++index) {
+  for (uint32_t index = sequence.kvValid / checkpointTokens; index < fullBlocks; ++index) {
     hash = hashCheckpoint(hash, sequence.request + uint64_t(index) * checkpointTokens);
     for (auto entry = checkpointCache.begin(); entry != checkpointCache.end(); ++entry)
       if (entry->hash == hash) {
@@ -120,18 +124,40 @@ void Engine::restorePrefix(Sequence& sequence) {
         break;
       }
   }
-  if (best == checkpointCache.end())
+  if (best == checkpointCache.end() || best->bindings.size() <= sequence.bindings.size())
     return;
   checkpointCache.splice(checkpointCache.end(), checkpointCache, best);
   sequence.prefixHash = best->hash;
   const uint64_t touch = ++clock;
   retire(statePool[sequence.slot].first);
   statePool[sequence.slot].first = best->arena;
-  for (uint32_t physical : best->bindings) {
-    bind(sequence, physical);
-    blocks[physical].touch = touch;
+  for (size_t logical = sequence.bindings.size(); logical < best->bindings.size(); ++logical) {  // bind() appends one
+    bind(sequence, best->bindings[logical]);
+    blocks[best->bindings[logical]].touch = touch;
   }
   sequence.kvValid = uint32_t(best->bindings.size()) * blockTokens;
+}
+
+// True when another live sequence is right now computing the very 512-token block this sequence would compute next
+// (same prefix, same tokens) and is ahead of it, or level with it in a lower slot. The sequence then sits this pass
+// out: when the other one reaches the boundary it publishes the checkpoint, and restorePrefix picks it up. A prefix
+// shared by several requests that arrive together is thus computed once, with the whole row budget, instead of once
+// per request in lockstep. (No counterpart in the reference, which lets them all compute it.)
+bool Engine::waitsForSibling(const Sequence& sequence) const {
+  const uint32_t boundary = sequence.kvValid;
+  if (boundary % checkpointTokens || (sequence.requested - 1) / checkpointTokens <= boundary / checkpointTokens)
+    return false;
+  for (const Sequence* other : sequences) {
+    if (!other || other == &sequence || !other->active || other->kvValid < boundary || other->kvValid >= boundary + checkpointTokens)
+      continue;
+    if ((other->requested - 1) / checkpointTokens <= boundary / checkpointTokens || other->prefixHash != sequence.prefixHash)
+      continue;
+    if (other->kvValid == boundary && other->slot > sequence.slot)
+      continue;
+    if (!std::memcmp(other->request + boundary, sequence.request + boundary, checkpointTokens * sizeof(int32_t)))
+      return true;
+  }
+  return false;
 }
 
 // Publishes the sequence's state at every 512-token boundary (Engine::publishPrefix, engine.cpp:70-83).
@@ -144,7 +170,7 @@ void Engine::publishPrefix(Sequence& sequence) {
       checkpointCache.splice(checkpointCache.end(), checkpointCache, entry);
       return;
     }
-  if (checkpointCache.size() == maxCheckpoints) {
+  if (checkpointCache.size() >= maxCheckpoints) {
     retire(checkpointCache.front().arena);
     checkpointCache.pop_front();
   }
@@ -158,6 +184,7 @@ Engine::Engine(const std::filesystem::path& path, uint32_t context, const std::f
     throw std::runtime_error("INFENG_BLOCK_TOKENS must be a multiple of 16 that divides 512");
   device.commitTimeoutMs = environment("INFENG_COMMIT_TIMEOUT_MS", 120000);
   useGraphs = environment("INFENG_GRAPHS", 1) != 0;
+  maxCheckpoints = std::max(1u, environment("INFENG_CHECKPOINTS", 8));
   // The reference sizes the physical pool for one sequence of maximum context (engine.cpp:86); INFENG_KV_BLOCKS overrides.
   const uint32_t perSlot = (context + blockTokens - 1) / blockTokens;
   blocks.resize(environment("INFENG_KV_BLOCKS", perSlot));
@@ -257,9 +284,10 @@ void Engine::schedule() {
     for (Sequence* sequence : sequences) {
       if (!ready(sequence))
         continue;
+      restorePrefix(*sequence);
+      if (waitsForSibling(*sequence))
+        continue;
       sequence->busy = true;
-      if (!sequence->kvValid)
-        restorePrefix(*sequence);
       // The output state must not be an arena that a checkpoint still shares.
       if (statePool[sequence->slot].second.buffer.use_count() > 1)
         statePool[sequence->slot].second = freshState();
@@ -293,6 +321,10 @@ void Engine::schedule() {
       infdev_query& query = *prefills[i];
       query.count = std::min(query.count, remaining / (prefillCount - i));
       remaining -= query.count;
+    }
+    if (!batch.size) {  // every ready sequence waits for a sibling that stopped being ready meanwhile: look again shortly
+      condition.wait_for(lock, std::chrono::milliseconds(1));
+      continue;
     }
     bool success = reserve(batch);
     lock.unlock();
@@ -340,6 +372,9 @@ void Engine::schedule() {
         passDeviceNanos += uint64_t(double(infdev_event_elapsed_ms(device.ctx, passEvents[0], passEvents[1])) * 1.0e6);
         passMicros += uint64_t(std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - started).count());
         passRows += shape.rows;
+        for (uint32_t i = 0; i < batch.size; ++i)
+          if (batch.queries[i].state == unbound && batch.queries[i].count > 1)
+            prefillRows += batch.queries[i].count;
         ++passes;
       } catch (const std::exception&) {
         success = false;  // a device failure is reported to every sequence of the batch like a capacity failure
@@ -438,6 +473,15 @@ infeng_sequence* infeng_sequence_create(infeng_engine* engine, const int32_t* st
   }
 }
 
+int32_t infeng_sequence_seed(infeng_sequence* sequence, uint64_t seed) {
+  Engine& engine = sequence->engine;
+  std::lock_guard<std::mutex> lock(engine.mutex);
+  if (sequence->active || sequence->busy || sequence->requested)
+    return -3;
+  engine.seeds[sequence->slot] = mixSeed(seed);
+  return 0;
+}
+
 void infeng_sequence_release(infeng_sequence* sequence) {
   infeng_engine* engine = static_cast<infeng_engine*>(&sequence->engine);
   delete sequence;
@@ -494,6 +538,7 @@ uint64_t infeng_engine_info(infeng_engine* engine, uint32_t field) {
     case 12: return engine->buildMicros.load();
     case 13: return engine->lockMicros.load();
     case 14: return engine->publishMicros.load();
+    case 15: return engine->prefillRows.load();
     default: return 0;
   }
 }

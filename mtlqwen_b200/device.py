@@ -49,6 +49,7 @@ def library():
     "infdev_copy": (i32, (vp, vp, vp, ctypes.c_size_t)),
     "infdev_fill": (i32, (vp, vp, i32, ctypes.c_size_t)),
     "infdev_commit": (i32, (vp, u32)),
+    "infdev_check_abort_path": (i32, (vp, u32)),
     "infdev_event_create": (vp, (vp, )),
     "infdev_event_destroy": (None, (vp, vp)),
     "infdev_event_record": (i32, (vp, vp)),

@@ -27,6 +27,7 @@ def bind(path):
   lib.infeng_sequence_read.argtypes, lib.infeng_sequence_read.restype = (void, ctypes.c_uint32), ctypes.c_int32
   lib.infeng_engine_info.argtypes, lib.infeng_engine_info.restype = (void, ctypes.c_uint32), ctypes.c_uint64
   lib.infeng_sequence_info.argtypes, lib.infeng_sequence_info.restype = (void, ctypes.c_uint32), ctypes.c_uint64
+  lib.infeng_sequence_seed.argtypes, lib.infeng_sequence_seed.restype = (void, ctypes.c_uint64), ctypes.c_int32
   lib.infeng_sequence_state.argtypes, lib.infeng_sequence_state.restype = (void, ctypes.c_uint64, void, ctypes.c_uint64), ctypes.c_int64
   return lib
 
@@ -52,13 +53,15 @@ def _check(value, error=None):
 
 class Sequence:
 
-  def __init__(self, engine, stop_token_ids, temperature, top_p, top_k, speculative):
+  def __init__(self, engine, stop_token_ids, temperature, top_p, top_k, speculative, seed=None):
     self.engine, self.handle = engine, 0
     self.stop_token_ids, self.speculative = frozenset(stop_token_ids), bool(speculative and engine.draft_width)
     stops = (ctypes.c_int32 * len(stop_token_ids))(*stop_token_ids)
     error = ctypes.create_string_buffer(1024)
     self.handle = _check(self.engine.lib.infeng_sequence_create(engine.handle, stops, len(stops), temperature, top_p, top_k or 0, self.speculative, error),
                          error)
+    if seed is not None:
+      _check(self.engine.lib.infeng_sequence_seed(self.handle, seed))
 
   def append(self, tokens=()):
     ids = (ctypes.c_int32 * len(tokens))(*tokens)
@@ -117,8 +120,9 @@ class InferenceEngine:
     self.parameter_count = self.lib.infeng_engine_info(self.handle, 0)
     self.weight_bytes = self.lib.infeng_engine_info(self.handle, 1)
 
-  def sequence(self, *, stop_token_ids=None, temperature=0.0, top_p=1.0, top_k=None, speculative=False):
-    return Sequence(self, list(stop_token_ids or ()), temperature, top_p, top_k, speculative)
+  def sequence(self, *, stop_token_ids=None, temperature=0.0, top_p=1.0, top_k=None, speculative=False, seed=None):
+    """seed (an addition to the reference's signature): a sampling key of the caller's choice, for reproducible requests."""
+    return Sequence(self, list(stop_token_ids or ()), temperature, top_p, top_k, speculative, seed)
 
   @property
   def mapped_bytes(self):
@@ -131,7 +135,8 @@ class InferenceEngine:
     return {"passes": self.lib.infeng_engine_info(self.handle, 5), "rows": self.lib.infeng_engine_info(self.handle, 6),
             "micros": self.lib.infeng_engine_info(self.handle, 7), "device_ns": self.lib.infeng_engine_info(self.handle, 10),
             "launches": self.lib.infeng_engine_info(self.handle, 11), "build_micros": self.lib.infeng_engine_info(self.handle, 12),
-            "lock_micros": self.lib.infeng_engine_info(self.handle, 13), "publish_micros": self.lib.infeng_engine_info(self.handle, 14)}
+            "lock_micros": self.lib.infeng_engine_info(self.handle, 13), "publish_micros": self.lib.infeng_engine_info(self.handle, 14),
+            "prefill_rows": self.lib.infeng_engine_info(self.handle, 15)}
 
   def close(self):
     if getattr(self, "handle", 0): self.lib.infeng_engine_release(self.handle)

@@ -12,17 +12,24 @@ import numpy as np
 
 
 def route(prompts, world):
-  """Assigns each token-id prompt to a replica: streams with the same first 512 tokens share a replica, and
-  prefix groups are dealt out largest-first onto the least-loaded replica."""
+  """Assigns each token-id prompt to a replica. Streams with the same first 512 tokens stay together, so that the
+  replica's prefix cache is hit, as long as that does not give one replica more than its fair share
+  ceil(streams / world): a larger group is cut into pieces of that size and each replica that gets a piece computes
+  the shared prefix once. Pieces are dealt out largest-first onto the least-loaded replica."""
   groups = {}
   for index, prompt in enumerate(prompts):
     head = np.asarray(prompt[:512], dtype=np.int32).tobytes()
     groups.setdefault(hashlib.blake2b(head, digest_size=8).digest(), []).append(index)
+  share = max(1, -(-len(prompts) // world))
+  pieces = []
+  for key in sorted(groups):
+    members = groups[key]
+    pieces += [members[at:at + share] for at in range(0, len(members), share)]
   load, assignment = [0] * world, [[] for _ in range(world)]
-  for key in sorted(groups, key=lambda k: (-len(groups[k]), k)):
+  for piece in sorted(pieces, key=lambda p: (-len(p), p[0])):
     target = min(range(world), key=lambda r: (load[r], r))
-    assignment[target] += groups[key]
-    load[target] += len(groups[key])
+    assignment[target] += piece
+    load[target] += len(piece)
   return assignment
 
 

@@ -276,3 +276,15 @@ class Model:
     lib().orc_mtp_step(ctypes.byref(self._model), ctypes.byref(self._state), ctypes.c_int32(int(token)), _p(previous), ctypes.c_int32(int(position)),
                        ctypes.c_int32(int(store_only)), _p(hidden), _p(logits))
     return hidden, logits
+
+
+def decode_batch(models, tokens, want_logits=True):
+  """One decode step of several sequences of the same weights in one pass (orc_model_decode_batch): `models` are
+  Model instances built from the same tensors; returns (hidden [B,4096], logits [B,vocab] or None)."""
+  count = len(models)
+  states = (ctypes.POINTER(_State) * count)(*[ctypes.pointer(m._state) for m in models])
+  ids = np.ascontiguousarray(tokens, dtype=np.int32)
+  hidden = np.empty((count, 4096), np.float32)
+  logits = np.empty((count, models[0].vocab), np.float32) if want_logits else None
+  lib().orc_model_decode_batch(ctypes.byref(models[0]._model), states, _p(ids), _i64(count), _p(hidden), _p(logits))
+  return hidden, logits

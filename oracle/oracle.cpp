@@ -510,19 +510,16 @@ struct OrcState {
 
 namespace {
 
-// Gated full attention of Ops::decoder (forward.cpp:84-96) for T rows at positions pos .. pos + T - 1 of one
-// sequence: q/k/v projections, attention_prepare, cache append (attention.metal:126-133), causal softmax over the
-// cache, sigmoid gate, output projection added to h. keys / values: this layer's [maxContext][1024] cache.
-void attention_rows(const OrcModel* model, const OrcLayer& w, float* keys, float* values, int pos, int64_t T, const float* x, float* h) {
-  const int64_t H = 4096;
-  std::vector<float> qg(T * 8192), k(T * 1024), v(T * 1024), q(T * 4096), kr(T * 1024), o(T * 4096), y(T * H);
+// The per-sequence part of gated full attention (forward.cpp:89-95) for T rows at positions pos .. pos + T - 1:
+// attention_prepare, cache append (attention.metal:126-133), causal softmax over the cache, sigmoid gate. qg [T,8192],
+// k, v [T,1024] are the projections of the rows; o [T,4096]. keys / values: this layer's [maxContext][1024] cache.
+void attention_core(const OrcModel* model, const OrcLayer& w, float* keys, float* values, int pos, int64_t T, const float* qg, const float* k,
+                    const float* v, float* o) {
+  std::vector<float> q(T * 4096), kr(T * 1024);
   std::vector<int32_t> positions(T);
   for (int64_t t = 0; t < T; ++t)
     positions[t] = pos + int32_t(t);
-  orc_linear(w.wq, model->projType, 8192, H, x, T, qg.data(), nullptr);
-  orc_linear(w.wk, model->projType, 1024, H, x, T, k.data(), nullptr);
-  orc_linear(w.wv, model->projType, 1024, H, x, T, v.data(), nullptr);
-  orc_attention_prepare(qg.data(), k.data(), w.qNorm, w.kNorm, model->rope, positions.data(), T, q.data(), kr.data());
+  orc_attention_prepare(qg, k, w.qNorm, w.kNorm, model->rope, positions.data(), T, q.data(), kr.data());
   for (int64_t t = 0; t < T; ++t)
     for (int i = 0; i < 1024; ++i) {
       keys[size_t(pos + t) * 1024 + i] = half_round(kr[t * 1024 + i]);
@@ -552,23 +549,41 @@ void attention_rows(const OrcModel* model, const OrcLayer& w, float* keys, float
       for (int d = 0; d < 256; ++d)
         o[(t * 16 + head) * 256 + d] = float(numerator[d] / norm) * sigmoid(qg[(t * 16 + head) * 512 + 256 + d]);
     }
+}
+
+// Gated full attention of Ops::decoder (forward.cpp:84-96) for T rows of one sequence: q/k/v projections, the
+// per-sequence part above, output projection added to h.
+void attention_rows(const OrcModel* model, const OrcLayer& w, float* keys, float* values, int pos, int64_t T, const float* x, float* h) {
+  const int64_t H = 4096;
+  std::vector<float> qg(T * 8192), k(T * 1024), v(T * 1024), o(T * 4096), y(T * H);
+  orc_linear(w.wq, model->projType, 8192, H, x, T, qg.data(), nullptr);
+  orc_linear(w.wk, model->projType, 1024, H, x, T, k.data(), nullptr);
+  orc_linear(w.wv, model->projType, 1024, H, x, T, v.data(), nullptr);
+  attention_core(model, w, keys, values, pos, T, qg.data(), k.data(), v.data(), o.data());
   orc_linear(w.wo, model->projType, H, H, o.data(), T, y.data(), h);
   std::memcpy(h, y.data(), size_t(T) * H * 4);
 }
 
-// Gated delta network of Ops::decoder (forward.cpp:97-107) for T rows: projections, beta / g, causal conv with the
-// carried taps, the sequential delta rule, gated norm, output projection added to h.
-void gdn_rows(const OrcModel* model, const OrcLayer& w, float* convState, float* S, bool fresh, int64_t T, const float* x, float* h) {
-  const int64_t H = 4096;
-  std::vector<float> mixed(T * 8192), z(T * H), beta(T * 32), g(T * 32), q(T * 2048), k(T * 2048), v(T * 4096), o(T * 4096), gated(T * 4096),
-      conv(8192 * 4), y(T * H);
-  orc_linear(w.wqkv, model->projType, 8192, H, x, T, mixed.data(), nullptr);
-  orc_linear(w.wz, model->projType, H, H, x, T, z.data(), nullptr);
+// The per-sequence part of a gated delta network layer (forward.cpp:99-106) for T rows: beta / g, causal conv with the
+// carried taps, the sequential delta rule, gated norm. x [T,4096] normalised hidden, mixed [T,8192], z [T,4096]
+// projections; gated [T,4096] is what the output projection takes.
+void gdn_core(const OrcLayer& w, float* convState, float* S, bool fresh, int64_t T, const float* x, const float* mixed, const float* z,
+              float* gated) {
+  std::vector<float> beta(T * 32), g(T * 32), q(T * 2048), k(T * 2048), v(T * 4096), o(T * 4096), conv(8192 * 4);
   orc_gdn_ba(x, w.wBeta, w.wAlpha, w.ssmA, w.ssmDt, T, beta.data(), g.data());
-  orc_gdn_conv(mixed.data(), w.conv, fresh ? nullptr : convState, T, q.data(), k.data(), v.data(), conv.data(), 0);
+  orc_gdn_conv(mixed, w.conv, fresh ? nullptr : convState, T, q.data(), k.data(), v.data(), conv.data(), 0);
   std::memcpy(convState, conv.data(), conv.size() * 4);
   orc_delta_rule(q.data(), k.data(), v.data(), g.data(), beta.data(), T, S, o.data(), nullptr);
-  orc_gated_rms_norm(o.data(), z.data(), w.ssmNorm, T * 32, gated.data());
+  orc_gated_rms_norm(o.data(), z, w.ssmNorm, T * 32, gated);
+}
+
+// Gated delta network of Ops::decoder (forward.cpp:97-107) for T rows of one sequence.
+void gdn_rows(const OrcModel* model, const OrcLayer& w, float* convState, float* S, bool fresh, int64_t T, const float* x, float* h) {
+  const int64_t H = 4096;
+  std::vector<float> mixed(T * 8192), z(T * H), gated(T * 4096), y(T * H);
+  orc_linear(w.wqkv, model->projType, 8192, H, x, T, mixed.data(), nullptr);
+  orc_linear(w.wz, model->projType, H, H, x, T, z.data(), nullptr);
+  gdn_core(w, convState, S, fresh, T, x, mixed.data(), z.data(), gated.data());
   orc_linear(w.wout, model->projType, H, H, gated.data(), T, y.data(), h);
   std::memcpy(h, y.data(), size_t(T) * H * 4);
 }
@@ -624,6 +639,51 @@ void orc_model_forward(const OrcModel* model, OrcState* state, const int32_t* to
 // One token (the decode step): orc_model_forward with T = 1.
 void orc_model_step(const OrcModel* model, OrcState* state, int32_t token, float* hidden, float* logits) {
   orc_model_forward(model, state, &token, 1, hidden, logits ? 1 : 0, logits);
+}
+
+// One decode step of B sequences in one pass, the way the engine batches them: every projection runs once over the
+// B stacked rows (so a weight row is dequantised once for all of them, as the GEMV kernels read it once), the
+// recurrent and attention parts run per sequence. Row b gets the same bits as orc_model_step on states[b] alone.
+// hidden (nullable) [B][4096], logits (nullable) [B][vocab].
+void orc_model_decode_batch(const OrcModel* model, OrcState* const* states, const int32_t* tokens, int64_t B, float* hidden, float* logits) {
+  const int64_t H = 4096;
+  std::vector<float> h(B * H), x(B * H), y(B * H);
+  orc_embedding(model->embd, model->embdType, H, tokens, B, h.data());
+  int gdn = 0, att = 0;
+  for (int L = 0; L < model->layers; ++L) {
+    const OrcLayer& w = model->layer[L];
+    orc_rms_norm(h.data(), w.attnNorm, B, H, 1.0e-6f, x.data());
+    if ((L + 1) % 4 == 0) {
+      std::vector<float> qg(B * 8192), k(B * 1024), v(B * 1024), o(B * 4096);
+      orc_linear(w.wq, model->projType, 8192, H, x.data(), B, qg.data(), nullptr);
+      orc_linear(w.wk, model->projType, 1024, H, x.data(), B, k.data(), nullptr);
+      orc_linear(w.wv, model->projType, 1024, H, x.data(), B, v.data(), nullptr);
+      for (int64_t b = 0; b < B; ++b)
+        attention_core(model, w, states[b]->keys + size_t(att) * model->maxContext * 1024, states[b]->values + size_t(att) * model->maxContext * 1024,
+                       states[b]->length, 1, qg.data() + b * 8192, k.data() + b * 1024, v.data() + b * 1024, o.data() + b * 4096);
+      orc_linear(w.wo, model->projType, H, H, o.data(), B, y.data(), h.data());
+      ++att;
+    } else {
+      std::vector<float> mixed(B * 8192), z(B * H), gated(B * 4096);
+      orc_linear(w.wqkv, model->projType, 8192, H, x.data(), B, mixed.data(), nullptr);
+      orc_linear(w.wz, model->projType, H, H, x.data(), B, z.data(), nullptr);
+      for (int64_t b = 0; b < B; ++b)
+        gdn_core(w, states[b]->conv + size_t(gdn) * 8192 * 4, states[b]->S + size_t(gdn) * 32 * 128 * 128, states[b]->length == 0, 1, x.data() + b * H,
+                 mixed.data() + b * 8192, z.data() + b * H, gated.data() + b * 4096);
+      orc_linear(w.wout, model->projType, H, H, gated.data(), B, y.data(), h.data());
+      ++gdn;
+    }
+    h = y;
+    mlp_rows(model, w, B, h.data());
+  }
+  for (int64_t b = 0; b < B; ++b)
+    ++states[b]->length;
+  if (hidden)
+    std::memcpy(hidden, h.data(), size_t(B) * H * 4);
+  if (logits) {
+    orc_rms_norm(h.data(), model->outputNorm, B, H, 1.0e-6f, x.data());
+    orc_linear(model->output, model->outType, model->vocab, H, x.data(), B, logits, nullptr);
+  }
 }
 
 // ---- MTP drafter -----------------------------------------------------------------------------

@@ -94,6 +94,35 @@ def test_integer_kernel_with_outliers_and_zero_blocks(dev):
   assert rel_err(got, want) < TOL
 
 
+def test_integer_kernel_with_one_large_outlier_per_block(dev):
+  """The worst case of the 16-bit activation grid: every 256-value block holds one value of 1e4 among values of
+  order one, as the residual stream of a real model does, so the grid step of the block is 1e4 / 32767 = 0.31 and
+  the small values keep about two bits. The outlier's own contribution is exact; what the grid costs is judged on
+  its own: against the oracle run on the activations without the outliers, the error the kernel adds must stay
+  within the rounding bound of the grid, sqrt(k) * step / sqrt(12) * |w|, and this is recorded here as the limit
+  of the scheme: such a block is represented to 0.3 absolute, not to 1e-3 of its small values."""
+  n, k, m = 256, 4096, 4
+  rng = np.random.default_rng(5)
+  w = synth.weight(D.Q4_K, n, k, 91)
+  small = synth.activations(m, k, 92)
+  x = small.copy()
+  spots = np.arange(0, k, 256) + rng.integers(0, 256, k // 256)
+  x[:, spots] = 1.0e4
+  got, want = run_linear(dev, D.Q4_K, n, k, m, 0, x=x, w=w)
+  assert rel_err(got, want) < TOL  # dominated by the outliers, as the norm-wise metric is
+  # the part of the result that the small values contribute
+  only_outliers = np.zeros_like(x)
+  only_outliers[:, spots] = 1.0e4
+  contribution = got - oracle.linear(w, D.Q4_K, n, k, only_outliers)
+  want_small = oracle.linear(w, D.Q4_K, n, k, small - np.where(only_outliers > 0, small, 0).astype(np.float32))
+  dense = oracle.dequant(w, D.Q4_K).reshape(n, k)
+  step = 1.0e4 / 32767.0
+  bound = 5.0 * np.sqrt(k / 12.0) * step * np.sqrt((dense**2).mean())  # five standard deviations of the rounding noise
+  error = np.abs(contribution - want_small)
+  assert error.max() <= bound, (float(error.max()), float(bound))
+  assert error.max() > 1e-3 * np.abs(want_small).max()  # and it is not small: the grid, not the arithmetic, sets it
+
+
 @pytest.mark.parametrize("qtype,n,k,m", [
   (D.Q4_K, 16, 256, 1),  # one tile, one super-block: most consumer warps idle
   (D.Q4_K, 48, 768, 3),  # partial stage (3 super-blocks)

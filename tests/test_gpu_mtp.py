@@ -50,7 +50,7 @@ def test_mtp_fuse_three_modes_match_the_oracle(dev):
     for i, q in enumerate(queries):
       for token in range(q.count):
         row = q.start + token
-        if mode == 2:
+        if mode == 2:  # drafting, step 0: the stored seed (a record without predecessor has none)
           h = seeds[i] if q.previous else None
         elif mode == 1:
           h = (seeds[i] if q.previous else None) if token == 0 else hidden[row - 1]
@@ -86,9 +86,9 @@ def test_drafter_proposals_match_the_oracle_teacher_forced(weights):
   try:
     sequence = engine.sequence(speculative=True)
     prompt = [int(t) for t in np.random.default_rng(5).integers(0, VOCAB, 150)]  # two prefill passes, then speculative steps
-    tokens, steps = list(prompt), []
+    tokens, steps, drafted = list(prompt), [], 0
     cursor = sequence.append(prompt)
-    for _ in range(10):
+    for _ in range(12):
       # one token, then stop the sequence and collect whatever the passes in flight still emitted
       token = sequence.read(cursor)
       assert token is not None
@@ -98,9 +98,9 @@ def test_drafter_proposals_match_the_oracle_teacher_forced(weights):
       while (token := sequence.read(cursor)) is not None:
         tokens.append(token)
         cursor += 1
-      anchor, proposals = sequence.draft_step()
-      if not steps or steps[-1][0] != anchor:
-        steps.append((anchor, proposals))
+      if sequence.speculative_counters()["drafted_tokens"] > drafted:  # a speculative step ran since the last look
+        drafted = sequence.speculative_counters()["drafted_tokens"]
+        steps.append(sequence.draft_step())
       assert sequence.append([]) == cursor
     sequence.cancel()
     counters = sequence.speculative_counters()

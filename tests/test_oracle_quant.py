@@ -2,6 +2,7 @@
 from pathlib import Path
 
 import numpy as np
+import pytest
 
 import oracle
 from mtlqwen_b200.testing import synth
@@ -28,17 +29,36 @@ def test_synthetic_weights_have_the_configured_distribution():
   assert abs(w.mean()) < 2e-3 and 0.015 < w.std() < 0.025
 
 
-def test_linear_matches_dense_matmul():
-  n, k, m = 48, 512, 3
+def gguf_py_matrix(w, qtype, n, k):
+  """The dense matrix as gguf-py (the third-party implementation of the K-quant formats) dequantises it."""
+  gguf = pytest.importorskip("gguf")
+  kind = gguf.GGMLQuantizationType.Q4_K if qtype == oracle.Q4_K else gguf.GGMLQuantizationType.Q6_K
+  return np.asarray(gguf.quants.dequantize(np.ascontiguousarray(w).reshape(n, -1), kind), dtype=np.float64).reshape(n, k)
+
+
+def test_linear_matches_a_dense_matmul_of_the_gguf_py_matrix():
+  """End to end through the oracle's linear (block walk, row stride, accumulation, residual), pinned on a matrix
+  dequantised by gguf-py rather than by the oracle itself."""
+  n, k, m = 48, 1024, 3
   for qtype in (oracle.Q4_K, oracle.Q6_K):
     w = synth.weight(qtype, n, k, 3)
     x = synth.activations(m, k, 4)
-    dense = oracle.dequant(w, qtype).reshape(n, k).astype(np.float64)
-    want = x.astype(np.float64) @ dense.T
+    want = x.astype(np.float64) @ gguf_py_matrix(w, qtype, n, k).T
     got = oracle.linear(w, qtype, n, k, x)
     assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
     res = synth.activations(m, n, 5)
     assert np.allclose(oracle.linear(w, qtype, n, k, x, res), got + res, atol=1e-6)
+    # more rows than one cache block of the oracle's row loop
+    tall = synth.activations(70, k, 6)
+    assert np.abs(oracle.linear(w, qtype, n, k, tall) - tall.astype(np.float64) @ gguf_py_matrix(w, qtype, n, k).T).max() <= 1e-5 * np.abs(want).max()
+
+
+def test_embedding_rows_are_the_gguf_py_rows():
+  n, k = 64, 512
+  ids = [0, 63, 5, 5, 17]
+  for qtype in (oracle.Q4_K, oracle.Q6_K):
+    w = synth.weight(qtype, n, k, 9)
+    assert np.array_equal(oracle.embedding(w, qtype, k, ids), gguf_py_matrix(w, qtype, n, k)[ids].astype(np.float32))
 
 
 def test_gate_up_is_silu_times_up():

@@ -25,6 +25,20 @@ def test_route_keeps_shared_prefixes_together_and_balances():
   assert len(replicas.route(prompts, 1)[0]) == 16
 
 
+def test_route_cuts_a_prefix_group_that_exceeds_the_fair_share():
+  """64 streams with one shared 2048-token prefix (the multi-replica benchmark configuration): every replica gets
+  64 / N of them and computes the prefix once, instead of one replica getting all."""
+  rng = np.random.default_rng(1)
+  shared = [int(t) for t in rng.integers(0, 1000, 2048)]
+  prompts = [shared + [int(t) for t in rng.integers(0, 1000, 64 + i)] for i in range(64)]
+  for world in (1, 2, 4, 8):
+    assignment = replicas.route(prompts, world)
+    assert sorted(sum(assignment, [])) == list(range(64))
+    assert [len(a) for a in assignment] == [64 // world] * world
+  uneven = replicas.route(prompts[:10], 4)
+  assert sorted(len(a) for a in uneven) == [1, 3, 3, 3]
+
+
 def test_combine_over_two_gloo_ranks(tmp_path):
   script = tmp_path / "rank.py"
   script.write_text(textwrap.dedent(f"""

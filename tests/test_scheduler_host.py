@@ -338,3 +338,32 @@ def test_engine_outlives_close_while_sequences_live(library, weights):
   model.close()
   assert len(complete(sequence, [7, 8, 9], 2)) == 2
   sequence.close()
+
+
+def test_requests_arriving_together_compute_a_shared_prefix_once(library, weights):
+  """Eight requests with the same 1024-token prefix and different suffixes start at the same moment. One of them
+  computes each 512-token block of the prefix while the others sit those passes out and then restore the published
+  checkpoint, so the engine prefills the prefix once plus the suffixes, and every request still gets the tokens it
+  gets alone."""
+  model = engine_of(library, weights, context=2048, INFENG_KV_BLOCKS=128, INFENG_CHECKPOINTS=32)
+  try:
+    prefix = tokens_of(40, 1024)
+    prompts = [prefix + tokens_of(41 + i, 30 + 7 * i) for i in range(8)]
+    alone = []
+    for prompt in prompts[:3]:
+      fresh = engine_of(library, weights, context=2048)
+      sequence = fresh.sequence()
+      alone.append(complete(sequence, prompt, 3))
+      sequence.close()
+      fresh.close()
+    sequences = [model.sequence() for _ in range(8)]
+    before = model.step_counters()["prefill_rows"]
+    together = parallel([lambda s=s, p=p: complete(s, p, 3) for s, p in zip(sequences, prompts)])
+    computed = model.step_counters()["prefill_rows"] - before
+    assert together[:3] == alone
+    suffixes = sum(len(p) - 1024 for p in prompts)
+    assert 1024 + suffixes <= computed <= 1024 + suffixes + 64, (computed, suffixes)
+    for sequence in sequences:
+      sequence.close()
+  finally:
+    model.close()
