@@ -132,6 +132,57 @@ def cpu_decode(path, contexts, steps, warmup, seconds_budget=None):
   return len(models) * done / elapsed, done, elapsed, cores
 
 
+def cpu_configs():
+  """BASELINE configs 1 to 3 on the CPU oracle, single-threaded and on all host cores (median of 3 runs each), on the
+  seeded inputs of the GPU cases: the Q4_K linear 12288 x 4096 with 8 rows, one GDN layer decode step of 8 sequences,
+  and decode attention over 8 contexts uniform in [1, 32768]."""
+  cores = host_threads()
+  import oracle
+  from mtlqwen_b200.testing import synth
+  rng = np.random.default_rng(SEED + 11)
+  w, x = synth.weight(oracle.Q4_K, 12288, 4096, 1235), synth.activations(8, 4096, 1236)
+  gdn = dict(x=synth.activations(8, 4096, 8), mixed=synth.activations(8, 8192, 9), z=synth.activations(8, 4096, 10),
+             wb=(rng.standard_normal((32, 4096)) / 64).astype(np.float32), wa=(rng.standard_normal((32, 4096)) / 64).astype(np.float32),
+             A=(-rng.uniform(1, 16, 32)).astype(np.float32), dt=(0.1 * rng.standard_normal(32)).astype(np.float32),
+             conv=(0.5 * rng.standard_normal((8192, 4))).astype(np.float32), norm=np.ones(128, np.float32),
+             taps=rng.standard_normal((8, 8192, 4)).astype(np.float32), S=(0.01 * rng.standard_normal((8, 32, 128, 128))).astype(np.float32))
+  contexts = [int(c) for c in np.random.default_rng(7).integers(1, 32769, 8)]
+  blocks = [-(-c // 16) for c in contexts]
+  table = np.zeros((8, max(blocks)), np.int32)
+  order, at = rng.permutation(sum(blocks)).astype(np.int32), 0
+  for i, count in enumerate(blocks):
+    table[i, :count] = order[at:at + count]
+    at += count
+  keys = rng.standard_normal((sum(blocks), 4, 16, 256), dtype=np.float32).astype(np.float16).view(np.uint16)
+  values = rng.standard_normal((sum(blocks), 4, 16, 256), dtype=np.float32).astype(np.float16).view(np.uint16)
+  q, qg = rng.standard_normal((8, 16, 256)).astype(np.float32), rng.standard_normal((8, 16, 512)).astype(np.float32)
+
+  def gdn_step():
+    for i in range(8):
+      beta, g = oracle.gdn_ba(gdn["x"][i:i + 1], gdn["wb"], gdn["wa"], gdn["A"], gdn["dt"])
+      qo, ko, vo, _ = oracle.gdn_conv(gdn["mixed"][i:i + 1], gdn["conv"], gdn["taps"][i])
+      o, _, _ = oracle.delta_rule(qo, ko, vo, g, beta, gdn["S"][i])
+      oracle.gated_rms_norm(o, gdn["z"][i:i + 1], gdn["norm"])
+
+  cases = {"cfg1_m8": lambda: oracle.linear(w, oracle.Q4_K, 12288, 4096, x), "cfg2_gdn_decode": gdn_step,
+           "cfg3_attention": lambda: oracle.attention(q, qg, keys, values, table, contexts, 16)}
+  out = {}
+  for name, call in cases.items():
+    entry = {}
+    for label, threads in (("one_thread_ms", 1), ("all_cores_ms", cores)):
+      oracle.set_threads(threads)
+      samples = []
+      for _ in range(3):
+        started = time.perf_counter()
+        call()
+        samples.append(time.perf_counter() - started)
+      entry[label] = 1e3 * statistics.median(samples)
+    entry["cores"] = cores
+    out[name] = entry
+  oracle.set_threads(cores)
+  return out
+
+
 def reference_contexts(warmup):
   return [len(p) + warmup for p in prompts()]
 
@@ -391,6 +442,8 @@ def run_ours(args, rank, world):
                        "note": "rank 0, all passes before the timed decode window"}
   if world == 1:
     rate, done, elapsed, cores = cpu_decode(path, reference_contexts(args.warmup), None, 1, seconds_budget=12.0)
+    for name, entry in cpu_configs().items():  # the oracle on the single-kernel configurations, beside the GPU figures
+      kernels[name]["cpu_oracle"] = entry
     line["cpu_baseline"] = {"value": rate, "unit": "tok/s", "cores": cores, "kind": "port",
                             "sample": f"{done} batched decode steps of the same 8 sequences at the same contexts on the host cores ({elapsed:.1f} s); "
                                       "K/V and recurrent states filled with seeded synthetic values"}
@@ -404,8 +457,8 @@ def run_case(args):
   local = int(os.environ.get("LOCAL_RANK", 0))
   if args.case in ("step", "cfg5"):
     path = synth.ensure_full_model()
-    if args.case == "step":  # decode steps of config 4 at short contexts: few launches before the timed passes
-      r = run_config4(args, local, path, None, longest=160)
+    if args.case == "step":  # decode steps of config 4; --context bounds the prompt lengths (short ones: few launches before the timed passes)
+      r = run_config4(args, local, path, None, longest=max(args.context, 130))
       print(json.dumps({"case": "step", "ms_per_step": 1e3 * r["device_seconds"] / max(r["passes"], 1), "passes": int(r["passes"]),
                         "launches": int(r["launches"]), "contexts": r["contexts"]}))
     else:
@@ -433,6 +486,7 @@ def main():
   parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
   parser.add_argument("--case", default=None, choices=("cfg1", "cfg1_m1", "lm_head", "prefill", "cfg2", "cfg2_prefill", "cfg3", "step", "cfg5"),
                       help="run one small case alone and print its line (the commands of the profile summaries)")
+  parser.add_argument("--context", type=int, default=160, help="--case step only: upper bound of the ragged prompt lengths (4096 = the headline workload)")
   parser.add_argument("--no-cfg5", action="store_true", help="leave the config-5 block out of the line")
   args = parser.parse_args()
   args.warmup = max(args.warmup, 3)

@@ -30,7 +30,7 @@ enum {
 };
 
 /* ggml tensor type ids used by the GGUF files (forward.cpp:55 indexes kernels by `type - 11`). */
-enum { INFDEV_F32 = 0, INFDEV_F16 = 1, INFDEV_Q4_K = 12, INFDEV_Q6_K = 14 };
+enum { INFDEV_F32 = 0, INFDEV_F16 = 1, INFDEV_Q8_0 = 8, INFDEV_Q4_K = 12, INFDEV_Q5_K = 13, INFDEV_Q6_K = 14, INFDEV_IQ4_XS = 23 };
 
 /* Per-query ragged metadata, the CUDA form of GpuQuery (backend/metal/kernel/batch.hpp:11-16).
  * previous/next are device addresses of the slot's state record (0 = fresh sequence); state is the first
@@ -120,11 +120,14 @@ int infdev_graph_launch(infdev_ctx* ctx, void* graph);
 void infdev_graph_destroy(infdev_ctx* ctx, void* graph);
 
 /* ---- quantised linear algebra ---- */
-/* Block dequantisation to fp32, bit-exact with dequant_tile (quant_linear.metal:32-48 Q4_K, :69-85 Q6_K). */
+/* Block dequantisation to fp32, bit-exact with dequant_tile (quant_linear.metal:32-48 Q4_K, :50-67 Q5_K, :69-85 Q6_K,
+ * :87-97 Q8_0, :99-115 IQ4_XS); `count` blocks of 256 values (32 for Q8_0). INFDEV_F16 converts count * 256 halves. */
 int infdev_dequant(infdev_ctx* ctx, int type, const void* blocks, int64_t count, float* out);
 /* y[m,n] = x[m,k] . W[n,k]^T (+ residual[m,n]); replaces Ops::linear (forward.cpp:51-70) over
  * linear_decode_q4_k[_add] (quant_linear.metal:245-327), linear_decode_q6_k[_add] (:436-512) and, for
- * m > 8, linear_prefill (:151-233). x, y, residual fp32 row-major; residual may alias y or be null. */
+ * m > 8, linear_prefill (:151-233). x, y, residual fp32 row-major; residual may alias y or be null.
+ * Q5_K, Q8_0 and IQ4_XS matrices (linear_decode_q5_k, linear_decode_q8_0, :329-434, 514-570; the types the real
+ * Qwen3.5 files mix in) are served by a plain dequantise-and-multiply kernel: correct, not tuned. */
 int infdev_linear(infdev_ctx* ctx, int type, const void* w, int64_t n, int64_t k, const float* x, int64_t m, float* y, const float* residual);
 /* Up to four weight matrices sharing x in one launch (the q/k/v and qkv/z projections of Ops::decoder,
  * forward.cpp:86-88, 98). */

@@ -269,10 +269,27 @@ void Engine::loadModel(const std::filesystem::path& path, const std::filesystem:
     if (w.n != n || w.k != k)
       throw std::runtime_error("weight " + name + " has shape " + std::to_string(w.n) + " x " + std::to_string(w.k) + ", expected " + std::to_string(n) +
                                " x " + std::to_string(k));
-    const bool supported = quantised ? (w.type == INFDEV_Q4_K || w.type == INFDEV_Q6_K) : w.type == INFDEV_F32;
+    const bool supported = quantised ? (w.type == INFDEV_Q4_K || w.type == INFDEV_Q6_K || w.type == INFDEV_Q5_K || w.type == INFDEV_Q8_0 ||
+                                        w.type == INFDEV_IQ4_XS)
+                                     : w.type == INFDEV_F32;
     if (!supported)
       throw std::runtime_error("weight " + name + " has ggml type " + std::to_string(w.type) + "; this build runs " +
-                               (quantised ? "Q4_K and Q6_K projections" : "F32 norms and GDN parameters"));
+                               (quantised ? "Q4_K, Q5_K, Q6_K, Q8_0 and IQ4_XS projections" : "F32 norms and GDN parameters"));
+  };
+  // ssm_beta / ssm_alpha come as F16 in the real files (gdn_ba_prepare_4096x32 takes either, native_ops.metal:89-113); the
+  // kernels here read fp32, so such a tensor is widened once at load time.
+  auto widen = [&](const std::string& name) {
+    auto found = weights.find(name);
+    if (found == weights.end() || found->second.type != INFDEV_F16)
+      return;
+    Weight& w = found->second;
+    const uint64_t elements = uint64_t(w.n) * w.k;
+    if (elements % 256)
+      throw std::runtime_error("weight " + name + ": an F16 tensor must hold a multiple of 256 values");
+    Tensor wide = device.empty(elements * sizeof(float));
+    device.check(infdev_dequant(device.ctx, INFDEV_F16, w.as<void>(), int64_t(elements / 256), wide.as<float>()));
+    static_cast<Tensor&>(w) = wide;
+    w.type = INFDEV_F32;
   };
   require("token_embd.weight", vocab, hiddenSize, true);
   require("output.weight", vocab, hiddenSize, true);
@@ -284,6 +301,8 @@ void Engine::loadModel(const std::filesystem::path& path, const std::filesystem:
     require(p + "ffn_gate.weight", intermediateSize, hiddenSize, true);
     require(p + "ffn_up.weight", intermediateSize, hiddenSize, true);
     require(p + "ffn_down.weight", hiddenSize, intermediateSize, true);
+    if (weights.at(p + "ffn_gate.weight").type != weights.at(p + "ffn_up.weight").type)
+      throw std::runtime_error("blk." + std::to_string(layer) + ": ffn_gate and ffn_up must share a quantisation type (one fused kernel serves the pair)");
     if (layer >= targetLayers || (layer + 1) % fullAttentionInterval == 0) {
       require(p + "attn_q.weight", 8192, hiddenSize, true);
       require(p + "attn_k.weight", 1024, hiddenSize, true);
@@ -295,6 +314,8 @@ void Engine::loadModel(const std::filesystem::path& path, const std::filesystem:
       require(p + "attn_qkv.weight", 8192, hiddenSize, true);
       require(p + "attn_gate.weight", hiddenSize, hiddenSize, true);
       require(p + "ssm_out.weight", hiddenSize, hiddenSize, true);
+      widen(p + "ssm_beta.weight");
+      widen(p + "ssm_alpha.weight");
       require(p + "ssm_beta.weight", 32, hiddenSize, false);
       require(p + "ssm_alpha.weight", 32, hiddenSize, false);
       require(p + "ssm_a", 1, 32, false);
@@ -303,6 +324,7 @@ void Engine::loadModel(const std::filesystem::path& path, const std::filesystem:
       require(p + "ssm_norm.weight", 1, 128, false);
     }
   }
+  device.check(device.commit());  // the widened copies are complete before their sources could be released
   if (hasMtp) {
     const std::string p = "blk." + std::to_string(targetLayers) + ".nextn.";
     require(p + "enorm.weight", 1, hiddenSize, false);

@@ -423,9 +423,11 @@ void infdev_graph_destroy(infdev_ctx* ctx, void* graph) {
 
 int infdev_dequant(infdev_ctx* ctx, int type, const void* blocks, int64_t count, float* out) {
   Bind bind(ctx);
-  if (type != INFDEV_Q4_K && type != INFDEV_Q6_K)
-    return fail(ctx, INFDEV_E_ARGUMENT, "dequant: type must be Q4_K or Q6_K");
   ctx->launches += 1;
+  if (infdev::format_supported(type) || type == INFDEV_F16)
+    return check(ctx, infdev::format_dequant_launch(type, blocks, count, out, ctx->stream), "dequant");
+  if (type != INFDEV_Q4_K && type != INFDEV_Q6_K)
+    return fail(ctx, INFDEV_E_ARGUMENT, "dequant: unsupported block type " + std::to_string(type));
   return check(ctx, infdev::dequant_launch(type, blocks, count, out, ctx->stream), "dequant");
 }
 
@@ -550,6 +552,17 @@ static int linear_common(infdev_ctx* ctx, int type, bool pair, int count, const 
   uint8_t* captured = take_capture(ctx);
   if (captured && (count != 1 || n[0] % 256))
     return fail(ctx, INFDEV_E_ARGUMENT, "linear: an image of the result needs a single matrix with n a multiple of 256");
+  if (infdev::format_supported(type)) {  // Q5_K, Q8_0, IQ4_XS: one plain launch per matrix and 8-row slice
+    if (m < 0 || k <= 0 || k % 256 || !aligned16(x))
+      return fail(ctx, INFDEV_E_ARGUMENT, "linear: k must be a positive multiple of 256 and the activations 16-byte aligned");
+    for (int i = 0; i < count; ++i) {
+      if (int r = check(ctx, infdev::format_linear_launch(type, pair, w[i], pair ? w2[i] : nullptr, n[i], k, x, m, y[i], residual ? residual[i] : nullptr, ctx->stream),
+                        "linear"))
+        return r;
+      ctx->launches += uint64_t((m + 7) / 8);
+    }
+    return captured ? quantize_rows(ctx, y[0], m, n[0], captured) : INFDEV_OK;
+  }
   if (int r = linear_run(ctx, type, pair, count, w, w2, n, k, x, m, y, residual, supplied))
     return r;
   // A GEMV tile is 16 outputs wide, a 256-value image block spans 16 tiles on different SMs: the image of the result
@@ -582,9 +595,13 @@ int infdev_gather_tokens(infdev_ctx* ctx, const infdev_query* queries, int query
 
 int infdev_embedding(infdev_ctx* ctx, int type, const void* table, int64_t k, const int32_t* rowTokens, int64_t rows, float* out) {
   Bind bind(ctx);
-  if ((type != INFDEV_Q4_K && type != INFDEV_Q6_K) || k % 256)
-    return fail(ctx, INFDEV_E_ARGUMENT, "embedding: table must be Q4_K or Q6_K with k a multiple of 256");
+  if (k % 256)
+    return fail(ctx, INFDEV_E_ARGUMENT, "embedding: k must be a multiple of 256");
   ctx->launches += 1;
+  if (infdev::format_supported(type))
+    return check(ctx, infdev::format_embedding_launch(type, table, k, rowTokens, rows, out, ctx->stream), "embedding");
+  if (type != INFDEV_Q4_K && type != INFDEV_Q6_K)
+    return fail(ctx, INFDEV_E_ARGUMENT, "embedding: unsupported table type " + std::to_string(type));
   return check(ctx, infdev::embedding_launch(type, table, k, rowTokens, rows, out, ctx->stream), "embedding");
 }
 

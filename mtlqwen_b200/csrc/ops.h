@@ -6,6 +6,13 @@
 
 namespace infdev {
 
+// Q5_K, Q8_0, IQ4_XS (and F16 for dequantisation): formats.cu
+bool format_supported(int type);
+int format_block_values(int type);
+cudaError_t format_dequant_launch(int type, const void* blocks, int64_t count, float* out, cudaStream_t stream);
+cudaError_t format_embedding_launch(int type, const void* table, int64_t k, const int32_t* tokens, int64_t rows, float* out, cudaStream_t stream);
+cudaError_t format_linear_launch(int type, bool pair, const void* w, const void* w2, int64_t n, int64_t k, const float* x, int64_t m, float* y,
+                                 const float* residual, cudaStream_t stream);
 cudaError_t bounded_wait_probe_launch(uint32_t limit, int* status, cudaStream_t stream);
 cudaError_t dequant_launch(int type, const void* blocks, int64_t count, float* out, cudaStream_t stream);
 cudaError_t embedding_launch(int type, const void* table, int64_t k, const int32_t* tokens, int64_t rows, float* out, cudaStream_t stream);

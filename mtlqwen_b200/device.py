@@ -10,8 +10,8 @@ import numpy as np
 
 from . import build as _build
 
-F32, F16, Q4_K, Q6_K = 0, 1, 12, 14
-BLOCK_BYTES = {Q4_K: 144, Q6_K: 210}
+F32, F16, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_XS = 0, 1, 8, 12, 13, 14, 23
+BLOCK_BYTES = {Q4_K: 144, Q6_K: 210, Q5_K: 176, IQ4_XS: 136, Q8_0: 34}
 CONV_STATE_BYTES, RECURRENT_STATE_BYTES = 8192 * 4 * 4, 32 * 128 * 128 * 4
 GDN_LAYER_STATE_BYTES = CONV_STATE_BYTES + RECURRENT_STATE_BYTES
 UNBOUND = 0xffffffff

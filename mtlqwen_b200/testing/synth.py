@@ -7,6 +7,9 @@ uniform, fp16 super-block scales chosen so the dequantised weights are about N(0
 import numpy as np
 
 Q4_K, Q6_K, F32 = 12, 14, 0
+F16, Q8_0, Q5_K, IQ4_XS = 1, 8, 13, 23
+BLOCK_BYTES = {Q4_K: 144, Q6_K: 210, Q5_K: 176, IQ4_XS: 136, Q8_0: 34}
+BLOCK_VALUES = {Q4_K: 256, Q6_K: 256, Q5_K: 256, IQ4_XS: 256, Q8_0: 32}
 
 
 def q4k_blocks(count, rng, target_std=0.02, subnormal=False):
@@ -33,10 +36,38 @@ def q6k_blocks(count, rng, target_std=0.02):
   return blocks
 
 
+def q5k_blocks(count, rng, target_std=0.02):
+  """`count` Q5_K super-blocks (176 B): as Q4_K plus 32 bytes of fifth bits, q ~ U{0..31}. E[sc q] = 488.25 and
+  E[m] = 31.5 so dmin = 15.5 d centres the weights; std(w) = 527 d."""
+  blocks = np.frombuffer(rng.bytes(count * 176), dtype=np.uint8).reshape(count, 176).copy()
+  d16 = ((target_std / 527.0) * rng.uniform(0.8, 1.2, count)).astype(np.float16)
+  m16 = (d16.astype(np.float32) * 15.5).astype(np.float16)
+  blocks[:, 0:2] = d16.view(np.uint8).reshape(count, 2)
+  blocks[:, 2:4] = m16.view(np.uint8).reshape(count, 2)
+  return blocks
+
+
+def q8_0_blocks(count, rng, target_std=0.02):
+  """`count` Q8_0 blocks (34 B per 32 values): fp16 d, 32 int8 ~ U{-128..127} (std 73.9)."""
+  blocks = np.frombuffer(rng.bytes(count * 34), dtype=np.uint8).reshape(count, 34).copy()
+  blocks[:, 0:2] = ((target_std / 73.9) * rng.uniform(0.8, 1.2, count)).astype(np.float16).view(np.uint8).reshape(count, 2)
+  return blocks
+
+
+def iq4xs_blocks(count, rng, target_std=0.02):
+  """`count` IQ4_XS super-blocks (136 B): fp16 d, 6-bit sub-block scales ls ~ U{0..63} (factor ls - 32), 4-bit indices
+  into the non-linear grid (std about 72): std(w) is about 1330 d."""
+  blocks = np.frombuffer(rng.bytes(count * 136), dtype=np.uint8).reshape(count, 136).copy()
+  blocks[:, 0:2] = ((target_std / 1330.0) * rng.uniform(0.8, 1.2, count)).astype(np.float16).view(np.uint8).reshape(count, 2)
+  return blocks
+
+
+GENERATORS = {Q4_K: q4k_blocks, Q6_K: q6k_blocks, Q5_K: q5k_blocks, Q8_0: q8_0_blocks, IQ4_XS: iq4xs_blocks}
+
+
 def weight(qtype, n, k, seed):
   rng = np.random.default_rng(seed)
-  count = n * (k // 256)
-  return q4k_blocks(count, rng) if qtype == Q4_K else q6k_blocks(count, rng)
+  return GENERATORS[qtype](n * (k // BLOCK_VALUES[qtype]), rng)
 
 
 def activations(m, k, seed):
@@ -48,20 +79,31 @@ GGUF_MAGIC, GGUF_ALIGNMENT = 0x46554747, 32
 HIDDEN, INTERMEDIATE = 4096, 12288
 
 
-def model_tensors(layers=32, vocab=248320, mtp=False, seed=1234):
+def model_tensors(layers=32, vocab=248320, mtp=False, seed=1234, mixed=False):
   """Yields (name, ggml type, shape as (n, k) or (dim,), generator of the raw bytes). Projections Q4_K, embedding
-  and lm_head Q6_K, norms F32 at 1 +- 0.01, GDN parameters as in the gated-delta-rule benchmark configuration."""
+  and lm_head Q6_K, norms F32 at 1 +- 0.01, GDN parameters as in the gated-delta-rule benchmark configuration.
+  mixed: the type mix of the real Qwen3.5 GGUF files instead - projections cycle through Q4_K, Q5_K, IQ4_XS, Q6_K and
+  Q8_0 (a gate / up pair shares its type), the embedding table is Q4_K, ssm_beta / ssm_alpha are F16 and the MTP
+  projection eh_proj is Q8_0."""
   counter = [seed]
+  cycle = [0]
 
   def rng():
     counter[0] += 1
     return np.random.default_rng(counter[0])
 
-  def q4(n, k):
-    return (Q4_K, (n, k), lambda: q4k_blocks(n * k // 256, rng()))
+  def quantised(qtype, n, k):
+    return (qtype, (n, k), lambda: GENERATORS[qtype](n * k // BLOCK_VALUES[qtype], rng()))
+
+  def q4(n, k, advance=True):
+    if not mixed:
+      return quantised(Q4_K, n, k)
+    if advance:
+      cycle[0] += 1
+    return quantised((Q4_K, Q5_K, IQ4_XS, Q6_K, Q8_0)[cycle[0] % 5], n, k)
 
   def q6(n, k):
-    return (Q6_K, (n, k), lambda: q6k_blocks(n * k // 256, rng()))
+    return quantised(Q6_K, n, k)
 
   def norm(dim):
     return (F32, (dim, ), lambda: (1 + 0.01 * rng().standard_normal(dim)).astype(np.float32))
@@ -69,14 +111,14 @@ def model_tensors(layers=32, vocab=248320, mtp=False, seed=1234):
   def f32(shape, make):
     return (F32, shape, lambda: make(rng()).astype(np.float32))
 
-  yield ("token_embd.weight", *q6(vocab, HIDDEN))
+  yield ("token_embd.weight", *(quantised(Q4_K, vocab, HIDDEN) if mixed else q6(vocab, HIDDEN)))
   yield ("output_norm.weight", *norm(HIDDEN))
   yield ("output.weight", *q6(vocab, HIDDEN))
 
   def ffn(prefix):
     yield (prefix + "post_attention_norm.weight", *norm(HIDDEN))
     yield (prefix + "ffn_gate.weight", *q4(INTERMEDIATE, HIDDEN))
-    yield (prefix + "ffn_up.weight", *q4(INTERMEDIATE, HIDDEN))
+    yield (prefix + "ffn_up.weight", *q4(INTERMEDIATE, HIDDEN, advance=False))
     yield (prefix + "ffn_down.weight", *q4(HIDDEN, INTERMEDIATE))
 
   def attention(prefix):
@@ -97,8 +139,12 @@ def model_tensors(layers=32, vocab=248320, mtp=False, seed=1234):
     yield (prefix + "attn_norm.weight", *norm(HIDDEN))
     yield (prefix + "attn_qkv.weight", *q4(8192, HIDDEN))
     yield (prefix + "attn_gate.weight", *q4(HIDDEN, HIDDEN))
-    yield (prefix + "ssm_beta.weight", *f32((32, HIDDEN), lambda r: r.standard_normal((32, HIDDEN)) / 64))
-    yield (prefix + "ssm_alpha.weight", *f32((32, HIDDEN), lambda r: r.standard_normal((32, HIDDEN)) / 64))
+    if mixed:
+      yield (prefix + "ssm_beta.weight", F16, (32, HIDDEN), lambda: (rng().standard_normal((32, HIDDEN)) / 64).astype(np.float16))
+      yield (prefix + "ssm_alpha.weight", F16, (32, HIDDEN), lambda: (rng().standard_normal((32, HIDDEN)) / 64).astype(np.float16))
+    else:
+      yield (prefix + "ssm_beta.weight", *f32((32, HIDDEN), lambda r: r.standard_normal((32, HIDDEN)) / 64))
+      yield (prefix + "ssm_alpha.weight", *f32((32, HIDDEN), lambda r: r.standard_normal((32, HIDDEN)) / 64))
     yield (prefix + "ssm_a", *f32((32, ), lambda r: -r.uniform(1, 16, 32)))
     yield (prefix + "ssm_dt.bias", *f32((32, ), lambda r: 0.1 * r.standard_normal(32)))
     yield (prefix + "ssm_conv1d.weight", *f32((8192, 4), lambda r: 0.5 * r.standard_normal((8192, 4))))
@@ -109,7 +155,7 @@ def model_tensors(layers=32, vocab=248320, mtp=False, seed=1234):
     prefix = f"blk.{layers}."
     yield (prefix + "nextn.enorm.weight", *norm(HIDDEN))
     yield (prefix + "nextn.hnorm.weight", *norm(HIDDEN))
-    yield (prefix + "nextn.eh_proj.weight", *q4(HIDDEN, 2 * HIDDEN))
+    yield (prefix + "nextn.eh_proj.weight", *(quantised(Q8_0, HIDDEN, 2 * HIDDEN) if mixed else q4(HIDDEN, 2 * HIDDEN)))
     yield (prefix + "nextn.shared_head_norm.weight", *norm(HIDDEN))
     yield from attention(prefix)
 
@@ -119,14 +165,15 @@ def _gguf_string(text):
   return np.uint64(len(raw)).tobytes() + raw
 
 
-def write_gguf(path, layers=32, vocab=248320, mtp=False, seed=1234):
+def tensor_bytes(qtype, elements):
+  return elements * 4 if qtype == F32 else elements * 2 if qtype == F16 else elements // BLOCK_VALUES[qtype] * BLOCK_BYTES[qtype]
+
+
+def write_gguf(path, layers=32, vocab=248320, mtp=False, seed=1234, mixed=False):
   """Writes a GGUF v3 file. ne[0] is the contiguous dimension: a weight [n, k] is stored with shape (k, n),
   which the engine reads back as n = shape[1], k = shape[0] (forward.cpp:18-22)."""
-  tensors = list(model_tensors(layers, vocab, mtp, seed))
-  sizes = []
-  for _, qtype, shape, _ in tensors:
-    elements = int(np.prod(shape))
-    sizes.append(elements * 4 if qtype == F32 else elements // 256 * (144 if qtype == Q4_K else 210))
+  tensors = list(model_tensors(layers, vocab, mtp, seed, mixed))
+  sizes = [tensor_bytes(qtype, int(np.prod(shape))) for _, qtype, shape, _ in tensors]
   header = bytearray()
   header += np.uint32(GGUF_MAGIC).tobytes() + np.uint32(3).tobytes() + np.uint64(len(tensors)).tobytes() + np.uint64(3).tobytes()
   header += _gguf_string("general.architecture") + np.uint32(8).tobytes() + _gguf_string("qwen35")
@@ -189,8 +236,7 @@ def read_gguf(path):
   data_offset = -(-at[0] // alignment) * alignment
   tensors = {}
   for name, dims, qtype, offset in infos:
-    elements = int(np.prod(dims))
-    size = elements * 4 if qtype == F32 else elements // 256 * (144 if qtype == Q4_K else 210)
+    size = tensor_bytes(qtype, int(np.prod(dims)))
     view = raw[data_offset + offset:data_offset + offset + size]
     tensors[name] = (np.frombuffer(view, dtype=np.float32) if qtype == F32 else np.frombuffer(view, dtype=np.uint8), qtype)
   return tensors

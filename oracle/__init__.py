@@ -11,8 +11,9 @@ import numpy as np
 
 ROOT = Path(__file__).resolve().parent
 LIB = ROOT / "_build" / "liboracle.so"
-F32, F16, Q4_K, Q6_K = 0, 1, 12, 14
-BLOCK_BYTES = {Q4_K: 144, Q6_K: 210}
+F32, F16, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_XS = 0, 1, 8, 12, 13, 14, 23
+BLOCK_BYTES = {Q4_K: 144, Q6_K: 210, Q5_K: 176, IQ4_XS: 136, Q8_0: 34}
+BLOCK_VALUES = {Q4_K: 256, Q6_K: 256, Q5_K: 256, IQ4_XS: 256, Q8_0: 32}
 
 
 def build(force=False):
@@ -49,10 +50,15 @@ def _i64(value):
   return ctypes.c_int64(int(value))
 
 
+def set_threads(threads):
+  """OpenMP threads of the oracle's parallel loops from now on."""
+  lib().orc_set_threads(ctypes.c_int(int(threads)))
+
+
 def dequant(blocks, qtype):
   blocks = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1, BLOCK_BYTES[qtype])
-  out = np.empty((blocks.shape[0], 256), dtype=np.float32)
-  (lib().orc_dequant_q4k if qtype == Q4_K else lib().orc_dequant_q6k)(_p(blocks), _i64(blocks.shape[0]), _p(out))
+  out = np.empty((blocks.shape[0], BLOCK_VALUES[qtype]), dtype=np.float32)
+  lib().orc_dequant(ctypes.c_int(qtype), _p(blocks), _i64(blocks.shape[0]), _p(out))
   return out
 
 
@@ -67,7 +73,7 @@ def linear(w, qtype, n, k, x, residual=None):
 def gate_up(wg, wu, qtype, n, k, x):
   x = _f32(x).reshape(-1, k)
   y = np.empty((x.shape[0], n), dtype=np.float32)
-  lib().orc_gate_up(_p(wg), _p(wu), ctypes.c_int(qtype), _i64(n), _i64(k), _p(x), _i64(x.shape[0]), _p(y))
+  lib().orc_gate_up(_p(wg), _p(wu), ctypes.c_int(qtype), ctypes.c_int(qtype), _i64(n), _i64(k), _p(x), _i64(x.shape[0]), _p(y))
   return y
 
 
@@ -177,14 +183,18 @@ def hash_checkpoint(previous, tokens):
   return int(lib().orc_hash_checkpoint(ctypes.c_uint64(previous), _p(tokens)))
 
 
+_QUANTISED = ("gate", "up", "down", "wq", "wk", "wv", "wo", "wqkv", "wz", "wout")
+
+
 class _Layer(ctypes.Structure):
   _fields_ = [(name, ctypes.c_void_p) for name in ("attnNorm", "postNorm", "gate", "up", "down", "wq", "wk", "wv", "wo", "qNorm", "kNorm", "wqkv",
                                                    "wz", "wout", "wBeta", "wAlpha", "ssmA", "ssmDt", "conv", "ssmNorm")]
+  _fields_ += [(name + "Type", ctypes.c_int32) for name in _QUANTISED]
 
 
 class _Model(ctypes.Structure):
   _fields_ = [("layers", ctypes.c_int32), ("vocab", ctypes.c_int32), ("embdType", ctypes.c_int32), ("outType", ctypes.c_int32),
-              ("projType", ctypes.c_int32), ("maxContext", ctypes.c_int32), ("embd", ctypes.c_void_p), ("output", ctypes.c_void_p),
+              ("mtpProjType", ctypes.c_int32), ("maxContext", ctypes.c_int32), ("embd", ctypes.c_void_p), ("output", ctypes.c_void_p),
               ("outputNorm", ctypes.c_void_p), ("rope", ctypes.c_void_p), ("layer", _Layer * 64), ("mtpEnorm", ctypes.c_void_p),
               ("mtpHnorm", ctypes.c_void_p), ("mtpHeadNorm", ctypes.c_void_p), ("mtpProj", ctypes.c_void_p)]
 
@@ -212,8 +222,9 @@ class Model:
     m = _Model()
     m.layers, m.vocab, m.maxContext = layers, vocab, max_context
     m.embdType, m.outType = tensors["token_embd.weight"][1], tensors["output.weight"][1]
-    m.projType = tensors["blk.0.ffn_gate.weight"][1]
-    ptr = lambda name: tensors[name][0].ctypes.data
+    # F16 tensors (ssm_beta / ssm_alpha of the real files) are handed to the C side as float32 copies
+    self._converted = {name: np.ascontiguousarray(array.view(np.float16).astype(np.float32)) for name, (array, kind) in tensors.items() if kind == F16}
+    ptr = lambda name: (self._converted[name] if name in self._converted else tensors[name][0]).ctypes.data
     m.embd, m.output, m.outputNorm = ptr("token_embd.weight"), ptr("output.weight"), ptr("output_norm.weight")
     self._rope = rope_table(max_context)
     m.rope = self._rope.ctypes.data
@@ -230,10 +241,13 @@ class Model:
         key = f"blk.{L}.{name}"
         if key in tensors:
           setattr(m.layer[L], field, ptr(key))
+          if field in _QUANTISED:
+            setattr(m.layer[L], field + "Type", tensors[key][1])
     if self.has_mtp:
       nextn = f"blk.{layers}.nextn."
       m.mtpEnorm, m.mtpHnorm = ptr(nextn + "enorm.weight"), ptr(nextn + "hnorm.weight")
       m.mtpHeadNorm, m.mtpProj = ptr(nextn + "shared_head_norm.weight"), ptr(nextn + "eh_proj.weight")
+      m.mtpProjType = tensors[nextn + "eh_proj.weight"][1]
     self._model = m
     gdn, att = layers - layers // 4, layers // 4
     self._conv = np.zeros((max(gdn, 1), 8192, 4), np.float32)

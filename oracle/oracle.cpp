@@ -14,6 +14,7 @@
 // Precision policy: activations are fp32 (the reference stores fp16 at every kernel boundary);
 // dot products accumulate per 256-element block in fp32 and across blocks in double; the K/V cache is
 // fp16 as in the reference. Built with -ffp-contract=off so the dequantisers match numpy exactly.
+#include <omp.h>
 #include <algorithm>
 #include <cmath>
 #include <cstdint>
@@ -74,9 +75,67 @@ void dequant_block_q6k(const uint8_t* b, float* out) {
       }
 }
 
-enum { TYPE_F32 = 0, TYPE_F16 = 1, TYPE_Q4_K = 12, TYPE_Q6_K = 14 };
+// One 34-byte Q8_0 block -> 32 floats: fp16 d, then 32 int8. quant_linear.metal:87-97.
+void dequant_block_q8_0(const uint8_t* b, float* out) {
+  float d = h16(b);
+  for (unsigned l = 0; l < 32; ++l)
+    out[l] = d * float(int8_t(b[2 + l]));
+}
 
-inline size_t block_bytes(int type) { return type == TYPE_Q4_K ? 144 : type == TYPE_Q6_K ? 210 : 0; }
+// One 176-byte Q5_K super-block -> 256 floats: fp16 d, fp16 dmin, 12 B of 6-bit scales / mins as in Q4_K, 32 B of
+// high bits (bit j of byte l belongs to element 32 j + l), 128 B of low nibbles laid out as in Q4_K.
+// quant_linear.metal:50-67.
+void dequant_block_q5k(const uint8_t* b, float* out) {
+  float d = h16(b), dm = h16(b + 2);
+  for (unsigned t = 0; t < 4; ++t) {
+    uint8_t sc0, mn0, sc1, mn1;
+    scale_min_k4(2 * t, b + 4, sc0, mn0);
+    scale_min_k4(2 * t + 1, b + 4, sc1, mn1);
+    float d0 = d * float(sc0), m0 = dm * float(mn0), d1 = d * float(sc1), m1 = dm * float(mn1);
+    for (unsigned l = 0; l < 32; ++l) {
+      uint8_t q = b[48 + t * 32 + l], hm = b[16 + l];
+      out[t * 64 + l] = d0 * float((q & 15) + ((hm & (1u << (2 * t))) ? 16 : 0)) - m0;
+      out[t * 64 + 32 + l] = d1 * float((q >> 4) + ((hm & (1u << (2 * t + 1))) ? 16 : 0)) - m1;
+    }
+  }
+}
+
+// The 16 code points of the IQ4 non-linear 4-bit grid (quant_linear.metal:5).
+const float kIq4nl[16] = {-127.0f, -104.0f, -83.0f, -65.0f, -49.0f, -35.0f, -22.0f, -10.0f, 1.0f, 13.0f, 25.0f, 38.0f, 53.0f, 69.0f, 89.0f, 113.0f};
+
+// One 136-byte IQ4_XS super-block -> 256 floats: fp16 d, u16 of 2-bit scale highs, 4 B of 4-bit scale lows, 128 B of
+// 4-bit code indices (16 bytes per 32-value sub-block: low nibbles are its first 16 values, high nibbles the last 16).
+// quant_linear.metal:99-115.
+void dequant_block_iq4xs(const uint8_t* b, float* out) {
+  float d = h16(b);
+  unsigned sh = unsigned(b[2]) | (unsigned(b[3]) << 8);
+  for (unsigned j = 0; j < 8; ++j) {
+    int ls = int((b[4 + (j >> 1)] >> (4 * (j & 1))) & 15) | int(((sh >> (2 * j)) & 3) << 4);
+    float dl = d * float(ls - 32);
+    for (unsigned l = 0; l < 32; ++l) {
+      uint8_t q = b[8 + j * 16 + (l & 15)];
+      out[j * 32 + l] = dl * kIq4nl[(l & 16) ? (q >> 4) : (q & 15)];
+    }
+  }
+}
+
+enum { TYPE_F32 = 0, TYPE_F16 = 1, TYPE_Q8_0 = 8, TYPE_Q4_K = 12, TYPE_Q5_K = 13, TYPE_Q6_K = 14, TYPE_IQ4_XS = 23 };
+
+// Bytes and values of one block of a quantised type.
+inline size_t block_bytes(int type) {
+  return type == TYPE_Q4_K ? 144 : type == TYPE_Q6_K ? 210 : type == TYPE_Q5_K ? 176 : type == TYPE_IQ4_XS ? 136 : type == TYPE_Q8_0 ? 34 : 0;
+}
+inline int64_t block_values(int type) { return type == TYPE_Q8_0 ? 32 : 256; }
+
+inline void dequant_block(int type, const uint8_t* b, float* out) {
+  switch (type) {
+    case TYPE_Q4_K: return dequant_block_q4k(b, out);
+    case TYPE_Q6_K: return dequant_block_q6k(b, out);
+    case TYPE_Q5_K: return dequant_block_q5k(b, out);
+    case TYPE_IQ4_XS: return dequant_block_iq4xs(b, out);
+    case TYPE_Q8_0: return dequant_block_q8_0(b, out);
+  }
+}
 
 void dequant_row(const uint8_t* w, int type, int64_t n, int64_t k, float* out) {
   if (type == TYPE_F32) {
@@ -89,10 +148,11 @@ void dequant_row(const uint8_t* w, int type, int64_t n, int64_t k, float* out) {
       out[i] = float(p[i]);
     return;
   }
-  size_t bb = block_bytes(type);
-  const uint8_t* row = w + size_t(n) * (k / 256) * bb;
-  for (int64_t b = 0; b < k / 256; ++b)
-    (type == TYPE_Q4_K ? dequant_block_q4k : dequant_block_q6k)(row + b * bb, out + b * 256);
+  const size_t bb = block_bytes(type);
+  const int64_t values = block_values(type);
+  const uint8_t* row = w + size_t(n) * (k / values) * bb;
+  for (int64_t b = 0; b < k / values; ++b)
+    dequant_block(type, row + b * bb, out + b * values);
 }
 
 inline double dot(const float* a, const float* b, int64_t k) {
@@ -117,6 +177,9 @@ inline float sigmoid(float v) { return 1.0f / (1.0f + std::exp(-v)); }
 
 extern "C" {
 
+// Threads the parallel loops below use from now on (for timing the oracle single-threaded and on all cores).
+void orc_set_threads(int threads) { omp_set_num_threads(threads > 0 ? threads : 1); }
+
 // ---- quant formats ---------------------------------------------------------------------------
 void orc_dequant_q4k(const uint8_t* blocks, int64_t count, float* out) {
 #pragma omp parallel for
@@ -128,6 +191,14 @@ void orc_dequant_q6k(const uint8_t* blocks, int64_t count, float* out) {
 #pragma omp parallel for
   for (int64_t i = 0; i < count; ++i)
     dequant_block_q6k(blocks + i * 210, out + i * 256);
+}
+
+// Any block type: `count` blocks -> count * (32 or 256) floats.
+void orc_dequant(int type, const uint8_t* blocks, int64_t count, float* out) {
+  const int64_t bytes = int64_t(block_bytes(type)), values = block_values(type);
+#pragma omp parallel for
+  for (int64_t i = 0; i < count; ++i)
+    dequant_block(type, blocks + i * bytes, out + i * values);
 }
 
 // ---- linear ----------------------------------------------------------------------------------
@@ -156,7 +227,7 @@ void orc_linear(const uint8_t* w, int type, int64_t n, int64_t k, const float* x
 
 // y[m,n] = silu(x.Wg[n]) * (x.Wu[n]). fused_kernels.metal:48-78 (decode) and the `post == 2` epilogue of
 // quant_linear.metal:224-232 (prefill).
-void orc_gate_up(const uint8_t* wg, const uint8_t* wu, int type, int64_t n, int64_t k, const float* x, int64_t m, float* y) {
+void orc_gate_up(const uint8_t* wg, const uint8_t* wu, int type, int typeUp, int64_t n, int64_t k, const float* x, int64_t m, float* y) {
   for (int64_t r0 = 0; r0 < m; r0 += 32) {
     const int64_t r1 = std::min<int64_t>(m, r0 + 32);
 #pragma omp parallel
@@ -165,7 +236,7 @@ void orc_gate_up(const uint8_t* wg, const uint8_t* wu, int type, int64_t n, int6
 #pragma omp for schedule(static)
       for (int64_t i = 0; i < n; ++i) {
         dequant_row(wg, type, i, k, g.data());
-        dequant_row(wu, type, i, k, u.data());
+        dequant_row(wu, typeUp, i, k, u.data());
         for (int64_t r = r0; r < r1; ++r)
           y[r * n + i] = silu(float(dot(x + r * k, g.data(), k))) * float(dot(x + r * k, u.data(), k));
       }
@@ -484,10 +555,12 @@ struct OrcLayer {
   // gated delta net
   const uint8_t *wqkv, *wz, *wout;
   const float *wBeta, *wAlpha, *ssmA, *ssmDt, *conv, *ssmNorm;
+  // ggml types of the quantised matrices above (the real files mix Q4_K, Q5_K, Q6_K, Q8_0 and IQ4_XS)
+  int32_t gateType, upType, downType, wqType, wkType, wvType, woType, wqkvType, wzType, woutType;
 };
 
 struct OrcModel {
-  int32_t layers, vocab, embdType, outType, projType, maxContext;
+  int32_t layers, vocab, embdType, outType, mtpProjType, maxContext;
   const uint8_t *embd, *output;
   const float* outputNorm;
   const float* rope;  // [maxContext,32,2]
@@ -556,11 +629,11 @@ void attention_core(const OrcModel* model, const OrcLayer& w, float* keys, float
 void attention_rows(const OrcModel* model, const OrcLayer& w, float* keys, float* values, int pos, int64_t T, const float* x, float* h) {
   const int64_t H = 4096;
   std::vector<float> qg(T * 8192), k(T * 1024), v(T * 1024), o(T * 4096), y(T * H);
-  orc_linear(w.wq, model->projType, 8192, H, x, T, qg.data(), nullptr);
-  orc_linear(w.wk, model->projType, 1024, H, x, T, k.data(), nullptr);
-  orc_linear(w.wv, model->projType, 1024, H, x, T, v.data(), nullptr);
+  orc_linear(w.wq, w.wqType, 8192, H, x, T, qg.data(), nullptr);
+  orc_linear(w.wk, w.wkType, 1024, H, x, T, k.data(), nullptr);
+  orc_linear(w.wv, w.wvType, 1024, H, x, T, v.data(), nullptr);
   attention_core(model, w, keys, values, pos, T, qg.data(), k.data(), v.data(), o.data());
-  orc_linear(w.wo, model->projType, H, H, o.data(), T, y.data(), h);
+  orc_linear(w.wo, w.woType, H, H, o.data(), T, y.data(), h);
   std::memcpy(h, y.data(), size_t(T) * H * 4);
 }
 
@@ -581,10 +654,10 @@ void gdn_core(const OrcLayer& w, float* convState, float* S, bool fresh, int64_t
 void gdn_rows(const OrcModel* model, const OrcLayer& w, float* convState, float* S, bool fresh, int64_t T, const float* x, float* h) {
   const int64_t H = 4096;
   std::vector<float> mixed(T * 8192), z(T * H), gated(T * 4096), y(T * H);
-  orc_linear(w.wqkv, model->projType, 8192, H, x, T, mixed.data(), nullptr);
-  orc_linear(w.wz, model->projType, H, H, x, T, z.data(), nullptr);
+  orc_linear(w.wqkv, w.wqkvType, 8192, H, x, T, mixed.data(), nullptr);
+  orc_linear(w.wz, w.wzType, H, H, x, T, z.data(), nullptr);
   gdn_core(w, convState, S, fresh, T, x, mixed.data(), z.data(), gated.data());
-  orc_linear(w.wout, model->projType, H, H, gated.data(), T, y.data(), h);
+  orc_linear(w.wout, w.woutType, H, H, gated.data(), T, y.data(), h);
   std::memcpy(h, y.data(), size_t(T) * H * 4);
 }
 
@@ -593,8 +666,8 @@ void mlp_rows(const OrcModel* model, const OrcLayer& w, int64_t T, float* h) {
   const int64_t H = 4096, I = 12288;
   std::vector<float> x(T * H), t(T * I), y(T * H);
   orc_rms_norm(h, w.postNorm, T, H, 1.0e-6f, x.data());
-  orc_gate_up(w.gate, w.up, model->projType, I, H, x.data(), T, t.data());
-  orc_linear(w.down, model->projType, H, I, t.data(), T, y.data(), h);
+  orc_gate_up(w.gate, w.up, w.gateType, w.upType, I, H, x.data(), T, t.data());
+  orc_linear(w.down, w.downType, H, I, t.data(), T, y.data(), h);
   std::memcpy(h, y.data(), size_t(T) * H * 4);
 }
 
@@ -655,22 +728,22 @@ void orc_model_decode_batch(const OrcModel* model, OrcState* const* states, cons
     orc_rms_norm(h.data(), w.attnNorm, B, H, 1.0e-6f, x.data());
     if ((L + 1) % 4 == 0) {
       std::vector<float> qg(B * 8192), k(B * 1024), v(B * 1024), o(B * 4096);
-      orc_linear(w.wq, model->projType, 8192, H, x.data(), B, qg.data(), nullptr);
-      orc_linear(w.wk, model->projType, 1024, H, x.data(), B, k.data(), nullptr);
-      orc_linear(w.wv, model->projType, 1024, H, x.data(), B, v.data(), nullptr);
+      orc_linear(w.wq, w.wqType, 8192, H, x.data(), B, qg.data(), nullptr);
+      orc_linear(w.wk, w.wkType, 1024, H, x.data(), B, k.data(), nullptr);
+      orc_linear(w.wv, w.wvType, 1024, H, x.data(), B, v.data(), nullptr);
       for (int64_t b = 0; b < B; ++b)
         attention_core(model, w, states[b]->keys + size_t(att) * model->maxContext * 1024, states[b]->values + size_t(att) * model->maxContext * 1024,
                        states[b]->length, 1, qg.data() + b * 8192, k.data() + b * 1024, v.data() + b * 1024, o.data() + b * 4096);
-      orc_linear(w.wo, model->projType, H, H, o.data(), B, y.data(), h.data());
+      orc_linear(w.wo, w.woType, H, H, o.data(), B, y.data(), h.data());
       ++att;
     } else {
       std::vector<float> mixed(B * 8192), z(B * H), gated(B * 4096);
-      orc_linear(w.wqkv, model->projType, 8192, H, x.data(), B, mixed.data(), nullptr);
-      orc_linear(w.wz, model->projType, H, H, x.data(), B, z.data(), nullptr);
+      orc_linear(w.wqkv, w.wqkvType, 8192, H, x.data(), B, mixed.data(), nullptr);
+      orc_linear(w.wz, w.wzType, H, H, x.data(), B, z.data(), nullptr);
       for (int64_t b = 0; b < B; ++b)
         gdn_core(w, states[b]->conv + size_t(gdn) * 8192 * 4, states[b]->S + size_t(gdn) * 32 * 128 * 128, states[b]->length == 0, 1, x.data() + b * H,
                  mixed.data() + b * 8192, z.data() + b * H, gated.data() + b * 4096);
-      orc_linear(w.wout, model->projType, H, H, gated.data(), B, y.data(), h.data());
+      orc_linear(w.wout, w.woutType, H, H, gated.data(), B, y.data(), h.data());
       ++gdn;
     }
     h = y;
@@ -712,12 +785,12 @@ void orc_mtp_step(const OrcModel* model, OrcState* state, int32_t token, const f
   std::vector<float> embedding(H), fused(2 * H), h(H), x(H);
   orc_embedding(model->embd, model->embdType, H, &token, 1, embedding.data());
   orc_mtp_fuse(embedding.data(), previousHidden, model->mtpEnorm, model->mtpHnorm, fused.data());
-  orc_linear(model->mtpProj, model->projType, H, 2 * H, fused.data(), 1, h.data(), nullptr);
+  orc_linear(model->mtpProj, model->mtpProjType, H, 2 * H, fused.data(), 1, h.data(), nullptr);
   orc_rms_norm(h.data(), w.attnNorm, 1, H, 1.0e-6f, x.data());
   if (storeOnly) {
     std::vector<float> k(1024), v(1024), kr(1024), qg(8192, 0.0f), q(4096);
-    orc_linear(w.wk, model->projType, 1024, H, x.data(), 1, k.data(), nullptr);
-    orc_linear(w.wv, model->projType, 1024, H, x.data(), 1, v.data(), nullptr);
+    orc_linear(w.wk, w.wkType, 1024, H, x.data(), 1, k.data(), nullptr);
+    orc_linear(w.wv, w.wvType, 1024, H, x.data(), 1, v.data(), nullptr);
     orc_attention_prepare(qg.data(), k.data(), w.kNorm, w.kNorm, model->rope, &position, 1, q.data(), kr.data());
     for (int i = 0; i < 1024; ++i) {
       state->mtpKeys[size_t(position) * 1024 + i] = half_round(kr[i]);

@@ -22,6 +22,14 @@ def test_q6k_dequant_matches_gguf_py_bit_exact():
   assert got.tobytes() == golden["q6k_values"].tobytes()
 
 
+@pytest.mark.parametrize("name,qtype", [("q5k", oracle.Q5_K), ("q8_0", oracle.Q8_0), ("iq4xs", oracle.IQ4_XS)])
+def test_other_gguf_types_dequant_match_gguf_py_bit_exact(name, qtype):
+  """The block formats of the real Qwen3.5 GGUF files beyond Q4_K / Q6_K (quant_linear.metal:50-67, 87-115)."""
+  golden = np.load(GOLDEN)
+  got = oracle.dequant(golden[name + "_blocks"], qtype)
+  assert got.tobytes() == golden[name + "_values"].tobytes()
+
+
 def test_synthetic_weights_have_the_configured_distribution():
   w = oracle.dequant(synth.weight(synth.Q4_K, 64, 4096, 1), oracle.Q4_K)
   assert abs(w.mean()) < 2e-3 and 0.015 < w.std() < 0.025
