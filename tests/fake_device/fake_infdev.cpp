@@ -111,6 +111,7 @@ int infdev_linear_group(infdev_ctx* ctx, int, int, const void* const*, const int
 }
 int infdev_gate_up(infdev_ctx* ctx, int, const void*, const void*, int64_t, int64_t, const float*, int64_t, float*) { return ++ctx->launches, 0; }
 int infdev_embedding(infdev_ctx* ctx, int, const void*, int64_t, const int32_t*, int64_t, float*) { return ++ctx->launches, 0; }
+int infdev_dequant(infdev_ctx* ctx, int, const void*, int64_t, float*) { return ++ctx->launches, 0; }
 int infdev_rms_norm(infdev_ctx* ctx, const float*, const float*, int64_t, int64_t, float*) { return ++ctx->launches, 0; }
 int infdev_rms_norm_gather(infdev_ctx* ctx, const float*, const float*, const infdev_query*, int, int64_t, float*) { return ++ctx->launches, 0; }
 int infdev_rope_table(infdev_ctx*, int64_t, float*) { return 0; }
