@@ -83,9 +83,9 @@ void* infdev_event_create(infdev_ctx* ctx);
 void infdev_event_destroy(infdev_ctx* ctx, void* event);
 int infdev_event_record(infdev_ctx* ctx, void* event);
 float infdev_event_elapsed_ms(infdev_ctx* ctx, void* start, void* stop);
-/* Which quantised-linear kernel serves Q4_K matrices with n % 128 == 0 and k % 2048 == 0: 0 = always the mma.sync GEMV,
- * 1 (default) = the tcgen05 / TMEM GEMM for more than 8 activation rows (prefill, speculative rows) and the GEMV for
- * decode, 2 = tcgen05 for every row count. Environment: INFENG_UMMA. */
+/* Which quantised-linear kernel serves Q4_K matrices with n % 128 == 0 and k % 2048 == 0 when a launch has more than 8
+ * activation rows (prefill chunks, speculative rows): 1 (default) = the tcgen05 / TMEM GEMM, 0 = the GEMV kernels in
+ * slices of 8 rows, which compute every activation row on its own. Environment: INFENG_UMMA. */
 int infdev_set_umma(infdev_ctx* ctx, int enabled);
 /* Activation split of the fp16 tensor-core GEMV: 2 = hi+lo fp16 (fp32-accurate, default), 1 = hi only. */
 int infdev_set_xsplit(infdev_ctx* ctx, int xsplit);

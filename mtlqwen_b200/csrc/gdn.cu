@@ -97,10 +97,37 @@ __global__ void __launch_bounds__(256) gdn_prepare_kernel(const float* x, const 
 // its 128 q, k and v channels (the taps of the q / k channels are written by the first of the two value heads that
 // share a key head) and its beta / g dot products, with the same arithmetic and summation order; q, k, v, g, beta
 // are then not read. One launch less per layer for passes without prefill chunks.
+//
+// What bounds a decode launch is latency, not bytes: all 256 CTAs are resident at once, so the time is the longest
+// dependent chain of one CTA. The kernel therefore asks for everything up front and keeps block-wide barriers to two per
+// token:
+//  * before griddepcontrol.wait (these depend on nothing the preceding kernel writes): the gate-projection rows of the
+//    head, the conv weights and taps go to shared memory with cp.async (no registers held while in flight), then the 64
+//    KB state goes to registers; after the wait the token's input row follows. The small operands, which hit the L2,
+//    arrive and are consumed while the state is still on its way from HBM.
+//  * after the first barrier every thread derives the q / k norms and the two gates itself from the partial sums
+//    (redundantly; a second barrier to broadcast them costs more than 256 threads repeating a few instructions);
+//  * after the second barrier (partial products with the state) every warp sums the eight partials of its own four
+//    columns, so each has delta and the output for them without another barrier; warp 0 alone normalises, gates and
+//    stores the 128 outputs and runs the image protocol while the others update and store the state.
 struct GdnInputs {
   const float *x, *wBeta, *wAlpha, *A, *dt, *mixed, *convWeight;
   uint64_t convStateOffset;
+  bool ahead;  // the query table and the state records may be read before griddepcontrol.wait (see the kernel)
 };
+
+struct GdnStage {                      // dynamic shared memory of the fused form
+  float4 x[1024];                      // the token's input row (4096 values)
+  float4 wBeta[1024], wAlpha[1024];    // this head's rows of the two gate projections
+  float4 window[3][kHeadDim];          // conv taps of this CTA's q, k and v channels, rolled forward token by token
+  float4 convWeight[3][kHeadDim];
+};
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 template <bool FUSED>
 __global__ void __launch_bounds__(256, 2) delta_rule_kernel(const float* q, const float* k, const float* v, const float* g, const float* beta,
@@ -108,13 +135,46 @@ __global__ void __launch_bounds__(256, 2) delta_rule_kernel(const float* q, cons
                                                          uint64_t stateOffset, uint64_t stateBytes, float* out, uint8_t* image, int* counters,
                                                          uint32_t chunkedFrom, GdnInputs in) {
   pdl_launch_dependents();
-  pdl_wait();
+  // The weights never change. The query table and the state records were written by the first kernels of this pass and
+  // by the pass before it: when only the GEMV kernels and their followers are launched early, those have completed
+  // before the preceding kernel could start, and both may be read ahead of the wait. When every kernel of the pass is
+  // launched early nothing bounds how far ahead this one runs, and it waits first.
+  if (!in.ahead)
+    pdl_wait();
   const infdev_query info = queries[blockIdx.y];
   const int head = blockIdx.x, keyHead = head % kKeyHeads, tid = threadIdx.x, part = tid >> 5, lane = tid & 31;
   const bool speculative = info.state != kUnbound;
   if (chunkedFrom && !speculative && info.count >= chunkedFrom)  // delta_rule_chunked_kernel takes this query
     return;
-  __shared__ float qs[kHeadDim], ks[kHeadDim], red[12], partialPred[8][kHeadDim], partialQ[8][kHeadDim], delta[kHeadDim], scalars[4], dots[8];
+  extern __shared__ float4 stageRaw[];
+  GdnStage& stage = *reinterpret_cast<GdnStage*>(stageRaw);
+  __shared__ float qraw[kHeadDim], kraw[kHeadDim], vraw[kHeadDim], red[12], dots[8];
+  __shared__ float4 partialPred[8][32], partialQ[8][32];
+  const int channels[3] = {keyHead * kHeadDim + (tid & 127), 2048 + keyHead * kHeadDim + (tid & 127), 4096 + head * kHeadDim + (tid & 127)};
+  float headA = 0.f, headDt = 0.f;
+
+  if (FUSED) {
+    const float4* wb = reinterpret_cast<const float4*>(in.wBeta + size_t(head) * 4096);
+    const float4* wa = reinterpret_cast<const float4*>(in.wAlpha + size_t(head) * 4096);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      cp_async16(&stage.wBeta[tid + 256 * i], wb + tid + 256 * i);
+      cp_async16(&stage.wAlpha[tid + 256 * i], wa + tid + 256 * i);
+    }
+    if (tid < kHeadDim) {
+      const float4* taps = reinterpret_cast<const float4*>(info.previous + in.convStateOffset);
+#pragma unroll
+      for (int which = 0; which < 3; ++which) {
+        cp_async16(&stage.convWeight[which][tid], reinterpret_cast<const float4*>(in.convWeight) + channels[which]);
+        if (info.previous)
+          cp_async16(&stage.window[which][tid], taps + channels[which]);
+        else
+          stage.window[which][tid] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    cp_async_commit();
+    headA = in.A[head], headDt = in.dt[head];
+  }
 
   float4 S[16];
   if (info.previous) {
@@ -127,53 +187,70 @@ __global__ void __launch_bounds__(256, 2) delta_rule_kernel(const float* q, cons
     for (int i = 0; i < 16; ++i)
       S[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
+  if (in.ahead)
+    pdl_wait();
 
   for (uint32_t t = 0; t < info.count; ++t) {
     const size_t row = info.start + t;
-    // L2-normalise q (scaled by 1/sqrt(128)) and k; q.k of the normalised vectors (delta_rule.metal:281-311).
-    float qv = 0.f, kv = 0.f, vv = 0.f;
+    const size_t at = (row * kValueHeads + head) * kHeadDim + 4 * lane;  // warp 0: this lane's four outputs
+    float qv = 0.f, kv = 0.f, vv = 0.f, decay = 0.f, betaValue = 0.f;
     if (FUSED) {
+      float mixedNow[3] = {0.f, 0.f, 0.f};
+      if (tid < kHeadDim) {
+#pragma unroll
+        for (int which = 0; which < 3; ++which)
+          mixedNow[which] = in.mixed[row * kChannels + channels[which]];
+      }
+      const float4* xrow = reinterpret_cast<const float4*>(in.x + row * 4096);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        cp_async16(&stage.x[tid + 256 * i], xrow + tid + 256 * i);
+      cp_async_commit();
+      cp_async_wait_all();
+      __syncthreads();
       // beta / g: warps 0..3 share the dot product with wBeta, warps 4..7 the one with wAlpha (as gdn_prepare_kernel)
-      const float* weights = ((part >> 2) ? in.wAlpha : in.wBeta) + size_t(head) * 4096 + (part & 3) * 1024;
-      const float* src = in.x + row * 4096 + (part & 3) * 1024;
+      const float4* weights = ((part >> 2) ? stage.wAlpha : stage.wBeta) + (part & 3) * 256;
+      const float4* src = stage.x + (part & 3) * 256;
       float sum = 0.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float4 a = *reinterpret_cast<const float4*>(src + i * 128 + lane * 4), b = *reinterpret_cast<const float4*>(weights + i * 128 + lane * 4);
+        const float4 a = src[i * 32 + lane], b = weights[i * 32 + lane];
         sum += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
       }
       sum = warp_sum(sum);
       if (lane == 0)
         dots[part] = sum;
-    }
-    if (tid < kHeadDim) {
-      if (FUSED) {
-        // causal conv + SiLU of this head's q, k and v channel `tid` (gdn_causal_conv_silu, fused_kernels.metal:202-232)
-        const int channels[3] = {keyHead * kHeadDim + tid, 2048 + keyHead * kHeadDim + tid, 4096 + head * kHeadDim + tid};
-        const float* previous = reinterpret_cast<const float*>(info.previous + in.convStateOffset);
+      if (tid < kHeadDim) {
+        // causal conv + SiLU of this head's q, k and v channel `tid` (gdn_causal_conv_silu, fused_kernels.metal:202-232):
+        // the window holds the three tokens before this one, oldest first in .y (.x is the tap that falls out)
         float values[3];
 #pragma unroll
         for (int which = 0; which < 3; ++which) {
-          const int c = channels[which];
-          float context[4], acc = 0.f;
-#pragma unroll
-          for (int r = 0; r < 4; ++r) {
-            const int64_t position = int64_t(t) - 3 + r;
-            context[r] = position >= 0 ? in.mixed[(info.start + position) * kChannels + c] : info.previous ? previous[c * 4 + position + 4] : 0.f;
-            acc = fmaf(context[r], in.convWeight[c * 4 + r], acc);
-          }
+          const float4 taps = stage.window[which][tid], w4 = stage.convWeight[which][tid];
+          const float4 context = make_float4(taps.y, taps.z, taps.w, mixedNow[which]);
+          float acc = fmaf(context.x, w4.x, 0.f);
+          acc = fmaf(context.y, w4.y, acc), acc = fmaf(context.z, w4.z, acc), acc = fmaf(context.w, w4.w, acc);
           values[which] = silu_f(acc);
+          stage.window[which][tid] = context;
           if ((speculative || t + 1 == info.count) && (which == 2 || head < kKeyHeads)) {
-            float* state = reinterpret_cast<float*>(info.next + in.convStateOffset + (speculative ? uint64_t(t) * stateBytes : 0)) + c * 4;
-            *reinterpret_cast<float4*>(state) = make_float4(context[0], context[1], context[2], context[3]);
+            float* state = reinterpret_cast<float*>(info.next + in.convStateOffset + (speculative ? uint64_t(t) * stateBytes : 0)) + channels[which] * 4;
+            *reinterpret_cast<float4*>(state) = context;
           }
         }
         qv = values[0], kv = values[1], vv = values[2];
-      } else {
+      }
+    } else {
+      if (tid < kHeadDim) {
         qv = q[(row * kKeyHeads + keyHead) * kHeadDim + tid];
         kv = k[(row * kKeyHeads + keyHead) * kHeadDim + tid];
         vv = v[(row * kValueHeads + head) * kHeadDim + tid];
       }
+      decay = expf(g[row * kValueHeads + head]);
+      betaValue = beta[row * kValueHeads + head];
+    }
+    // L2-normalise q (scaled by 1/sqrt(128)) and k; q.k of the normalised vectors (delta_rule.metal:281-311).
+    if (tid < kHeadDim) {
+      qraw[tid] = qv, kraw[tid] = kv, vraw[tid] = vv;
       const float a = warp_sum(qv * qv), b = warp_sum(kv * kv), c = warp_sum(qv * kv);
       if (lane == 0) {
         red[part] = a;
@@ -182,77 +259,69 @@ __global__ void __launch_bounds__(256, 2) delta_rule_kernel(const float* q, cons
       }
     }
     __syncthreads();
-    if (tid < kHeadDim) {
-      const float qn = rsqrtf(red[0] + red[1] + red[2] + red[3] + 1.0e-6f) * 0.08838834764831845f;
-      const float kn = rsqrtf(red[4] + red[5] + red[6] + red[7] + 1.0e-6f);
-      qs[tid] = qv * qn;
-      ks[tid] = kv * kn;
-      if (tid == 0) {
-        scalars[0] = (red[8] + red[9] + red[10] + red[11]) * qn * kn;
-        if (FUSED) {
-          const float dotBeta = (dots[0] + dots[1]) + (dots[2] + dots[3]), dotAlpha = (dots[4] + dots[5]) + (dots[6] + dots[7]);
-          scalars[1] = expf(in.A[head] * logf(1.0f + expf(dotAlpha + in.dt[head])));
-          scalars[2] = 1.0f / (1.0f + expf(-dotBeta));
-        } else {
-          scalars[1] = expf(g[row * kValueHeads + head]);
-          scalars[2] = beta[row * kValueHeads + head];
-        }
-      }
+    float4 gate = make_float4(0.f, 0.f, 0.f, 0.f), weight = gate;
+    if (part == 0 && z)  // needed after the next barrier; asked for here
+      gate = *reinterpret_cast<const float4*>(z + at), weight = *reinterpret_cast<const float4*>(normWeight + 4 * lane);
+    const float qn = rsqrtf(red[0] + red[1] + red[2] + red[3] + 1.0e-6f) * 0.08838834764831845f;
+    const float kn = rsqrtf(red[4] + red[5] + red[6] + red[7] + 1.0e-6f);
+    const float qk = (red[8] + red[9] + red[10] + red[11]) * qn * kn;
+    if (FUSED) {
+      const float dotBeta = (dots[0] + dots[1]) + (dots[2] + dots[3]), dotAlpha = (dots[4] + dots[5]) + (dots[6] + dots[7]);
+      decay = expf(headA * logf(1.0f + expf(dotAlpha + headDt)));
+      betaValue = 1.0f / (1.0f + expf(-dotBeta));
     }
-    __syncthreads();
-    const float decay = scalars[1];
     float4 pred = make_float4(0.f, 0.f, 0.f, 0.f), qstate = pred;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const float kk = ks[part + 8 * i], qq = qs[part + 8 * i];
+      const float kk = kraw[part + 8 * i] * kn, qq = qraw[part + 8 * i] * qn;
       S[i].x *= decay, S[i].y *= decay, S[i].z *= decay, S[i].w *= decay;
       pred.x = fmaf(S[i].x, kk, pred.x), pred.y = fmaf(S[i].y, kk, pred.y), pred.z = fmaf(S[i].z, kk, pred.z), pred.w = fmaf(S[i].w, kk, pred.w);
       qstate.x = fmaf(S[i].x, qq, qstate.x), qstate.y = fmaf(S[i].y, qq, qstate.y), qstate.z = fmaf(S[i].z, qq, qstate.z),
       qstate.w = fmaf(S[i].w, qq, qstate.w);
     }
-    *reinterpret_cast<float4*>(&partialPred[part][lane * 4]) = pred;
-    *reinterpret_cast<float4*>(&partialQ[part][lane * 4]) = qstate;
+    partialPred[part][lane] = pred;
+    partialQ[part][lane] = qstate;
     __syncthreads();
-    float o = 0.f;
-    if (tid < kHeadDim) {
-      float p = 0.f, s = 0.f;
+    // every warp: the sums of the eight partials for its lanes' four columns, delta and the output there
+    float4 p4 = make_float4(0.f, 0.f, 0.f, 0.f), s4 = p4;
 #pragma unroll
-      for (int w = 0; w < 8; ++w) {
-        p += partialPred[w][tid];
-        s += partialQ[w][tid];
-      }
-      const float d = (vv - p) * scalars[2];
-      delta[tid] = d;
-      o = s + d * scalars[0];
-      const float ss = warp_sum(o * o);
-      if (lane == 0)
-        red[part] = ss;
+    for (int w = 0; w < 8; ++w) {
+      const float4 a = partialPred[w][lane], b = partialQ[w][lane];
+      p4.x += a.x, p4.y += a.y, p4.z += a.z, p4.w += a.w;
+      s4.x += b.x, s4.y += b.y, s4.z += b.z, s4.w += b.w;
     }
-    __syncthreads();
-    if (tid < kHeadDim) {
-      const size_t at = (row * kValueHeads + head) * kHeadDim + tid;
+    const float4 v4 = *reinterpret_cast<const float4*>(&vraw[4 * lane]);
+    const float4 d4 = make_float4((v4.x - p4.x) * betaValue, (v4.y - p4.y) * betaValue, (v4.z - p4.z) * betaValue, (v4.w - p4.w) * betaValue);
+    if (part == 0) {
+      float4 o = make_float4(s4.x + d4.x * qk, s4.y + d4.y * qk, s4.z + d4.z * qk, s4.w + d4.w * qk);
       if (z) {  // gated_rms_norm_128
-        const float scale = rsqrtf((red[0] + red[1] + red[2] + red[3]) / float(kHeadDim) + 1.0e-6f);
-        out[at] = o * scale * normWeight[tid] * silu_f(z[at]);
-      } else
-        out[at] = o;
-    }
-    // The count of the image protocol is taken before the state is written: the fence then covers only the 128 output
-    // stores, and the answer travels while the state update runs.
-    const bool imaged = image && row < kImageCounters / (kValueHeads / 2);  // block-uniform; later rows have no counter and get no image
-    __shared__ int arrivals;
-    const int entry = int(row) * (kValueHeads / 2) + (head >> 1);
-    if (imaged) {
-      __syncthreads();  // all of this CTA's stores to `out` are issued
-      if (tid == 0) {
-        __threadfence();
-        arrivals = atomicAdd(&counters[entry], 1);
+        const float scale = rsqrtf(warp_sum(o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w) / float(kHeadDim) + 1.0e-6f);
+        o = make_float4(o.x * scale * weight.x * silu_f(gate.x), o.y * scale * weight.y * silu_f(gate.y), o.z * scale * weight.z * silu_f(gate.z),
+                        o.w * scale * weight.w * silu_f(gate.w));
+      }
+      *reinterpret_cast<float4*>(out + at) = o;
+      if (image && row < kImageCounters / (kValueHeads / 2)) {  // later rows have no counter and get no image
+        const int entry = int(row) * (kValueHeads / 2) + (head >> 1);
+        __syncwarp();
+        int arrivals = 0;
+        if (lane == 0) {
+          __threadfence();
+          arrivals = atomicAdd(&counters[entry], 1);
+        }
+        if (__shfl_sync(0xffffffffu, arrivals, 0) == 1) {
+          __threadfence();
+          const float* src = out + (row * kValueHeads + (head & ~1)) * kHeadDim + lane * 8;
+          const float4 a = __ldcg(reinterpret_cast<const float4*>(src)), b = __ldcg(reinterpret_cast<const float4*>(src + 4));
+          const float values[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+          image_store_block(image + (size_t(row >> 3) * (kValueHeads / 2) + (head >> 1)) * kImageBlockBytes, int(row & 7), lane, values);
+          if (lane == 0)
+            counters[entry] = 0;
+        }
       }
     }
-    const float4 d4 = *reinterpret_cast<const float4*>(&delta[lane * 4]);
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const float kk = ks[part + 8 * i];
+      const float kk = kraw[part + 8 * i] * kn;
       S[i].x = fmaf(kk, d4.x, S[i].x), S[i].y = fmaf(kk, d4.y, S[i].y), S[i].z = fmaf(kk, d4.z, S[i].z), S[i].w = fmaf(kk, d4.w, S[i].w);
     }
     if (speculative || t + 1 == info.count) {
@@ -261,19 +330,8 @@ __global__ void __launch_bounds__(256, 2) delta_rule_kernel(const float* q, cons
       for (int i = 0; i < 16; ++i)
         dst[(part + 8 * i) * 32 + lane] = S[i];
     }
-    __syncthreads();  // qs/ks/delta/red are rewritten by the next token; `arrivals` is published
-    if (imaged) {
-      if (arrivals == 1 && tid < 32) {
-        __threadfence();
-        const float* src = out + (row * kValueHeads + (head & ~1)) * kHeadDim + tid * 8;
-        const float4 a = __ldcg(reinterpret_cast<const float4*>(src)), b = __ldcg(reinterpret_cast<const float4*>(src + 4));
-        const float values[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-        image_store_block(image + (size_t(row >> 3) * (kValueHeads / 2) + (head >> 1)) * kImageBlockBytes, int(row & 7), tid, values);
-        if (tid == 0)
-          counters[entry] = 0;
-      }
-      __syncthreads();  // `arrivals` is rewritten by the next token
-    }
+    if (t + 1 < info.count)
+      __syncthreads();  // the shared arrays are rewritten for the next token
   }
 }
 
@@ -493,8 +551,11 @@ cudaError_t gdn_decode_launch(const float* x, const float* mixed, const float* w
                               cudaStream_t stream) {
   if (queryCount <= 0)
     return cudaSuccess;
-  launch_kernel<2>(delta_rule_kernel<true>, dim3(kValueHeads, unsigned(queryCount)), 256, 0, stream, nullptr, nullptr, nullptr, nullptr, nullptr, z, normWeight,
-                   queries, stateOffset, stateBytes, out, image, counters, 0u, GdnInputs{x, wBeta, wAlpha, A, dt, mixed, convWeight, convStateOffset});
+  static PerDeviceOnce configured;
+  if (cudaError_t e = configure_shared_memory(delta_rule_kernel<true>, sizeof(GdnStage), configured))
+    return e;
+  launch_kernel<1>(delta_rule_kernel<true>, dim3(kValueHeads, unsigned(queryCount)), 256, sizeof(GdnStage), stream, nullptr, nullptr, nullptr, nullptr, nullptr, z, normWeight,
+                   queries, stateOffset, stateBytes, out, image, counters, 0u, GdnInputs{x, wBeta, wAlpha, A, dt, mixed, convWeight, convStateOffset, pdl_mode() != 1});
   return cudaGetLastError();
 }
 

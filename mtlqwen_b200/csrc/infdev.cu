@@ -17,15 +17,14 @@
 
 struct infdev_ctx {
   int device = 0, sms = 0, xsplit = 2;
-  int umma = 1;  // tcgen05 GEMM for Q4_K: 0 never, 1 for more than 8 rows, 2 always
+  int umma = 1;  // tcgen05 GEMM for Q4_K launches of more than 8 activation rows: 0 off, 1 on
   int integerDecode = 1;     // Q4_K decode GEMV: 1 integer-MMA kernel over an activation image, 0 fp16-MMA kernel
   uint8_t* image = nullptr;  // activation image for the integer decode kernel (K up to 16384)
   int* imageCounters = nullptr;        // arrival counters of the kernels that write images block by block (zero between launches)
   uint8_t* captureImage = nullptr;     // one-shot: where the next producer call writes the image of its result
   const uint8_t* supplyImage = nullptr;  // one-shot: image the next linear call reads instead of quantising x
   float* ummaPartial = nullptr;  // K-slice partial results of the tcgen05 prefill GEMM: [4][128][8192] floats, allocated on first use
-  void* ummaActs = nullptr;  // prepared activations + sums for the tcgen05 path (K up to 16384)
-  float* ummaSums = nullptr;
+  void* ummaActs = nullptr;  // fp16 activations laid out for the tcgen05 prefill GEMM (K up to 16384)
   std::atomic<uint64_t> launches{0};  // kernels launched through this context
   cudaStream_t stream = nullptr;
   cudaEvent_t done = nullptr;
@@ -165,7 +164,7 @@ infdev_ctx* infdev_create(int device, char* error) {
   if (const char* env = std::getenv("INFENG_XSPLIT"))
     ctx->xsplit = std::atoi(env) == 1 ? 1 : 2;
   if (const char* env = std::getenv("INFENG_UMMA"))
-    ctx->umma = std::atoi(env);
+    ctx->umma = std::atoi(env) != 0;
   if (const char* env = std::getenv("INFENG_INTEGER_DECODE"))
     ctx->integerDecode = std::atoi(env) != 0;
   if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess ||
@@ -176,7 +175,6 @@ infdev_ctx* infdev_create(int device, char* error) {
       (e = cudaMalloc(reinterpret_cast<void**>(&ctx->imageCounters), infdev::kImageCounters * sizeof(int))) != cudaSuccess ||
       (e = cudaMemset(ctx->imageCounters, 0, infdev::kImageCounters * sizeof(int))) != cudaSuccess ||
       (e = cudaMalloc(&ctx->ummaActs, size_t(64) * infdev::kUmmaMaxActBytesPerBlock)) != cudaSuccess ||
-      (e = cudaMalloc(reinterpret_cast<void**>(&ctx->ummaSums), size_t(64) * 64 * sizeof(float))) != cudaSuccess ||
       (e = cudaHostAlloc(reinterpret_cast<void**>(&ctx->statusHost), sizeof(int), cudaHostAllocDefault)) != cudaSuccess) {
     std::string text = std::string("context setup: ") + cudaGetErrorString(e);
     delete ctx;
@@ -198,7 +196,6 @@ void infdev_destroy(infdev_ctx* ctx) {
   cudaFree(ctx->imageCounters);
   cudaFree(ctx->ummaPartial);
   cudaFree(ctx->ummaActs);
-  cudaFree(ctx->ummaSums);
   cudaFreeHost(ctx->statusHost);
   cudaEventDestroy(ctx->done);
   cudaStreamDestroy(ctx->stream);
@@ -345,7 +342,7 @@ float infdev_event_elapsed_ms(infdev_ctx* ctx, void* start, void* stop) {
 }
 
 int infdev_set_umma(infdev_ctx* ctx, int enabled) {
-  ctx->umma = enabled < 0 ? 0 : enabled > 2 ? 2 : enabled;
+  ctx->umma = enabled != 0;
   return INFDEV_OK;
 }
 
@@ -446,7 +443,7 @@ static int linear_run(infdev_ctx* ctx, int type, bool pair, int count, const voi
     return fail(ctx, INFDEV_E_ARGUMENT, "gate_up: k must not exceed 4096");
   if (!aligned16(x) || (k % 4))
     return fail(ctx, INFDEV_E_ARGUMENT, "linear: activations must be 16-byte aligned");
-  bool umma = (ctx->umma == 2 || (ctx->umma == 1 && m > 8)) && type == INFDEV_Q4_K && k % 2048 == 0 && k <= 16384;
+  bool umma = ctx->umma && m > 8 && type == INFDEV_Q4_K && k % 2048 == 0 && k <= 16384;
   for (int i = 0; i < count; ++i)
     umma = umma && n[i] > 0 && n[i] % infdev::kUmmaTileRows == 0 && aligned16(w[i]) && (!pair || aligned16(w2[i]));
   if (umma) {
@@ -479,9 +476,8 @@ static int linear_run(infdev_ctx* ctx, int type, bool pair, int count, const voi
         return r;
     u.partial = ctx->ummaPartial;
     u.acts = static_cast<const uint8_t*>(ctx->ummaActs);
-    u.actSums = ctx->ummaSums;
     u.status = ctx->status;
-    const int64_t slice = m <= 8 ? 8 : 128;  // exact decode mode up to 8 rows, fp16-weight GEMM mode up to 128 rows per launch
+    const int64_t slice = 128;  // activation rows per launch
     for (int64_t row = 0; row < m; row += slice) {
       u.m = int(m - row < slice ? m - row : slice);
       for (int i = 0; i < count; ++i) {

@@ -37,19 +37,18 @@ constexpr int kImageCounters = 4096;  // arrival counters a context owns for blo
 constexpr int kActivationImageBlockBytes = 4384;  // act_image.cuh: image bytes per 256 activations x 8 rows
 
 // ---- tcgen05 path (umma.cu) ----
-constexpr int kUmmaTileRows = 128, kUmmaMaxActBytesPerBlock = 16 * 128 * 16 * 2;  // prefill mode: 64 KB of fp16 activations per super-block
+constexpr int kUmmaTileRows = 128, kUmmaMaxActBytesPerBlock = 16 * 128 * 16 * 2;  // 64 KB of fp16 activations per super-block
 
 struct UmmaParams {
   alignas(64) CUtensorMap map[4][2];  // box = one super-block (18 x 8 bytes) x 128 rows
   GemvSeg seg[4];
   int nseg, tiles;  // tiles of 128 rows
-  // Prefill mode, one matrix: K is cut into `splits` slices that different CTAs take; their partial results go to
+  // One matrix: K is cut into `splits` slices that different CTAs take; their partial results go to
   // `partial` [splits][m][n] and are summed (with the residual) by a second small kernel, in a fixed order.
   int splits;
   float* partial;
   int m, k;
-  const uint8_t* acts;   // prepared activations: k/256 blocks of kUmmaActBytesPerBlock
-  const float* actSums;  // [k/256][8 sub-blocks][8 rows]
+  const uint8_t* acts;   // prepared activations: k/256 blocks of kUmmaMaxActBytesPerBlock
   int* status;
 };
 

@@ -196,7 +196,7 @@ def test_bad_arguments_are_refused(dev):
   w, x, y = dev.empty(144 * 16, np.uint8), dev.empty((1, 256)), dev.empty((1, 16))
   assert dev.lib.infdev_linear(dev.ctx, D.Q4_K, w.ptr, 15, 256, x.ptr, 1, y.ptr, None) == -2
   assert dev.lib.infdev_linear(dev.ctx, D.Q4_K, w.ptr, 16, 200, x.ptr, 1, y.ptr, None) == -2
-  assert dev.lib.infdev_linear(dev.ctx, 13, w.ptr, 16, 256, x.ptr, 1, y.ptr, None) == -2
+  assert dev.lib.infdev_linear(dev.ctx, 2, w.ptr, 16, 256, x.ptr, 1, y.ptr, None) == -2  # Q4_0: not a type of these files
   assert "linear" in dev.error()
 
 
