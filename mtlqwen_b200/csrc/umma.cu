@@ -101,6 +101,45 @@ __device__ __forceinline__ uint64_t smem_descriptor(uint32_t address, uint32_t l
   return uint64_t((address & 0x3FFFFu) >> 4) | (uint64_t(leading >> 4) << 16) | (uint64_t(stride >> 4) << 32) | (uint64_t(1) << 46);
 }
 
+// The epilogue of one (item, matrix) accumulator for the 32 TMEM lanes (= weight rows = output columns) of the calling
+// warp: groups of eight activation rows `first`, `first + stride`, ... of the 16. Everything the store loop needs is
+// copied out of the parameter block first: the segment is a run-time index, so the block is reached through a generic
+// address, and the compiler must assume that the stores change it and would read pointer and pitch again after every
+// one of them (measured: 110 ns per store instead of 10).
+template <int NMAT> __device__ __forceinline__ void store_accumulator(const UmmaParams& p, int item, int mat, uint32_t accumulator, int row, int first,
+                                                                      int stride) {
+  const int tile = item % p.tiles, slice = item / p.tiles;
+  int segment = 0;
+  while (segment + 1 < p.nseg && tile >= p.seg[segment + 1].tile0)
+    ++segment;
+  float* const y = p.seg[segment].y;
+  const float* const residual = p.seg[segment].res;
+  const size_t pitch = size_t(p.seg[segment].ldy), column = size_t(tile - p.seg[segment].tile0) * kRows + row;
+  const int liveRows = p.m;
+  float* const partial = NMAT == 1 && p.splits > 1 ? p.partial + size_t(slice) * p.m * pitch : nullptr;
+  for (int c = first; c < kActs / 8 && c * 8 < liveRows; c += stride) {
+    float v[8];
+    tmem_load8(accumulator + c * 8, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int m = c * 8 + i;
+      if (m < liveRows) {
+        const size_t at = size_t(m) * pitch + column;
+        float value = v[i];
+        if (partial) {  // a K slice: the partial sums are added up, with the residual, by umma_reduce_kernel
+          partial[at] = value;
+          continue;
+        }
+        if (NMAT == 2)  // the gate half parks in y until the up half arrives (post == 2 epilogue, quant_linear.metal:224-232)
+          value = mat == 0 ? value : silu_f(y[at]) * value;
+        else if (residual)
+          value += residual[at];
+        y[at] = value;
+      }
+    }
+  }
+}
+
 template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_kernel(const __grid_constant__ UmmaParams p) {
   extern __shared__ uint8_t smemRaw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
@@ -113,6 +152,7 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
   // With p.splits > 1 (one matrix) the work items are (tile, K slice) pairs, so that a matrix of few 128-row tiles still
   // fills the GPU; `blocksPerRow` is then the super-blocks of one slice. One accumulator buffer per (item, matrix).
   const int blocksPerRow = p.k / 256 / p.splits, items = p.tiles * p.splits;
+  const uint32_t units = int(blockIdx.x) < items ? uint32_t((items - 1 - int(blockIdx.x)) / int(gridDim.x) + 1) * NMAT : 0u;  // accumulators of this CTA
   volatile int* abortFlag = &ctl.abort;
 
   if (tid == 0) {
@@ -293,6 +333,20 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
             mbar_arrive(&ctl.slotFree[slot]);
           }
         }
+    if (ok && units > 0) {
+      // their share of the CTA's last accumulator (see the epilogue warps): groups of eight activation rows 1 + group,
+      // 4 + group, ...; the accumulator has no later user, so nobody waits for these reads
+      const uint32_t unit = units - 1, buffer = unit & 1;
+      pdl_wait();
+      ok = mbar_wait_bounded(&ctl.dReady[buffer], (unit >> 1) & 1, abortFlag);
+      if (ok && NMAT == 2)  // the up half reads the gate half that the epilogue warps parked in y: wait until they are through with it
+        ok = mbar_wait_bounded(&ctl.dFree[(unit - 1) & 1], ((unit - 1) >> 1) & 1, abortFlag);
+      if (ok) {
+        fence_after_sync();
+        const int lastItem = int(blockIdx.x) + int((units - 1) / NMAT) * int(gridDim.x);
+        store_accumulator<NMAT>(p, lastItem, NMAT - 1, tmem + (uint32_t(quadrant * 32) << 16) + kColD + buffer * 128, row, 1 + group, 3);
+      }
+    }
     if (!ok && lane == 0) {
       *abortFlag = 1;
       atomicExch(p.status, kStatusBarrierTimeout);
@@ -304,46 +358,21 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
     const uint32_t laneBase = tmem + (uint32_t(quadrant * 32) << 16) + kColD;
     uint32_t unit = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
-      const int tile = item % p.tiles, slice = item / p.tiles;
-      int segment = 0;
-      while (segment + 1 < p.nseg && tile >= p.seg[segment + 1].tile0)
-        ++segment;
-      const GemvSeg& seg = p.seg[segment];
-      const size_t column = size_t(tile - seg.tile0) * kRows + row;
+    for (int item = blockIdx.x; item < items && ok; item += gridDim.x)
       for (int mat = 0; mat < NMAT && ok; ++mat, ++unit) {
         const uint32_t buffer = unit & 1;
         ok = mbar_wait_bounded(&ctl.dReady[buffer], (unit >> 1) & 1, abortFlag);
         if (!ok)
           break;
         fence_after_sync();
-        for (int c = 0; c < kActs / 8; ++c) {
-          float v[8];
-          tmem_load8(laneBase + buffer * 128 + c * 8, v);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int m = c * 8 + i;
-            if (m < p.m) {
-              const size_t at = size_t(m) * seg.ldy + column;
-              float value = v[i];
-              if (NMAT == 1 && p.splits > 1) {  // a K slice: the partial sums are added up, with the residual, by umma_reduce_kernel
-                p.partial[(size_t(slice) * p.m + m) * seg.ldy + column] = value;
-                continue;
-              }
-              if (NMAT == 2)  // the gate half parks in y until the up half arrives (post == 2 epilogue, quant_linear.metal:224-232)
-                value = mat == 0 ? value : silu_f(seg.y[at]) * value;
-              else if (seg.res)
-                value += seg.res[at];
-              seg.y[at] = value;
-            }
-          }
-        }
+        // the CTA's last accumulator: the dequant warps, idle by then, take two thirds of it
+        const bool last = unit + 1 == units;
+        store_accumulator<NMAT>(p, item, mat, laneBase + buffer * 128, row, 0, last ? 3 : 1);
         fence_before_sync();
         __syncwarp();
         if (lane == 0)
           mbar_arrive(&ctl.dFree[buffer]);
       }
-    }
     if (!ok && lane == 0) {
       *abortFlag = 1;
       atomicExch(p.status, kStatusBarrierTimeout);
@@ -361,16 +390,15 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
 // 4 * (s % 2) .. +3; TMEM column c of a step holds the nibbles of bytes (c % 2, c % 2 + 2) of word c / 2. Eight
 // consecutive k of a super-block are thus one 16-byte core-matrix row of a k-step (in the order 0,2,1,3,4,6,5,7), and a
 // thread turns two float4 loads into one 16-byte store.
-// grid (k / 256, 4), 256 threads: 128 rows x 32 groups of eight per super-block, four items per thread; a warp reads one
-// activation row's 256 values at a time.
+// grid (k / 256, 16), 256 threads: 128 rows x 32 groups of eight per super-block, one per thread; a warp reads one
+// activation row's 256 values.
 __global__ void __launch_bounds__(256) umma_prepare_rows_kernel(const float* x, int ldx, int m, __half* acts) {
   pdl_launch_dependents();
   pdl_wait();
   const int sb = blockIdx.x;
   __half* out = acts + size_t(sb) * (kActBytesPerSb / 2);
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int item = (blockIdx.y * 4 + j) * 256 + threadIdx.x, n = item >> 5, group = item & 31;
+  {
+    const int item = blockIdx.y * 256 + threadIdx.x, n = item >> 5, group = item & 31;
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
     if (n < m) {
       const float4* src = reinterpret_cast<const float4*>(x + size_t(n) * ldx + size_t(sb) * 256 + group * 8);
@@ -407,7 +435,7 @@ template <int NMAT> cudaError_t launch_tiles(const UmmaParams& p, const float* x
   static PerDeviceOnce configured;
   if (const cudaError_t e = configure_shared_memory(umma_linear_kernel<NMAT>, kSharedBytes, configured))
     return e;
-  launch_kernel(umma_prepare_rows_kernel, dim3(p.k / 256, 4), 256, 0, stream, x, ldx, p.m, reinterpret_cast<__half*>(const_cast<uint8_t*>(p.acts)));
+  launch_kernel(umma_prepare_rows_kernel, dim3(p.k / 256, 16), 256, 0, stream, x, ldx, p.m, reinterpret_cast<__half*>(const_cast<uint8_t*>(p.acts)));
   const int items = p.tiles * p.splits, grid = items < sms ? items : sms;
   launch_kernel<1>(umma_linear_kernel<NMAT>, grid, kThreads, kSharedBytes, stream, p);
   if (p.splits > 1) {
