@@ -45,7 +45,7 @@ DTYPE = ("f32 activations in HBM; Q4_K GEMV (<= 8 rows): u8 x int16-per-256-bloc
 
 def prompts(vocab=VOCAB, longest=4096):
   rng = np.random.default_rng(SEED + 4)
-  lengths = rng.integers(128, longest + 1, SEQUENCES)
+  lengths = rng.integers(min(128, longest), longest + 1, SEQUENCES)
   return [[int(t) for t in rng.integers(0, vocab, int(n))] for n in lengths]
 
 
@@ -458,7 +458,7 @@ def run_case(args):
   if args.case in ("step", "cfg5"):
     path = synth.ensure_full_model()
     if args.case == "step":  # decode steps of config 4; --context bounds the prompt lengths (short ones: few launches before the timed passes)
-      r = run_config4(args, local, path, None, longest=max(args.context, 130))
+      r = run_config4(args, local, path, None, longest=max(args.context, 1))
       print(json.dumps({"case": "step", "ms_per_step": 1e3 * r["device_seconds"] / max(r["passes"], 1), "passes": int(r["passes"]),
                         "launches": int(r["launches"]), "contexts": r["contexts"]}))
     else:
@@ -486,7 +486,7 @@ def main():
   parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
   parser.add_argument("--case", default=None, choices=("cfg1", "cfg1_m1", "lm_head", "prefill", "cfg2", "cfg2_prefill", "cfg3", "step", "cfg5"),
                       help="run one small case alone and print its line (the commands of the profile summaries)")
-  parser.add_argument("--context", type=int, default=160, help="--case step only: upper bound of the ragged prompt lengths (4096 = the headline workload)")
+  parser.add_argument("--context", type=int, default=160, help="--case step only: upper bound of the ragged prompt lengths (4096 = the headline workload; 1 = no prefill passes, for launch lists)")
   parser.add_argument("--no-cfg5", action="store_true", help="leave the config-5 block out of the line")
   args = parser.parse_args()
   args.warmup = max(args.warmup, 3)

@@ -355,6 +355,20 @@ template <class Q, int NMAT, int XSPLIT> __global__ void __launch_bounds__(kThre
     named_barrier(1, kConsumerWarps * kWarp);
 
     for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++tileCounter) {
+      // Where this thread's element of the tile goes and what is added to it (the residual, or the sum over the earlier
+      // K chunks), looked up and fetched before the arithmetic: the parameter block is reached through a generic address
+      // (the segment is a run-time index), and a chain of such reads after the reduction would delay every tile.
+      float* destination = nullptr;
+      float addend = 0.f;
+      if (tid < 128 && (tid >> 4) < p.m) {
+        const GemvSeg& seg = p.nseg == 1 ? p.seg[0] : p.seg[find_segment(p, tile)];
+        const size_t at = size_t(tid >> 4) * seg.ldy + size_t(tile - seg.tile0) * kTileRows + (tid & 15);
+        destination = seg.y + at;
+        if (NMAT == 1 && chunk > 0)
+          addend = *destination;
+        else if (NMAT == 1 && seg.res)
+          addend = seg.res[at];
+      }
       float total[NMAT][4];
 #pragma unroll
       for (int mat = 0; mat < NMAT; ++mat)
@@ -401,7 +415,6 @@ template <class Q, int NMAT, int XSPLIT> __global__ void __launch_bounds__(kThre
       }
       named_barrier(1, kConsumerWarps * kWarp);
       if (tid < 128) {
-        const int row = tid >> 4, local = tid & 15;
         float sum[NMAT];
 #pragma unroll
         for (int mat = 0; mat < NMAT; ++mat) {
@@ -410,18 +423,8 @@ template <class Q, int NMAT, int XSPLIT> __global__ void __launch_bounds__(kThre
           for (int w = 0; w < kConsumerWarps; ++w)
             sum[mat] += mine[(mat * kConsumerWarps + w) * 128 + tid];
         }
-        if (row < p.m) {
-          const GemvSeg& seg = p.seg[find_segment(p, tile)];
-          const size_t at = size_t(row) * seg.ldy + size_t(tile - seg.tile0) * kTileRows + local;
-          float value = sum[0];
-          if (NMAT == 2)
-            value = silu_f(sum[0]) * sum[1];
-          else if (chunk > 0)
-            value += seg.y[at];
-          else if (seg.res)
-            value += seg.res[at];
-          seg.y[at] = value;
-        }
+        if (destination)
+          *destination = NMAT == 2 ? silu_f(sum[0]) * sum[NMAT - 1] : sum[0] + addend;
       }
     }
   }

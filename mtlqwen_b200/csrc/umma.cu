@@ -16,12 +16,13 @@
 // flag, records a status code, and every role leaves its loops.
 // The fp16 activations of a super-block are 64 KB, so weight slabs and activations travel through separate rings, the
 // activations in two halves of eight k-steps each: 3 slab stages + 5 half stages keep two and a half super-blocks in
-// flight. Three 18 KB slabs in flight per SM are far too few to stream weights from HBM at speed, so the producer warp
-// first asks for the whole tile (and the next one of this CTA) with L2 prefetches, which need no shared memory; the
-// slab copies then hit the L2.
+// flight. The producer warp first asks the L2 for the whole tile (and the next one of this CTA) with bulk prefetches,
+// which need no shared memory, so that three 18 KB slab copies in flight are enough.
 // The kernel is launched programmatically dependent on the kernel that lays out the activations: set-up, the
 // prefetches and the first weight slab run while that one is still at work, and only the activation copies and the
 // epilogue wait for it.
+// Measured at 12288 x 4096 x 128 rows: 1.18 us per super-block (the 16 MMAs of a super-block keep the tensor pipe busy
+// for about two thirds of that), 31 us per call of which 4 us are the layout kernel; 96 tiles occupy 96 of 148 SMs.
 #include "common.cuh"
 #include "kernels.h"
 
