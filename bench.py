@@ -133,7 +133,7 @@ def cpu_decode(path, contexts, steps, warmup, seconds_budget=None):
 
 
 def cpu_configs():
-  """BASELINE configs 1 to 3 on the CPU oracle, single-threaded and on all host cores (median of 3 runs each), on the
+  """BASELINE configs 1 to 3 on the CPU oracle, single-threaded and on all host cores (median of 5 runs each), on the
   seeded inputs of the GPU cases: the Q4_K linear 12288 x 4096 with 8 rows, one GDN layer decode step of 8 sequences,
   and decode attention over 8 contexts uniform in [1, 32768]."""
   cores = host_threads()
@@ -172,7 +172,7 @@ def cpu_configs():
     for label, threads in (("one_thread_ms", 1), ("all_cores_ms", cores)):
       oracle.set_threads(threads)
       samples = []
-      for _ in range(3):
+      for _ in range(5):
         started = time.perf_counter()
         call()
         samples.append(time.perf_counter() - started)
