@@ -24,7 +24,10 @@ typedef struct infeng_sequence infeng_sequence;
  * 0), INFENG_KV_BLOCKS (physical 128-token K/V blocks, default ceil(context/128) as engine.cpp:86),
  * INFENG_DRAFT_WIDTH (MTP proposals per step, default 2 as forward.cpp:139), INFENG_SEED (base of the sampling
  * keys: sequence number i of an engine draws from a Philox stream keyed by (seed, i); default the clock), INFENG_CHECKPOINTS (entries of the prefix-checkpoint cache, default 8 as qwen35.hpp:24; each holds one state record),
- * INFENG_BLOCK_TOKENS, INFENG_COMMIT_TIMEOUT_MS, INFENG_GRAPHS (0 disables CUDA-graph replay of decode passes). */
+ * INFENG_BLOCK_TOKENS, INFENG_COMMIT_TIMEOUT_MS, INFENG_GRAPHS (0 disables CUDA-graph replay of decode passes),
+ * INFENG_BATCH_INVARIANT (1: every row goes through kernels that treat it on its own, the GEMV kernels for any row
+ * count and the token-by-token delta rule, so a sequence's tokens are the same bits whatever shares its passes and
+ * however the scheduler cut its prompt; prefill is several times slower). */
 infeng_engine* infeng_engine_create(const char* weights, const char* draftWeights, const char* kernels, uint32_t context, char* error);
 /* engine.cpp:251-254: drops one reference; the engine dies with its last sequence. */
 void infeng_engine_release(infeng_engine* engine);

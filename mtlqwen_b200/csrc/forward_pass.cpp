@@ -204,7 +204,7 @@ struct Ops {
                                  scratch.gdnG.as<float>()));
         capture(scratch.temporaryImage);
         // a pass that carries prefill chunks lets its long queries take the chunked kernel
-        check((rows > imageRows ? infdev_delta_rule_prefill : infdev_delta_rule)(ctx, scratch.q.as<float>(), scratch.k.as<float>(), scratch.v.as<float>(),
+        check((rows > imageRows && !engine.batchInvariant ? infdev_delta_rule_prefill : infdev_delta_rule)(ctx, scratch.q.as<float>(), scratch.k.as<float>(), scratch.v.as<float>(),
                                                                                  scratch.gdnG.as<float>(), scratch.gdnB.as<float>(),
                                                                                  scratch.gate.as<float>(), f32("ssm_norm.weight"), queries,
                                                                                  int(queryCount), offset + INFDEV_CONV_STATE_BYTES,

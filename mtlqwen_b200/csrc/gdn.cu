@@ -19,6 +19,13 @@ namespace {
 constexpr int kChannels = 8192, kHeadDim = 128, kValueHeads = 32, kKeyHeads = 16;
 constexpr uint32_t kUnbound = 0xffffffffu;
 
+// The four products of a gate dot-product step with the roundings spelled out: the preparation kernel and the fused
+// decode kernel must agree bit for bit (a token's result may not depend on which kind of pass computed it), and the
+// compiler is otherwise free to contract a.x*b.x + a.y*b.y + ... differently in the two.
+__device__ __forceinline__ float dot4(const float4& a, const float4& b) {
+  return __fmaf_rn(a.w, b.w, __fmaf_rn(a.z, b.z, __fmaf_rn(a.y, b.y, __fmul_rn(a.x, b.x))));
+}
+
 __device__ __forceinline__ const infdev_query& query_of_row(const infdev_query* queries, uint32_t row) {
   while (row >= queries->start + queries->count)
     ++queries;
@@ -46,7 +53,7 @@ __global__ void __launch_bounds__(256) gdn_prepare_kernel(const float* x, const 
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const float4 a = *reinterpret_cast<const float4*>(src + i * 128 + lane * 4), b = *reinterpret_cast<const float4*>(weights + i * 128 + lane * 4);
-      sum += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+      sum += dot4(a, b);
     }
     sum = warp_sum(sum);
     __shared__ float parts[8];
@@ -215,7 +222,7 @@ __global__ void __launch_bounds__(256, 2) delta_rule_kernel(const float* q, cons
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const float4 a = src[i * 32 + lane], b = weights[i * 32 + lane];
-        sum += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+        sum += dot4(a, b);
       }
       sum = warp_sum(sum);
       if (lane == 0)

@@ -48,7 +48,8 @@ struct UmmaParams {
   int splits;
   float* partial;
   int m, k;
-  const uint8_t* acts;   // prepared activations: k/256 blocks of kUmmaMaxActBytesPerBlock
+  int actRows;           // MMA N: m rounded up to a multiple of 16 (set by umma_launch)
+  const uint8_t* acts;   // prepared activations: k/256 blocks of actRows x 512 bytes
   int* status;
 };
 

@@ -72,6 +72,10 @@ struct Engine {
   uint32_t maxContext, draftWidth = 0;
   uint32_t targetLayers = 0, kvLayers = 0, gdnLayers = 0, vocab = 0, blockTokens = 128;
   uint32_t maxCheckpoints = 8;  // entries of the prefix-checkpoint cache (qwen35.hpp:24); INFENG_CHECKPOINTS overrides
+  // INFENG_BATCH_INVARIANT=1: every row is computed by kernels that treat it on its own (the GEMV kernels for any row
+  // count instead of the tensor-core GEMM, the token-by-token delta rule instead of the 16-token chunks), so a
+  // sequence's tokens are the same bits whatever shares its passes and however its prompt was cut. Prefill is slower.
+  bool batchInvariant = false;
   uint64_t stateBytes = 0;
   std::unique_ptr<PagedKV> kv;
   Weights weights;

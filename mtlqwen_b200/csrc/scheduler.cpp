@@ -185,6 +185,9 @@ Engine::Engine(const std::filesystem::path& path, uint32_t context, const std::f
   device.commitTimeoutMs = environment("INFENG_COMMIT_TIMEOUT_MS", 120000);
   useGraphs = environment("INFENG_GRAPHS", 1) != 0;
   maxCheckpoints = std::max(1u, environment("INFENG_CHECKPOINTS", 8));
+  batchInvariant = environment("INFENG_BATCH_INVARIANT", 0) != 0;
+  if (batchInvariant)
+    infdev_set_umma(device.ctx, 0);
   // The reference sizes the physical pool for one sequence of maximum context (engine.cpp:86); INFENG_KV_BLOCKS overrides.
   const uint32_t perSlot = (context + blockTokens - 1) / blockTokens;
   blocks.resize(environment("INFENG_KV_BLOCKS", perSlot));

@@ -30,13 +30,13 @@ namespace infdev {
 namespace {
 
 constexpr int kRows = kUmmaTileRows;      // weight rows per tile = TMEM lanes
-constexpr int kActs = 128;                // activation rows per launch = MMA N
+constexpr int kActs = 128;                // most activation rows per launch; the MMA N is the live rows rounded up to 16
 constexpr int kSlabBytes = kRows * 144;   // 18,432
 constexpr int kThreads = 512;
 constexpr int kStages = 3, kActStages = 5;
-constexpr int kActBytesPerSb = 16 * kActs * 16 * 2, kActHalfBytes = kActBytesPerSb / 2;  // 16 k-steps x [128 x 16] fp16
-// kind::f16 instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = 128, M = 128
-constexpr uint32_t kInstruction = (1u << 4) | (uint32_t(kActs >> 3) << 17) | (uint32_t(kRows >> 4) << 24);
+constexpr int kActHalfBytes = 8 * kActs * 16 * 2;  // ring stage: 8 k-steps x [128 x 16] fp16; a launch of N rows uses N x 256 of it
+// kind::f16 instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, M = 128
+__device__ __forceinline__ uint32_t instruction_descriptor(int n) { return (1u << 4) | (uint32_t(n >> 3) << 17) | (uint32_t(kRows >> 4) << 24); }
 constexpr int kTmemCols = 512;
 constexpr uint32_t kColA = 0, kColD = 256;  // A: 2 x 128 columns; D: 2 x 128 columns
 
@@ -198,6 +198,7 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
     };
     if (int(blockIdx.x) < items)
       prefetch(blockIdx.x);
+    const uint32_t halfBytes = uint32_t(p.actRows) * 256;  // 8 k-steps x [actRows x 16] fp16
     uint32_t it = 0;
     bool ok = true, waited = false;
     for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
@@ -227,9 +228,8 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
               if (actRound > 0)
                 ok = mbar_wait_bounded(&ctl.actFree[actSlot], (actRound - 1) & 1, abortFlag);
               if (ok) {
-                mbar_arrive_expect_tx(&ctl.actFull[actSlot], kActHalfBytes);
-                bulk_load(actRing + size_t(actSlot) * kActHalfBytes, p.acts + size_t(sb) * kActBytesPerSb + size_t(h) * kActHalfBytes, kActHalfBytes,
-                          &ctl.actFull[actSlot]);
+                mbar_arrive_expect_tx(&ctl.actFull[actSlot], halfBytes);
+                bulk_load(actRing + size_t(actSlot) * kActHalfBytes, p.acts + (size_t(sb) * 2 + h) * halfBytes, halfBytes, &ctl.actFull[actSlot]);
               }
             }
             if (!ok) {
@@ -245,6 +245,7 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
     if (lane == 0) {
       uint32_t it = 0, unit = 0;
       bool ok = true;
+      const uint32_t instruction = instruction_descriptor(p.actRows), stepBytes = uint32_t(p.actRows) * 32;
       for (int item = blockIdx.x; item < items && ok; item += gridDim.x)
         for (int mat = 0; mat < NMAT && ok; ++mat, ++unit) {
           const uint32_t buffer = unit & 1;
@@ -263,8 +264,8 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
               const uint32_t actBase = smem_u32(actRing + size_t(actSlot) * kActHalfBytes);
 #pragma unroll
               for (int step = 0; step < 8; ++step)
-                umma_ts(dColumn, tmem + kColA + aBuffer * 128 + (8 * h + step) * 8, smem_descriptor(actBase + step * (kActs * 32), 128, 256),
-                        kInstruction, (j | h | step) != 0);
+                umma_ts(dColumn, tmem + kColA + aBuffer * 128 + (8 * h + step) * 8, smem_descriptor(actBase + step * stepBytes, 128, 256), instruction,
+                        (j | h | step) != 0);
               umma_commit(&ctl.actFree[actSlot]);
             }
             if (!ok)
@@ -391,13 +392,13 @@ template <int NMAT> __global__ void __launch_bounds__(kThreads, 1) umma_linear_k
 // 4 * (s % 2) .. +3; TMEM column c of a step holds the nibbles of bytes (c % 2, c % 2 + 2) of word c / 2. Eight
 // consecutive k of a super-block are thus one 16-byte core-matrix row of a k-step (in the order 0,2,1,3,4,6,5,7), and a
 // thread turns two float4 loads into one 16-byte store.
-// grid (k / 256, 16), 256 threads: 128 rows x 32 groups of eight per super-block, one per thread; a warp reads one
-// activation row's 256 values.
-__global__ void __launch_bounds__(256) umma_prepare_rows_kernel(const float* x, int ldx, int m, __half* acts) {
+// grid (k / 256, actRows / 8), 256 threads: actRows x 32 groups of eight per super-block, one per thread; a warp reads
+// one activation row's 256 values.
+__global__ void __launch_bounds__(256) umma_prepare_rows_kernel(const float* x, int ldx, int m, int actRows, __half* acts) {
   pdl_launch_dependents();
   pdl_wait();
   const int sb = blockIdx.x;
-  __half* out = acts + size_t(sb) * (kActBytesPerSb / 2);
+  __half* out = acts + size_t(sb) * (actRows * 256);
   {
     const int item = blockIdx.y * 256 + threadIdx.x, n = item >> 5, group = item & 31;
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
@@ -409,7 +410,7 @@ __global__ void __launch_bounds__(256) umma_prepare_rows_kernel(const float* x, 
     uint4 packed;
     packed.x = *reinterpret_cast<const uint32_t*>(&h0), packed.y = *reinterpret_cast<const uint32_t*>(&h1);
     packed.z = *reinterpret_cast<const uint32_t*>(&h2), packed.w = *reinterpret_cast<const uint32_t*>(&h3);
-    *reinterpret_cast<uint4*>(out + size_t(group >> 1) * (kActs * 16) + (n >> 3) * 128 + (group & 1) * 64 + (n & 7) * 8) = packed;
+    *reinterpret_cast<uint4*>(out + size_t(group >> 1) * (actRows * 16) + (n >> 3) * 128 + (group & 1) * 64 + (n & 7) * 8) = packed;
   }
 }
 
@@ -432,11 +433,16 @@ __global__ void __launch_bounds__(256) umma_reduce_kernel(const float* partial, 
   *reinterpret_cast<float4*>(y + at) = sum;
 }
 
-template <int NMAT> cudaError_t launch_tiles(const UmmaParams& p, const float* x, int ldx, int sms, cudaStream_t stream) {
+template <int NMAT> cudaError_t launch_tiles(const UmmaParams& params, const float* x, int ldx, int sms, cudaStream_t stream) {
   static PerDeviceOnce configured;
   if (const cudaError_t e = configure_shared_memory(umma_linear_kernel<NMAT>, kSharedBytes, configured))
     return e;
-  launch_kernel(umma_prepare_rows_kernel, dim3(p.k / 256, 16), 256, 0, stream, x, ldx, p.m, reinterpret_cast<__half*>(const_cast<uint8_t*>(p.acts)));
+  // The MMA is as wide as the launch has rows, in steps of 16: a speculative pass of 40 rows moves 24 KB of activations
+  // per super-block instead of 64 KB and spends a third of the tensor time.
+  UmmaParams p = params;
+  p.actRows = (p.m + 15) / 16 * 16;
+  launch_kernel(umma_prepare_rows_kernel, dim3(p.k / 256, p.actRows / 8), 256, 0, stream, x, ldx, p.m, p.actRows,
+                reinterpret_cast<__half*>(const_cast<uint8_t*>(p.acts)));
   const int items = p.tiles * p.splits, grid = items < sms ? items : sms;
   launch_kernel<1>(umma_linear_kernel<NMAT>, grid, kThreads, kSharedBytes, stream, p);
   if (p.splits > 1) {

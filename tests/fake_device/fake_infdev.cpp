@@ -103,6 +103,7 @@ void infdev_graph_destroy(infdev_ctx*, void*) {}
 size_t infdev_image_bytes(int64_t rows, int64_t k) { return size_t((rows + 7) / 8) * size_t(k / 256) * 4384; }
 int infdev_image_capture(infdev_ctx*, uint8_t*) { return 0; }
 int infdev_image_supply(infdev_ctx*, const uint8_t*) { return 0; }
+int infdev_set_umma(infdev_ctx*, int) { return 0; }
 size_t infdev_attention_scratch_bytes(int64_t rows, uint32_t maxSplits) { return size_t(rows) * 16 * maxSplits * 260 * sizeof(float); }
 
 int infdev_linear(infdev_ctx* ctx, int, const void*, int64_t, int64_t, const float*, int64_t, float*, const float*) { return ++ctx->launches, 0; }

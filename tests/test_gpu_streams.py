@@ -23,15 +23,17 @@ def weights(tmp_path_factory):
 
 
 def make_engine(weights):
-  """INFENG_UMMA=0 keeps every projection on the GEMV kernels, which compute each activation row on its own: a row's
-  logits are then the same bits in a 40-row speculative pass and in a single-row pass, and sampled streams can be
-  compared token for token. (With the tensor-core GEMM taking the passes of more than 8 rows, as by default, the two
-  differ by some 1e-4, which a top-p boundary turns into a different token every few dozen samples.)"""
-  os.environ.update(INFENG_DRAFT_WIDTH=str(WIDTH), INFENG_SEED="9", INFENG_KV_BLOCKS="256", INFENG_UMMA="0")
+  """INFENG_BATCH_INVARIANT=1 keeps every projection on the GEMV kernels and the delta rule on its token-by-token form,
+  which compute each row on its own: a row's logits are then the same bits in a 40-row speculative pass and in a
+  single-row pass, and however the scheduler cut the prompt into pieces, so sampled streams can be compared token for
+  token. (By default the tensor-core GEMM takes the passes of more than 8 rows and prompt pieces go through the
+  delta rule in 16-token chunks counted from where a piece starts; both differ from the row-wise kernels by some 1e-4,
+  which a top-p boundary turns into a different token every few dozen samples.)"""
+  os.environ.update(INFENG_DRAFT_WIDTH=str(WIDTH), INFENG_SEED="9", INFENG_KV_BLOCKS="256", INFENG_BATCH_INVARIANT="1")
   try:
     return InferenceEngine(weights, draft_weights=weights, max_context=4096)
   finally:
-    os.environ.pop("INFENG_DRAFT_WIDTH"), os.environ.pop("INFENG_KV_BLOCKS"), os.environ.pop("INFENG_UMMA")
+    os.environ.pop("INFENG_DRAFT_WIDTH"), os.environ.pop("INFENG_KV_BLOCKS"), os.environ.pop("INFENG_BATCH_INVARIANT")
 
 
 def generate(engine, prompt, seed, speculative=True):
