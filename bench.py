@@ -356,8 +356,9 @@ def config5_block(local, rank, world, path, dist, generated=GENERATED):
 
 
 # ---- single-kernel configurations ---------------------------------------------------------------------------------
-def kernel_configs(local):
-  """Configs 1 to 3, lm_head and the prefill GEMM on one GPU: microseconds per launch and the algorithmic rate."""
+def kernel_configs(local, contexts):
+  """Configs 1 to 3, lm_head, the prefill GEMM and one attention layer at the decode step's contexts on one GPU:
+  microseconds per launch and the algorithmic rate."""
   from mtlqwen_b200 import device as D
   from mtlqwen_b200.testing import cases
   dev = D.Device(local)
@@ -371,6 +372,7 @@ def kernel_configs(local):
     out["cfg2_gdn_decode"] = cases.gdn_case(dev)
     out["cfg2_gdn_prefill"] = cases.gdn_prefill_case(dev)
     out["cfg3_attention"] = cases.attention_case(dev)
+    out["attention_layer_at_step_contexts"] = cases.attention_case(dev, contexts=contexts, block_tokens=128, layers=8, replays=20)
     prefill = cases.linear_case(dev, m=128, copies=8, replays=5)
     prefill["TFLOPs"] = 2.0 * 128 * 12288 * 4096 / prefill["us"] / 1e6
     out["prefill_gemm_m128"] = prefill
@@ -396,7 +398,7 @@ def run_ours(args, rank, world):
     dist.barrier()
   path = synth.full_model_path()
   r = run_config4(args, local, path, dist)
-  kernels = kernel_configs(local) if rank == 0 else None
+  kernels = kernel_configs(local, r["contexts"]) if rank == 0 else None
   cfg5 = None if args.no_cfg5 else config5_block(local, rank, world, path, dist)
   peak, peak_kind = measured_peak()
 
@@ -472,6 +474,8 @@ def run_case(args):
       "lm_head": lambda: cases.linear_case(dev, qtype=D.Q6_K, n=65536, copies=2, replays=2),
       "prefill": lambda: cases.linear_case(dev, m=128, **small), "cfg2": lambda: cases.gdn_case(dev, replays=2),
       "cfg2_prefill": lambda: cases.gdn_prefill_case(dev, replays=1), "cfg3": lambda: cases.attention_case(dev, replays=2),
+      # one attention layer at contexts like those of the config-4 decode step
+      "attention_step": lambda: cases.attention_case(dev, contexts=[2728, 4044, 899, 546, 1176, 3424, 3129, 2627], block_tokens=128, layers=8, replays=2),
     }
     print(json.dumps({"case": args.case, **table[args.case]()}))
   finally:
@@ -484,7 +488,7 @@ def main():
   parser.add_argument("--steps", type=int, default=128)
   parser.add_argument("--warmup", type=int, default=16)
   parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
-  parser.add_argument("--case", default=None, choices=("cfg1", "cfg1_m1", "lm_head", "prefill", "cfg2", "cfg2_prefill", "cfg3", "step", "cfg5"),
+  parser.add_argument("--case", default=None, choices=("cfg1", "cfg1_m1", "lm_head", "prefill", "cfg2", "cfg2_prefill", "cfg3", "attention_step", "step", "cfg5"),
                       help="run one small case alone and print its line (the commands of the profile summaries)")
   parser.add_argument("--context", type=int, default=160, help="--case step only: upper bound of the ragged prompt lengths (4096 = the headline workload; 1 = no prefill passes, for launch lists)")
   parser.add_argument("--no-cfg5", action="store_true", help="leave the config-5 block out of the line")

@@ -137,12 +137,15 @@ def gdn_prefill_case(dev, sequences=8, seed=9, replays=3):
   return {"us": micros, "rows": rows, "rows_per_s": rows / micros * 1e6, "longest_chunk": max(lengths), "lengths": lengths}
 
 
-def attention_case(dev, sequences=8, longest=32768, block_tokens=16, replays=10, seed=7):
+def attention_case(dev, sequences=8, longest=32768, block_tokens=16, replays=10, seed=7, contexts=None, layers=1):
   """BASELINE config 3: decode attention of `sequences` rows over paged fp16 K/V with contexts uniform in [1, longest],
   16-token blocks bound through a random permutation of the pool; scan + reduce, 4096 bytes of K and V per attended
-  token. The pool (about half a gigabyte) is larger than the L2."""
+  token. The pool (about half a gigabyte) is larger than the L2. With `contexts` given (the decode step's: a few
+  thousand tokens, where one layer's K/V would fit the L2) the launches cycle over `layers` pools, as the attention
+  layers of the model do."""
   rng = np.random.default_rng(seed)
-  contexts = [int(c) for c in rng.integers(1, longest + 1, sequences)]
+  contexts = [int(c) for c in contexts] if contexts is not None else [int(c) for c in rng.integers(1, longest + 1, sequences)]
+  sequences = len(contexts)
   blocks = [-(-c // block_tokens) for c in contexts]
   stride, physical = max(blocks), int(sum(blocks))
   permutation = rng.permutation(physical).astype(np.int32)
@@ -151,8 +154,10 @@ def attention_case(dev, sequences=8, longest=32768, block_tokens=16, replays=10,
     table[i, :count] = permutation[at:at + count]
     at += count
   pool = (physical, 4, block_tokens, 256)
-  keys = dev.array(rng.standard_normal(pool, dtype=np.float32).astype(np.float16).view(np.uint16))
-  values = dev.array(rng.standard_normal(pool, dtype=np.float32).astype(np.float16).view(np.uint16))
+  pools = []
+  for _ in range(layers):
+    pools.append((dev.array(rng.standard_normal(pool, dtype=np.float32).astype(np.float16).view(np.uint16)),
+                  dev.array(rng.standard_normal(pool, dtype=np.float32).astype(np.float16).view(np.uint16))))
   queries = []
   for i, context in enumerate(contexts):
     q = D.Query()
@@ -163,9 +168,9 @@ def attention_case(dev, sequences=8, longest=32768, block_tokens=16, replays=10,
   q, out = dev.array(rng.standard_normal((sequences, 16, 256)).astype(np.float32)), dev.empty((sequences, 16, 256))
   partials = dev.empty(dev.attention_scratch_bytes(sequences, 32) // 4)
 
-  def launch(_):
-    dev.attention(q, qg, keys, values, dq, sequences, sequences, dtable, stride, block_tokens, 32, partials, out)
+  def launch(item):
+    dev.attention(q, qg, item[0], item[1], dq, sequences, sequences, dtable, stride, block_tokens, 32, partials, out)
 
-  micros = timed(dev, launch, [None], replays, graph=False)
+  micros = timed(dev, launch, pools, replays, graph=layers > 1)
   algorithmic = sum(contexts) * 4096
-  return {"us": micros, "bytes": int(algorithmic), "GBs": algorithmic / micros / 1e3, "contexts": contexts, "launches_timed": replays}
+  return {"us": micros, "bytes": int(algorithmic), "GBs": algorithmic / micros / 1e3, "contexts": contexts, "launches_timed": replays * layers}
