@@ -218,7 +218,8 @@ int infdev_mtp_fuse(infdev_ctx* ctx, const float* embedding, const float* hidden
 int infdev_sample(infdev_ctx* ctx, const float* logits, int64_t vocab, infdev_query* queries, int queryCount, int64_t count, uint32_t mode,
                   int32_t* tokens);
 /* The packing loop of forward() (forward.cpp:171-191) on the device. in[i].samples carries the slot's
- * requested-token count. meta[4] receives rows, logit rows, flags (1 sequential, 2 prefill), packed count. */
+ * requested-token count. meta[4] receives rows, logit rows, flags (1 sequential, 2 prefill), packed count. At most 32
+ * queries (one lane each). */
 int infdev_pack_queries(infdev_ctx* ctx, const infdev_query* in, int count, int drafting, uint32_t draftWidth, const uint64_t* statePrevious,
                         const uint64_t* stateNext, uint64_t candidateBase, uint64_t stateBytes, infdev_query* out, uint32_t* meta);
 /* The acceptance loop of Engine::schedule (engine.cpp:205-216) on the device, for every query of a target pass:

@@ -101,7 +101,7 @@ __device__ __forceinline__ void copy_async16(void* dst, const void* src, uint32_
 // chain of load latencies. Both contractions run on the tensor cores as m16n8k16 with fp16 operands split hi + lo where
 // they are not fp16 already: warp 0 scores the tile's 16 tokens for the four query heads of the group, then warp w
 // accumulates the weighted values of dims 64w .. 64w+63 for all four heads.
-__global__ void __launch_bounds__(128, 4) attention_scan_kernel(const float* q, const __half* cacheK, const __half* cacheV,
+__global__ void __launch_bounds__(128, 6) attention_scan_kernel(const float* q, const __half* cacheK, const __half* cacheV,
                                                                 const infdev_query* queries, int queryCount, const int32_t* table, int tableStride,
                                                                 int blockTokens, uint32_t maxSplits, float* partials) {
   pdl_launch_dependents();
@@ -257,13 +257,22 @@ __global__ void __launch_bounds__(256) attention_reduce_kernel(const float* part
   uint32_t begin, end, count;
   split_range(attended, maxSplits, 0, begin, end, count);
   const float* src = partials + size_t(headRow) * maxSplits * kPartialStride;
-  float maximum = -1.0e30f;
-  for (uint32_t s = 0; s < count; ++s)
-    maximum = fmaxf(maximum, src[s * kPartialStride + kDim]);
+  // Lane s of every warp fetches the running maximum and norm of split s (at most 32 splits) in one trip to the L2; the
+  // weights of the splits then travel by shuffle, and the loop below has only independent loads, taken in split order
+  // so the sums are those of a sequential merge.
+  const uint32_t lane = dim & 31;
+  float splitMaximum = -1.0e30f, splitNorm = 0.f;
+  if (lane < count) {
+    const float2 pair = *reinterpret_cast<const float2*>(src + lane * kPartialStride + kDim);
+    splitMaximum = pair.x, splitNorm = pair.y;
+  }
+  const float maximum = warp_max(splitMaximum);
+  const float splitWeight = lane < count ? expf(splitMaximum - maximum) : 0.f;
   float norm = 0.f, numerator = 0.f;
+#pragma unroll 8
   for (uint32_t s = 0; s < count; ++s) {
-    const float w = expf(src[s * kPartialStride + kDim] - maximum);
-    norm += src[s * kPartialStride + kDim + 1] * w;
+    const float w = __shfl_sync(0xffffffffu, splitWeight, int(s));
+    norm += __shfl_sync(0xffffffffu, splitNorm, int(s)) * w;
     numerator += src[s * kPartialStride + dim] * w;
   }
   const float gate = qg[size_t(headRow) * kDim * 2 + kDim + dim];

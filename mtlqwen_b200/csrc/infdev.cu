@@ -762,6 +762,8 @@ int infdev_sample(infdev_ctx* ctx, const float* logits, int64_t vocab, infdev_qu
 int infdev_pack_queries(infdev_ctx* ctx, const infdev_query* in, int count, int drafting, uint32_t draftWidth, const uint64_t* statePrevious,
                         const uint64_t* stateNext, uint64_t candidateBase, uint64_t stateBytes, infdev_query* out, uint32_t* meta) {
   Bind bind(ctx);
+  if (count < 0 || count > 32)
+    return fail(ctx, INFDEV_E_ARGUMENT, "pack_queries: at most 32 queries per pass");
   ctx->launches += 1;
   return check(ctx,
                infdev::pack_queries_launch(in, count, drafting, draftWidth, statePrevious, stateNext, candidateBase, stateBytes, out, meta, ctx->stream),

@@ -287,33 +287,49 @@ __global__ void pack_queries_kernel(const infdev_query* in, int count, int draft
                                     const uint64_t* stateNext, uint64_t candidateBase, uint64_t stateBytes, infdev_query* out, uint32_t* meta) {
   pdl_launch_dependents();
   pdl_wait();
-  if (threadIdx.x || blockIdx.x)
+  // One lane per query (at most 32): the records and the state addresses live in host-visible memory, so every read is
+  // a trip over PCIe; the lanes make theirs at the same time and the running totals come from a warp scan.
+  const uint32_t lane = threadIdx.x;
+  if (blockIdx.x || lane >= 32)
     return;
-  uint32_t rows = 0, logits = 0, flags = 0, packed = 0;
-  for (int i = 0; i < count; ++i) {
-    infdev_query query = in[i];
-    const bool speculative = query.state != kUnbound;
-    if (drafting && !speculative)
-      continue;
+  infdev_query query = {};
+  bool keep = false, speculative = false;
+  if (int(lane) < count) {
+    query = in[lane];
+    speculative = query.state != kUnbound;
+    keep = !(drafting && !speculative);
+  }
+  uint32_t flags = 0;
+  if (keep) {
     const uint32_t requested = query.samples;
-    query.start = rows;
     if (drafting)
       query.count = 1;
     query.samples = drafting ? 1 : speculative ? query.count : (query.position + query.count == requested ? 1u : 0u);
-    flags |= (speculative || query.count == 1) ? 1u : 0u;
-    flags |= (!speculative && query.count > 1) ? 2u : 0u;
+    flags = ((speculative || query.count == 1) ? 1u : 0u) | ((!speculative && query.count > 1) ? 2u : 0u);
     query.previous = query.position ? statePrevious[query.slot] : 0;
     query.next = speculative ? candidateBase + uint64_t(query.state) * stateBytes : stateNext[query.slot];
-    query.logit = logits;
-    out[packed++] = query;
-    logits += query.samples;
-    rows += query.count;
+  }
+  // inclusive scans of rows, logit rows and kept queries over the lanes
+  uint32_t rows = keep ? query.count : 0u, logits = keep ? query.samples : 0u, packed = keep ? 1u : 0u;
+#pragma unroll
+  for (int step = 1; step < 32; step <<= 1) {
+    const uint32_t r = __shfl_up_sync(0xffffffffu, rows, step), l = __shfl_up_sync(0xffffffffu, logits, step), k = __shfl_up_sync(0xffffffffu, packed, step);
+    if (int(lane) >= step)
+      rows += r, logits += l, packed += k;
+  }
+  flags = __reduce_or_sync(0xffffffffu, flags);
+  if (keep) {
+    query.start = rows - query.count;
+    query.logit = logits - query.samples;
+    out[packed - 1] = query;
   }
   (void)draftWidth;
-  meta[0] = rows;
-  meta[1] = logits;
-  meta[2] = flags;
-  meta[3] = packed;
+  if (lane == 31) {
+    meta[0] = rows;
+    meta[1] = logits;
+    meta[2] = flags;
+    meta[3] = packed;
+  }
 }
 
 // The acceptance loop of Engine::schedule (engine.cpp:205-216) on the device, one thread per query. For query i it
