@@ -67,11 +67,27 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float* logits, i
     // first-index argmax (native_ops.metal:137-158)
     float best = -INFINITY;
     int index = 0;
-    for (int j = tid; j < vocab; j += kThreads) {
-      const float v = row[j];
-      if (v > best) {
-        best = v;
-        index = j;
+    if (vocab % 4 == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {  // four logits per load, visited in ascending order
+      const float4* row4 = reinterpret_cast<const float4*>(row);
+#pragma unroll 4
+      for (int j = tid; j < vocab / 4; j += kThreads) {
+        const float4 v = row4[j];
+        if (v.x > best)
+          best = v.x, index = 4 * j;
+        if (v.y > best)
+          best = v.y, index = 4 * j + 1;
+        if (v.z > best)
+          best = v.z, index = 4 * j + 2;
+        if (v.w > best)
+          best = v.w, index = 4 * j + 3;
+      }
+    } else {
+      for (int j = tid; j < vocab; j += kThreads) {
+        const float v = row[j];
+        if (v > best) {
+          best = v;
+          index = j;
+        }
       }
     }
 #pragma unroll
