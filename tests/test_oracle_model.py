@@ -31,6 +31,22 @@ def test_multi_token_pass_equals_single_steps(tensors):
   assert stepped.length == passed.length == 7
 
 
+def test_results_do_not_depend_on_the_thread_count(tensors):
+  """The oracle's loops are parallel over weight rows, heads and sequences, never over a summation index: one thread and
+  all threads give the same bits (the one-thread and all-core timings of the bench time the same arithmetic)."""
+  import os
+  tokens = [5, 17, 300, 400, 12, 9, 77, 1, 2, 3]
+  results = []
+  for threads in (1, max(2, os.cpu_count() or 2)):
+    oracle.set_threads(threads)
+    model = oracle.Model(tensors, LAYERS, VOCAB, 32)
+    hidden, logits = model.forward(tokens, 2)
+    results.append((hidden.copy(), logits.copy(), model.step(44)[1].copy()))
+  oracle.set_threads(max(1, os.cpu_count() or 1))
+  for one, many in zip(*results):
+    assert one.tobytes() == many.tobytes()
+
+
 def test_batched_decode_equals_solo_steps(tensors):
   batch = [oracle.Model(tensors, LAYERS, VOCAB, 32) for _ in range(3)]
   solo = [oracle.Model(tensors, LAYERS, VOCAB, 32) for _ in range(3)]
